@@ -1,0 +1,43 @@
+"""ctypes binding of libftb200.so (include/ftb200.h)."""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libftb200.so")
+
+
+class FtbError(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__("[FT][ERROR] ftb200 status %d: %s" % (status, msg))
+        self.status = status
+
+
+from ._abi import SamplingParams  # noqa: E402,F401
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "libftb200.so is not built (%s). Run `python -m fastertransformer_b200.build`; "
+            "there is no CPU fallback for the sampling kernels." % LIB_PATH)
+    l = C.CDLL(LIB_PATH)
+    l.ftb200_version.restype = C.c_char_p
+    l.ftb200_last_error_string.restype = C.c_char_p
+    l.ftb200_curand_init.argtypes = [C.c_void_p, C.c_int, C.c_ulonglong, C.c_void_p, C.c_void_p]
+    l.ftb200_curand_peek_uniforms.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    l.ftb200_setup_topk_runtime_args.argtypes = [
+        C.c_int, C.c_uint32, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    l.ftb200_setup_topp_runtime_args.argtypes = [
+        C.c_int, C.c_uint32, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    l.ftb200_sampling_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
+    l.ftb200_decode_step_sampling.argtypes = [C.POINTER(SamplingParams)]
+    return l
+
+
+lib = _load()
+
+
+def check(status):
+    if status != 0:
+        raise FtbError(status, lib.ftb200_last_error_string().decode())

@@ -1,0 +1,80 @@
+"""Build the sm_100a shared library of the decode-sampling kernels, in-tree.
+
+`python -m fastertransformer_b200.build` compiles every .cu under csrc/ with nvcc for
+compute_100a/sm_100a and links fastertransformer_b200/lib/libftb200.so.  Objects are rebuilt only
+when a source or header is newer.  The flags mirror the reference's release build
+(--use_fast_math, CMakeLists.txt:77 and :200-201 of FasterTransformer) because the kernels promise the
+same approximate exp / log / divide instructions.
+"""
+import concurrent.futures
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+INC = os.path.join(os.path.dirname(HERE), "include")
+OUT = os.path.join(HERE, "lib")
+OBJ = os.path.join(OUT, "obj")
+LIB = os.path.join(OUT, "libftb200.so")
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "--use_fast_math", "-lineinfo",
+    "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC", "-I" + INC, "-I" + CSRC,
+]
+
+
+def _newest_header():
+    t = 0.0
+    for d in (CSRC, INC):
+        for root, _, files in os.walk(d):
+            for f in files:
+                if f.endswith((".h", ".cuh")):
+                    t = max(t, os.path.getmtime(os.path.join(root, f)))
+    return t
+
+
+def _sources():
+    out = []
+    for root, _, files in os.walk(CSRC):
+        for f in sorted(files):
+            if f.endswith((".cu", ".cc")):
+                out.append(os.path.join(root, f))
+    return out
+
+
+def _compile(src, obj, verbose):
+    cmd = [NVCC] + FLAGS + ["-x", "cu", "-c", src, "-o", obj]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    return src, r.returncode, r.stdout + r.stderr
+
+
+def build(verbose=False, force=False):
+    os.makedirs(OBJ, exist_ok=True)
+    hdr_t = _newest_header()
+    jobs, objs = [], []
+    for src in _sources():
+        obj = os.path.join(OBJ, os.path.relpath(src, CSRC).replace(os.sep, "_").rsplit(".", 1)[0] + ".o")
+        objs.append(obj)
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_t):
+            jobs.append((src, obj))
+    if jobs:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
+            for src, rc, log in ex.map(lambda j: _compile(j[0], j[1], verbose), jobs):
+                if verbose or rc != 0:
+                    sys.stderr.write(log)
+                if rc != 0:
+                    raise RuntimeError("nvcc failed on " + src)
+    if jobs or not os.path.exists(LIB):
+        r = subprocess.run([NVCC, "-shared", "-o", LIB] + objs + ["-lcudart"], capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))

@@ -1,0 +1,113 @@
+// Shared device helpers for the decode-sampling kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace ftb200 {
+
+typedef unsigned long long u64;
+typedef unsigned int       u32;
+
+// ---- error plumbing shared by the extern "C" entry points --------------------------------------
+void        set_error(const std::string& msg);
+const char* get_error();
+void        note_launch(int n);
+void        reset_launch_count();
+
+#define FTB_CUDA_CHECK(expr)                                                                                           \
+    do {                                                                                                               \
+        cudaError_t e__ = (expr);                                                                                      \
+        if (e__ != cudaSuccess) {                                                                                      \
+            ftb200::set_error(std::string(#expr) + ": " + cudaGetErrorString(e__));                                    \
+            return FTB200_CUDA_ERROR;                                                                                  \
+        }                                                                                                              \
+    } while (0)
+
+// ---- order-preserving integer image of a float ---------------------------------------------------
+// key(a) < key(b)  <=>  a < b   for all non-NaN a, b (with -0 < +0).
+__device__ __forceinline__ u32 fkey(float x)
+{
+    u32 b = __float_as_uint(x);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float fkey_inv(u32 k)
+{
+    u32 b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(b);
+}
+
+// 16-byte read-only load that does not pollute L1.
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p)
+{
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+// ---- in-place ascending sort of u64 keys by a cooperating thread group ---------------------------
+// Bitonic network in its "all ascending" form (first sub-step of every merge compares mirrored
+// positions), which tolerates any n: positions >= n behave as +infinity and are never touched.
+// `sync` is __syncthreads for a whole CTA or __syncwarp for one warp.
+template<class Sync>
+__device__ __forceinline__ void group_sort_u64(u64* a, int n, int tid, int nthr, Sync sync)
+{
+    if (n < 2) {
+        return;
+    }
+    int np = 1;
+    while (np < n) {
+        np <<= 1;
+    }
+    const int half = np >> 1;
+    for (int k = 2; k <= np; k <<= 1) {
+        const int hk = k >> 1;
+        for (int i = tid; i < half; i += nthr) {
+            int l = (i / hk) * k + (i % hk);
+            int h = l ^ (k - 1);
+            if (h < n) {
+                u64 x = a[l], y = a[h];
+                if (x > y) {
+                    a[l] = y;
+                    a[h] = x;
+                }
+            }
+        }
+        sync();
+        for (int j = k >> 2; j > 0; j >>= 1) {
+            for (int i = tid; i < half; i += nthr) {
+                int l = 2 * i - (i & (j - 1));
+                int h = l + j;
+                if (h < n) {
+                    u64 x = a[l], y = a[h];
+                    if (x > y) {
+                        a[l] = y;
+                        a[h] = x;
+                    }
+                }
+            }
+            sync();
+        }
+    }
+}
+
+struct CtaSync {
+    __device__ __forceinline__ void operator()() const
+    {
+        __syncthreads();
+    }
+};
+struct WarpSync {
+    __device__ __forceinline__ void operator()() const
+    {
+        __syncwarp();
+    }
+};
+
+}  // namespace ftb200

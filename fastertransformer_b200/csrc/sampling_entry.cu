@@ -1,0 +1,201 @@
+// extern "C" entry of the fused decode-sampling step: argument checks, shared-memory plan, launch.
+#include "sampling_params.cuh"
+
+namespace ftb200 {
+
+template<int DT>
+int sampling_occupancy(size_t smem, int* per_sm);
+template<int DT>
+int sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st);
+extern template int sampling_occupancy<FTB200_F32>(size_t, int*);
+extern template int sampling_occupancy<FTB200_F16>(size_t, int*);
+extern template int sampling_occupancy<FTB200_BF16>(size_t, int*);
+extern template int sampling_launch<FTB200_F32>(const KParams&, int, size_t, cudaStream_t);
+extern template int sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
+extern template int sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
+
+static int sm_count()
+{
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) {
+            n = 148;
+        }
+    }
+    return n;
+}
+
+constexpr int kMaxCtasPerSm = 4;
+
+static size_t scratch_stride_for(int vocab_padded)
+{
+    return ((size_t)vocab_padded + 255) / 256 * 256;
+}
+
+}  // namespace ftb200
+
+using namespace ftb200;
+
+extern "C" int ftb200_sampling_workspace_bytes(int dtype, int local_batch_size, int vocab_size_padded, size_t* bytes)
+{
+    if (bytes == nullptr || local_batch_size < 0 || vocab_size_padded <= 0 || dtype < 0 || dtype > 2) {
+        set_error("ftb200_sampling_workspace_bytes: invalid argument");
+        return FTB200_INVALID_ARG;
+    }
+    size_t ctas = (size_t)sm_count() * kMaxCtasPerSm;
+    if ((size_t)local_batch_size < ctas) {
+        ctas = (size_t)local_batch_size;
+    }
+    *bytes = 256 + ctas * scratch_stride_for(vocab_size_padded) * sizeof(u64);
+    return FTB200_OK;
+}
+
+extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
+{
+    reset_launch_count();
+    if (p == nullptr || p->logits == nullptr || p->end_ids == nullptr || p->output_ids == nullptr) {
+        set_error("ftb200_decode_step_sampling: null logits / end_ids / output_ids");
+        return FTB200_INVALID_ARG;
+    }
+    if (p->dtype < 0 || p->dtype > 2 || p->local_batch_size < 0 || p->vocab_size <= 0
+        || p->vocab_size_padded < p->vocab_size || p->batch_size < p->local_batch_size || p->step < 0) {
+        set_error("ftb200_decode_step_sampling: bad shape or dtype");
+        return FTB200_INVALID_ARG;
+    }
+    if (p->vocab_size_padded > (1 << 21)) {
+        set_error("ftb200_decode_step_sampling: vocab_size_padded above 2^21 is not supported");
+        return FTB200_UNSUPPORTED;
+    }
+    if (p->topk_states == nullptr && p->topp_states == nullptr) {
+        set_error("ftb200_decode_step_sampling: neither a top-k nor a top-p layer state was given");
+        return FTB200_INVALID_ARG;
+    }
+    if (p->topk_states != nullptr) {
+        if (p->topk_ks == nullptr || p->topk_ps == nullptr) {
+            set_error("ftb200_decode_step_sampling: top-k layer needs topk_ks and topk_ps");
+            return FTB200_INVALID_ARG;
+        }
+        if (p->max_top_k < 1 || p->max_top_k > kMaxTopK) {
+            set_error("top-k kernel supports 1<=k<=1024 but got k=" + std::to_string(p->max_top_k));
+            return FTB200_DOMAIN_ERROR;
+        }
+    }
+    if (p->topp_states != nullptr && p->topp_ps == nullptr) {
+        set_error("ftb200_decode_step_sampling: top-p layer needs topp_ps");
+        return FTB200_INVALID_ARG;
+    }
+    if ((p->apply_temperature && p->temperature == nullptr) || (p->apply_repetition && p->repetition_penalty == nullptr)
+        || (p->apply_min_length && (p->min_lengths == nullptr || p->sequence_length == nullptr))) {
+        set_error("ftb200_decode_step_sampling: a penalty is switched on without its per-row array");
+        return FTB200_INVALID_ARG;
+    }
+    if (p->local_batch_size == 0) {
+        return FTB200_OK;
+    }
+    size_t need = 0;
+    ftb200_sampling_workspace_bytes(p->dtype, p->local_batch_size, p->vocab_size_padded, &need);
+    if (p->workspace == nullptr || p->workspace_bytes < need) {
+        set_error("ftb200_decode_step_sampling: workspace too small, need " + std::to_string(need) + " bytes");
+        return FTB200_WORKSPACE_SMALL;
+    }
+
+    KParams K;
+    K.dtype            = p->dtype;
+    K.batch_size       = p->batch_size;
+    K.local_batch      = p->local_batch_size;
+    K.ite              = p->ite;
+    K.vocab            = p->vocab_size;
+    K.vocab_padded     = p->vocab_size_padded;
+    K.step             = p->step;
+    K.max_input_len    = p->max_input_length;
+    K.logits           = p->logits;
+    K.bias             = p->embedding_bias;
+    K.end_ids          = p->end_ids;
+    K.input_lengths    = p->input_lengths;
+    K.output_ids       = p->output_ids;
+    K.bad_words        = p->bad_words_len > 0 ? p->bad_words : nullptr;
+    K.bad_words_len    = p->bad_words_len;
+    K.bad_words_shared = p->bad_words_shared;
+    K.temperature      = p->temperature;
+    K.apply_temp       = p->apply_temperature ? 1 : 0;
+    K.rep_penalty      = p->repetition_penalty;
+    K.penalty_type     = p->penalty_type;
+    K.apply_rep        = (p->apply_repetition && p->penalty_type != FTB200_PENALTY_NONE) ? 1 : 0;
+    K.min_lengths      = p->min_lengths;
+    K.apply_minlen     = p->apply_min_length ? 1 : 0;
+    K.topk_states      = (curandState_t*)p->topk_states;
+    K.topk_ks          = p->topk_ks;
+    K.topk_ps          = p->topk_ps;
+    K.topk_skip        = p->topk_skip;
+    K.max_top_k        = p->topk_states != nullptr ? p->max_top_k : 1;
+    K.topp_states      = (curandState_t*)p->topp_states;
+    K.topp_ps          = p->topp_ps;
+    K.topp_skip        = p->topp_skip;
+    K.topp_initial     = p->topp_initial_ps;
+    K.topp_decay       = (p->topp_decay && p->topp_min && p->topp_reset_ids && p->topp_initial_ps) ? p->topp_decay : nullptr;
+    K.topp_min         = p->topp_min;
+    K.topp_reset       = p->topp_reset_ids;
+    K.seq_len          = p->sequence_length;
+    K.finished         = p->finished;
+    K.cum_log_probs    = p->cum_log_probs;
+    K.out_log_probs    = p->output_log_probs;
+
+    // shared-memory plan: candidates, histogram, 1024 floats, vector flags, token hash
+    const int epv      = p->dtype == FTB200_F32 ? 4 : 8;
+    K.flag_words       = (p->vocab_size_padded / epv + 32) / 32;
+    int specials       = (K.apply_rep ? p->step : 0) + (K.bad_words ? p->bad_words_len : 0) + 2;
+    int slots          = 64;
+    while (slots < 2 * specials) {
+        slots <<= 1;
+    }
+    K.hash_slots = slots;
+    int lg       = 0;
+    while ((1 << lg) < slots) {
+        ++lg;
+    }
+    K.hash_shift = 32 - lg;
+    size_t smem  = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 4;
+    if (smem > 200 * 1024) {
+        set_error("ftb200_decode_step_sampling: token history too long for the shared-memory hash");
+        return FTB200_UNSUPPORTED;
+    }
+
+    int per_sm = 0, rc;
+    switch (p->dtype) {
+        case FTB200_F32: rc = sampling_occupancy<FTB200_F32>(smem, &per_sm); break;
+        case FTB200_F16: rc = sampling_occupancy<FTB200_F16>(smem, &per_sm); break;
+        default: rc = sampling_occupancy<FTB200_BF16>(smem, &per_sm); break;
+    }
+    if (rc != FTB200_OK) {
+        return rc;
+    }
+    if (per_sm < 1) {
+        set_error("ftb200_decode_step_sampling: kernel does not fit on an SM");
+        return FTB200_UNSUPPORTED;
+    }
+    if (per_sm > kMaxCtasPerSm) {
+        per_sm = kMaxCtasPerSm;
+    }
+    int grid = sm_count() * per_sm;
+    if (grid > p->local_batch_size) {
+        grid = p->local_batch_size;
+    }
+    K.ticket         = (u32*)p->workspace;
+    K.scratch        = (u64*)((char*)p->workspace + 256);
+    K.scratch_stride = scratch_stride_for(p->vocab_size_padded);
+
+    cudaStream_t st = (cudaStream_t)p->stream;
+    FTB_CUDA_CHECK(cudaMemsetAsync(K.ticket, 0, 256, st));
+    switch (p->dtype) {
+        case FTB200_F32: rc = sampling_launch<FTB200_F32>(K, grid, smem, st); break;
+        case FTB200_F16: rc = sampling_launch<FTB200_F16>(K, grid, smem, st); break;
+        default: rc = sampling_launch<FTB200_BF16>(K, grid, smem, st); break;
+    }
+    if (rc == FTB200_OK) {
+        note_launch(1);
+    }
+    return rc;
+}

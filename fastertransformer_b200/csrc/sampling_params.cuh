@@ -1,0 +1,59 @@
+// Constants and the kernel argument block of the fused decode-sampling step.
+#pragma once
+#include <curand_kernel.h>
+
+#include "common.cuh"
+#include "ftb200.h"
+
+namespace ftb200 {
+
+constexpr int kThreads   = 256;
+constexpr int kWarps     = kThreads / 32;
+constexpr int kNB        = 4096;  // histogram buckets
+constexpr int kCap       = 4096;  // candidate slots held in shared memory
+constexpr int kUnroll    = 4;     // 16-byte loads in flight per thread
+constexpr int kMaxTopK   = 1024;
+constexpr int kLinScale  = 64;    // linear buckets per logit unit below the row maximum
+constexpr int kWarpTile  = kCap / kWarps;
+constexpr u32 kHashEmpty = 0xffffffffu;
+constexpr u32 kFlagHist  = 1u;  // id occurs in the row's token history -> repetition / presence penalty
+constexpr u32 kFlagDead  = 2u;  // banned word or min-length mask -> can never be selected
+
+struct KParams {
+    int dtype, batch_size, local_batch, ite, vocab, vocab_padded, step, max_input_len;
+    const void* logits;
+    const void* bias;
+    const int*  end_ids;
+    const int*  input_lengths;
+    int*        output_ids;
+    const int*  bad_words;
+    int         bad_words_len, bad_words_shared;
+    const float* temperature;
+    int          apply_temp;
+    const float* rep_penalty;
+    int          penalty_type, apply_rep;
+    const int*   min_lengths;
+    int          apply_minlen;
+    curandState_t* topk_states;
+    const u32*     topk_ks;
+    const float*   topk_ps;
+    const uint8_t* topk_skip;
+    int            max_top_k;
+    curandState_t* topp_states;
+    float*         topp_ps;
+    const uint8_t* topp_skip;
+    const float*   topp_initial;
+    const float*   topp_decay;
+    const float*   topp_min;
+    const int*     topp_reset;
+    int*     seq_len;
+    uint8_t* finished;
+    float*   cum_log_probs;
+    float*   out_log_probs;
+    u32*     ticket;
+    u64*     scratch;         // per-CTA candidate overflow area
+    size_t   scratch_stride;  // u64 entries per CTA
+    int      hash_slots, hash_shift, flag_words;
+};
+
+}  // namespace ftb200

@@ -1,0 +1,228 @@
+"""Host-side mirror of FasterTransformer's DynamicDecodeLayer for the sampling path (beam_width == 1).
+
+Same keys, dtypes and placement as the reference's TensorMap interface
+(layers/DynamicDecodeLayer.cc:153-178 setup, :191-474 forward): runtime arguments are host arrays of
+shape [1] or [batch]; logits, ids and state live on the GPU.  torch is used only to own device memory
+and streams; every computation is a call into libftb200.so through the C ABI.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ._lib import SamplingParams, check, lib
+
+_DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+CURAND_STATE_BYTES = 48  # sizeof(curandState_t), XORWOW
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class _SamplingLayerState:
+    """Buffers one reference sampling layer keeps (BaseSamplingLayer.cc:29-53, TopK/TopP allocateBuffer)."""
+
+    def __init__(self, batch, device):
+        self.curand = torch.zeros(batch * CURAND_STATE_BYTES, dtype=torch.uint8, device=device)
+        self.top_ks = torch.zeros(batch, dtype=torch.int32, device=device)  # uint32 payload
+        self.top_ps = torch.zeros(batch, dtype=torch.float32, device=device)
+        self.skip = torch.zeros(batch, dtype=torch.uint8, device=device)
+        self.skip_host = np.ones(batch, dtype=bool)
+        self.active = False
+
+
+class DynamicDecodeLayer:
+    """Drop-in for the sampling half of fastertransformer::DynamicDecodeLayer<T>."""
+
+    def __init__(self, vocab_size, vocab_size_padded, dtype=torch.float32, device="cuda:0", stream=None):
+        self.vocab_size = int(vocab_size)
+        self.vocab_size_padded = int(vocab_size_padded)
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.stream = stream
+        self._workspace = None
+        self.launches = 0
+
+    # ---- helpers -------------------------------------------------------------------------------
+    def _stream_ptr(self):
+        s = self.stream if self.stream is not None else torch.cuda.current_stream(self.device)
+        return C.c_void_p(s.cuda_stream)
+
+    @staticmethod
+    def _arg(args, key):
+        v = args.get(key)
+        if v is None:
+            return None
+        return np.atleast_1d(np.asarray(v))
+
+    def _broadcast(self, arr, batch, dtype, default):
+        if arr is None:
+            arr = np.asarray([default], dtype=dtype)
+        arr = arr.astype(dtype)
+        if arr.size == 1:
+            return np.full(batch, arr[0], dtype=dtype)
+        if arr.size != batch:
+            raise ValueError("runtime argument must have shape [1] or [batch_size]")
+        return arr.copy()
+
+    # ---- setup (DynamicDecodeLayer.cc:153-178 -> TopK/TopPSamplingLayer::setup) -------------------
+    def setup(self, batch_size, beam_width, runtime_args):
+        if beam_width != 1:
+            raise NotImplementedError("beam search is served by fastertransformer_b200.beam_search")
+        B, dev, st = int(batch_size), self.device, self._stream_ptr()
+        self.batch_size = B
+        a = runtime_args
+        top_k = self._arg(a, "runtime_top_k")
+        top_p = self._arg(a, "runtime_top_p")
+        seeds = self._arg(a, "random_seed")
+        if "repetition_penalty" in a and "presence_penalty" in a:
+            raise RuntimeError("[FT][ERROR] Found ambiguous parameters repetition_penalty and presence_penalty "
+                               "which are mutually exclusive.")
+        # BaseSamplingLayer::setup (BaseSamplingLayer.cc:112-206)
+        self.temperature_host = self._broadcast(self._arg(a, "temperature"), B, np.float32, 1.0)
+        if "repetition_penalty" in a:
+            self.penalty_type, pen = 1, self._arg(a, "repetition_penalty")
+        elif "presence_penalty" in a:
+            self.penalty_type, pen = 0, self._arg(a, "presence_penalty")
+        else:
+            self.penalty_type, pen = 2, None
+        default_pen = 1.0 if self.penalty_type == 1 else 0.0
+        self.penalty_default = default_pen
+        self.penalty_host = self._broadcast(pen, B, np.float32, default_pen)
+        self.min_length_host = self._broadcast(self._arg(a, "min_length"), B, np.int32, 0)
+        self.temperature = torch.from_numpy(self.temperature_host).to(dev)
+        self.penalty = torch.from_numpy(self.penalty_host).to(dev)
+        self.min_length = torch.from_numpy(self.min_length_host).to(dev)
+
+        self.topk = _SamplingLayerState(B, dev)
+        self.topp = _SamplingLayerState(B, dev)
+        for layer in (self.topk, self.topp):
+            if seeds is None:
+                check(lib.ftb200_curand_init(_ptr(layer.curand), B, 0, None, st))
+            elif seeds.size == 1:
+                check(lib.ftb200_curand_init(_ptr(layer.curand), B, int(seeds[0]), None, st))
+            else:
+                if seeds.size != B:
+                    raise RuntimeError("[FT][ERROR] random_seeds must be of shape [1] or [batch_size]")
+                sd = torch.from_numpy(seeds.astype(np.uint64).view(np.int64)).to(dev)
+                check(lib.ftb200_curand_init(_ptr(layer.curand), B, 0, _ptr(sd), st))
+                torch.cuda.current_stream(dev).synchronize()
+
+        # TopKSamplingLayer::setup (TopKSamplingLayer.cu:134-186)
+        k_arr = top_k.astype(np.uint32) if top_k is not None else np.zeros(1, np.uint32)
+        k_scalar = int(k_arr.max())
+        p_scalar = float(top_p[0]) if top_p is not None else 0.0
+        if k_arr.size > 1:
+            self.topk.top_ks.copy_(torch.from_numpy(k_arr.view(np.int32)))
+        if top_p is not None and top_p.size > 1:
+            self.topk.top_ps.copy_(torch.from_numpy(top_p.astype(np.float32)))
+        check(lib.ftb200_setup_topk_runtime_args(B, k_scalar, _ptr(self.topk.top_ks), int(k_arr.size), p_scalar,
+                                                 _ptr(self.topk.top_ps), 0 if top_p is None else int(top_p.size),
+                                                 _ptr(self.topk.skip), st))
+        self.topk.skip_host = self.topk.skip.cpu().numpy().astype(bool)
+        self.max_top_k = int(self.topk.top_ks.cpu().numpy().view(np.uint32).max())
+        self.topk.active = True
+
+        # TopPSamplingLayer::setup (TopPSamplingLayer.cu:184-253)
+        if top_p is None:
+            self.topp.skip_host[:] = True
+            self.topp.active = False
+        else:
+            self.topp.initial = torch.zeros(B, dtype=torch.float32, device=dev)
+            self.topp.decay = torch.zeros(B, dtype=torch.float32, device=dev)
+            self.topp.min = torch.zeros(B, dtype=torch.float32, device=dev)
+            self.topp.reset = torch.zeros(B, dtype=torch.int32, device=dev)
+            if k_arr.size > 1:
+                self.topp.top_ks.copy_(torch.from_numpy(k_arr.view(np.int32)))
+            if top_p.size > 1:
+                self.topp.top_ps.copy_(torch.from_numpy(top_p.astype(np.float32)))
+            check(lib.ftb200_setup_topp_runtime_args(
+                B, int(k_arr[0]), _ptr(self.topp.top_ks), int(k_arr.size), p_scalar, _ptr(self.topp.top_ps),
+                int(top_p.size), _ptr(self.topp.skip), _ptr(self.topp.initial), _ptr(self.topp.decay),
+                _ptr(a.get("top_p_decay")), _ptr(self.topp.min), _ptr(a.get("top_p_min")), _ptr(self.topp.reset),
+                _ptr(a.get("top_p_reset_ids")), st))
+            self.topp.skip_host = self.topp.skip.cpu().numpy().astype(bool)
+            self.topp.active = True
+
+    # ---- forward (DynamicDecodeLayer.cc:191-474, sampling branch) ---------------------------------
+    def forward(self, outputs, inputs):
+        logits = inputs["logits"]
+        B = logits.shape[0]
+        step = int(inputs["step"])
+        ite = int(inputs.get("ite", 0))
+        lbs = int(inputs.get("local_batch_size", B))
+        mil = int(inputs["max_input_length"])
+        lo, hi = ite * lbs, (ite + 1) * lbs
+        Vp = self.vocab_size_padded
+        es = logits.element_size()
+
+        topk_on = self.topk.active and not self.topk.skip_host[lo:hi].all()
+        topp_on = self.topp.active and not self.topp.skip_host[lo:hi].all()
+        if not (topk_on or topp_on):
+            return
+
+        P = SamplingParams()
+        P.dtype = _DT[logits.dtype]
+        P.batch_size, P.local_batch_size, P.ite = B, lbs, ite
+        P.vocab_size, P.vocab_size_padded = self.vocab_size, Vp
+        P.step, P.max_input_length = step, mil
+        P.logits = logits.data_ptr() + lo * Vp * es
+        bias = inputs.get("embedding_bias")
+        P.embedding_bias = None if bias is None else bias.data_ptr()
+        P.end_ids = inputs["end_id"].data_ptr() + lo * 4
+        il = inputs.get("input_lengths")
+        P.input_lengths = None if il is None else il.data_ptr() + lo * 4
+        P.output_ids = outputs["output_ids"].data_ptr()
+        bw = inputs.get("bad_words_list")
+        if bw is not None:
+            shared = bw.dim() == 2 or bw.shape[0] == 1
+            L = bw.shape[-1]
+            P.bad_words = bw.data_ptr() if shared else bw.data_ptr() + lo * 2 * L * 4
+            P.bad_words_len, P.bad_words_shared = L, int(shared)
+        # host-side gating of the penalty kernels (BaseSamplingLayer.cc:302-349)
+        P.temperature = self.temperature.data_ptr() + lo * 4
+        P.apply_temperature = int(bias is not None or bool((self.temperature_host[lo:hi] != 1.0).any()))
+        P.repetition_penalty = self.penalty.data_ptr() + lo * 4
+        P.penalty_type = self.penalty_type
+        P.apply_repetition = int(step > 1 and self.penalty_type != 2
+                                 and bool((self.penalty_host[lo:hi] != self.penalty_default).any()))
+        P.min_lengths = self.min_length.data_ptr() + lo * 4
+        P.apply_min_length = int(bool((self.min_length_host[lo:hi] > step - mil).any()))
+
+        if topk_on:
+            P.topk_states = self.topk.curand.data_ptr() + lo * CURAND_STATE_BYTES
+            P.topk_ks = self.topk.top_ks.data_ptr() + lo * 4
+            P.topk_ps = self.topk.top_ps.data_ptr() + lo * 4
+            P.topk_skip = self.topk.skip.data_ptr() + lo
+            P.max_top_k = self.max_top_k
+        if topp_on:
+            P.topp_states = self.topp.curand.data_ptr() + lo * CURAND_STATE_BYTES
+            P.topp_ps = self.topp.top_ps.data_ptr() + lo * 4
+            P.topp_skip = self.topp.skip.data_ptr() + lo
+            P.topp_initial_ps = self.topp.initial.data_ptr() + lo * 4
+            P.topp_decay = self.topp.decay.data_ptr() + lo * 4
+            P.topp_min = self.topp.min.data_ptr() + lo * 4
+            P.topp_reset_ids = self.topp.reset.data_ptr() + lo * 4
+
+        def sl(key, width):
+            t = outputs.get(key)
+            return None if t is None else t.data_ptr() + lo * width
+
+        P.sequence_length = sl("sequence_length", 4)
+        P.finished = sl("finished", 1)
+        P.cum_log_probs = sl("cum_log_probs", 4)
+        olp = outputs.get("output_log_probs")
+        if olp is not None:
+            # [request_output_len, batch] sliced at (step - max_input_length) (DynamicDecodeLayer.cc:427-435)
+            P.output_log_probs = olp.data_ptr() + ((step - mil) * B + lo) * 4
+
+        need = C.c_size_t(0)
+        check(lib.ftb200_sampling_workspace_bytes(P.dtype, lbs, Vp, C.byref(need)))
+        if self._workspace is None or self._workspace.numel() < need.value:
+            self._workspace = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+        P.workspace = self._workspace.data_ptr()
+        P.workspace_bytes = self._workspace.numel()
+        P.stream = self._stream_ptr().value
+        check(lib.ftb200_decode_step_sampling(C.byref(P)))
+        self.launches += lib.ftb200_last_launch_count()

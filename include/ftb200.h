@@ -1,0 +1,168 @@
+/*
+ * ftb200.h - C ABI of the B200 (sm_100a) decode-sampling kernels.
+ *
+ * This is the boundary a FasterTransformer build binds to in place of its own
+ * kernels/ directory for the per-step token-selection path.  Every entry point
+ * is `extern "C"`, takes plain pointers and sizes, returns an int status
+ * (0 = OK, see ftb200_status) and never throws.  All device pointers belong to
+ * the caller; all work is enqueued on the caller's stream.
+ *
+ * Each declaration names the reference interface it replaces, as
+ * path:line inside the FasterTransformer source tree.
+ */
+#ifndef FTB200_H
+#define FTB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    FTB200_OK              = 0,
+    FTB200_INVALID_ARG     = 1, /* null pointer, bad shape, unsupported dtype ...                      */
+    FTB200_DOMAIN_ERROR    = 2, /* top-k outside [1,1024]: the reference throws std::domain_error      */
+    FTB200_CUDA_ERROR      = 3, /* a CUDA runtime call failed; see ftb200_last_error_string()          */
+    FTB200_WORKSPACE_SMALL = 4, /* workspace_bytes below ftb200_sampling_workspace_bytes()             */
+    FTB200_UNSUPPORTED     = 5, /* shape outside what the kernels handle (e.g. history too long)       */
+    FTB200_TIMEOUT         = 6  /* a bounded wait ran out                                              */
+} ftb200_status;
+
+typedef enum {
+    FTB200_F32  = 0,
+    FTB200_F16  = 1,
+    FTB200_BF16 = 2 /* not in the reference: computed as the fp32 path on the up-cast values */
+} ftb200_dtype;
+
+/* Mirrors RepetitionPenaltyType, kernels/penalty_types.h:24-28. */
+typedef enum {
+    FTB200_PENALTY_ADDITIVE       = 0, /* presence penalty:   x - theta                    */
+    FTB200_PENALTY_MULTIPLICATIVE = 1, /* repetition penalty: x < 0 ? x * theta : x / theta */
+    FTB200_PENALTY_NONE           = 2
+} ftb200_penalty_type;
+
+const char* ftb200_version(void);
+/* Text of the last failure on the calling thread ("" if none). */
+const char* ftb200_last_error_string(void);
+
+/* ------------------------------------------------------------------------------------------
+ * curand state set-up.  `states` is curandState_t[n] (XORWOW, 48 bytes each), the same layout
+ * the reference keeps per layer (layers/sampling_layers/BaseSamplingLayer.h:38).
+ * Replaces invokeCurandInitialize / invokeCurandBatchInitialize,
+ * kernels/sampling_topk_kernels.cu:39-65.  `seeds` (device, n values) wins over `seed` when non-null.
+ * ------------------------------------------------------------------------------------------ */
+int ftb200_curand_init(void* states, int n, unsigned long long seed, const unsigned long long* seeds, void* stream);
+
+/* Draw `n_draws` uniforms per row from COPIES of the states (the states are not advanced).
+ * out is device float [n_draws, n].  Test/diagnostic helper; curand_uniform as the kernels call it. */
+int ftb200_curand_peek_uniforms(const void* states, int n, int n_draws, float* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Runtime-argument normalisation.
+ * top-k layer: setup_topk_runtime_args<1024>, layers/sampling_layers/TopKSamplingLayer.cu:28-77
+ *   k==0&&p==0 -> k=1;  k>0&&p==0 -> p=1;  k clipped to 1024;  p clipped to [0,1];  skip = (k==0).
+ * top-p layer: set_topp_runtime_args, layers/sampling_layers/TopPSamplingLayer.cu:30-109
+ *   k==0&&p==0 -> k=1;  p clipped;  skip = (k>0);  initial_top_p/decay/min/reset-id buffers filled.
+ * top_ks/top_ps are device arrays [batch] that already hold the per-row values when
+ * top_ks_size/top_ps_size > 1 and are overwritten with the normalised values.
+ * ------------------------------------------------------------------------------------------ */
+int ftb200_setup_topk_runtime_args(int batch, uint32_t top_k, uint32_t* top_ks, int top_ks_size, float top_p,
+                                   float* top_ps, int top_ps_size, uint8_t* skip_decode, void* stream);
+int ftb200_setup_topp_runtime_args(int batch, uint32_t top_k, uint32_t* top_ks, int top_ks_size, float top_p,
+                                   float* top_ps, int top_ps_size, uint8_t* skip_decode, float* initial_top_p,
+                                   float* top_p_decay_buf, const float* top_p_decay, float* top_p_min_buf,
+                                   const float* top_p_min, int32_t* top_p_reset_ids_buf,
+                                   const uint32_t* top_p_reset_ids, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * One fused decode-sampling step.
+ *
+ * Replaces, for beam_width == 1, everything DynamicDecodeLayer::forward launches between the
+ * logits GEMM and the stop criteria (layers/DynamicDecodeLayer.cc:247-283, 389-445):
+ *   invokeBanBadWords                       kernels/ban_bad_words.cu:88-120
+ *   invokeBatchApplyTemperaturePenalty      kernels/sampling_penalty_kernels.cu:181-206
+ *   invokeBatchApplyRepetitionPenalty       kernels/sampling_penalty_kernels.cu:426-459
+ *   invokeMinLengthPenalty                  kernels/sampling_penalty_kernels.cu:502-517
+ *   invokeAddBiasEndMask                    kernels/sampling_topk_kernels.cu:96-110
+ *   invokeAddBiasSoftMax                    kernels/sampling_topp_kernels.cu:1347-1356
+ *   invokeBatchTopKSampling                 kernels/sampling_topk_kernels.cu:345-396
+ *   invokeTopPInitialize / invokeBatchTopPSampling   kernels/sampling_topp_kernels.cu:790-799, 1006-1170
+ *   invokeComputeToppDecay                  kernels/sampling_topp_kernels.cu:1410-1427
+ * The logits are read, never written.  Results (ids, flags, lengths) equal the reference's.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb200_sampling_params {
+    /* ---- geometry ---- */
+    int dtype;             /* ftb200_dtype of logits and embedding_bias                              */
+    int batch_size;        /* rows of the whole request batch = row stride of output_ids            */
+    int local_batch_size;  /* rows handled by this call                                              */
+    int ite;               /* micro-batch index; local row r is global row ite*local_batch_size + r  */
+    int vocab_size;
+    int vocab_size_padded; /* row stride of logits; columns >= vocab_size are masked                 */
+    int step;              /* position being generated; ids land in output_ids[step, :]              */
+    int max_input_length;
+
+    /* ---- inputs (device) ---- */
+    const void* logits;         /* [local_batch_size, vocab_size_padded], first local row            */
+    const void* embedding_bias; /* [vocab_size_padded] or null                                       */
+    const int*  end_ids;        /* [local_batch_size]                                                */
+    const int*  input_lengths;  /* [local_batch_size] or null                                        */
+    int*        output_ids;     /* [max_seq_len, batch_size], whole tensor: history in, new ids out  */
+    const int*  bad_words;      /* [2, bad_words_len] (shared) or [local_batch_size, 2, len]; null ok */
+    int         bad_words_len;
+    int         bad_words_shared;
+
+    /* ---- per-row runtime arguments (device, [local_batch_size]) and the host-side gating the
+     *      reference applies before each penalty kernel (BaseSamplingLayer.cc:302-349) ---- */
+    const float* temperature;
+    int          apply_temperature; /* embedding_bias != null || any temperature != 1              */
+    const float* repetition_penalty;
+    int          penalty_type;      /* ftb200_penalty_type                                          */
+    int          apply_repetition;  /* step > 1 && type != NONE && any row != default               */
+    const int*   min_lengths;
+    int          apply_min_length;  /* any min_length > step - max_input_length                     */
+
+    /* ---- top-k layer state (null topk_states: layer absent) ---- */
+    void*           topk_states; /* curandState_t[local_batch_size]                                  */
+    const uint32_t* topk_ks;     /* normalised k per row                                             */
+    const float*    topk_ps;     /* normalised p per row                                             */
+    const uint8_t*  topk_skip;   /* 1 = row not handled by the top-k layer                           */
+    int             max_top_k;   /* max k over the WHOLE batch (selects the reference's block sizes,
+                                    sampling_topk_kernels.cu:388-392, which fix its tie order)      */
+
+    /* ---- top-p layer state (null topp_states: layer absent) ---- */
+    void*          topp_states;
+    float*         topp_ps;      /* in/out: decayed after the step                                   */
+    const uint8_t* topp_skip;
+    const float*   topp_initial_ps;
+    const float*   topp_decay;
+    const float*   topp_min;
+    const int32_t* topp_reset_ids;
+
+    /* ---- outputs (device, first local row; null = not wanted) ---- */
+    int*     sequence_length;
+    uint8_t* finished; /* bool[local_batch_size], in/out */
+    float*   cum_log_probs;
+    float*   output_log_probs; /* [local_batch_size] slice for this step */
+
+    /* ---- scratch ---- */
+    void*  workspace;
+    size_t workspace_bytes;
+    void*  stream;
+} ftb200_sampling_params;
+
+/* Bytes of scratch ftb200_decode_step_sampling needs for this shape (depends on dtype, vocab and the
+ * SM count of the current device).  Replaces the nullptr-workspace size queries of
+ * invokeTopKSampling / invokeTopPSampling (TopKSamplingLayer.cu:93-108, TopPSamplingLayer.cu:120-141). */
+int ftb200_sampling_workspace_bytes(int dtype, int local_batch_size, int vocab_size_padded, size_t* bytes);
+
+int ftb200_decode_step_sampling(const ftb200_sampling_params* p);
+
+/* Number of kernels the last ftb200_decode_step_sampling call on this thread launched. */
+int ftb200_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTB200_H */

@@ -1,0 +1,615 @@
+/*
+ * TEST INFRASTRUCTURE - CPU restatement of FasterTransformer's decode sampling path.
+ *
+ * Plain C++ (no CUDA) that follows the reference's algorithm step by step so that the CUDA
+ * kernels can be checked against it.  Only tests, the smoke check and the benchmark's cpu_baseline
+ * leg may load this library; the product never does.
+ *
+ * Every function cites the reference code it restates (path:line inside the FasterTransformer tree,
+ * paths relative to src/fastertransformer/).  Differences a CPU cannot avoid:
+ *   - the reference is built with --use_fast_math, so its __expf / logf / division are the GPU's
+ *     approximate instructions; here they are libm's expf / logf and IEEE division.  Values agree to a
+ *     few ulp; a sampled id can differ only when a draw lands within that distance of a boundary.
+ *   - uniforms are an input: the caller draws them with curand from the same states the kernels use.
+ * Parity status: pinned against the reference's known-answer tests (tests/unittests/test_sampling_layer.cu,
+ * tests/golden/) and against outputs of the compiled reference itself (oracle/_ref) on a B200.
+ */
+#include <algorithm>
+#include <cfloat>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "../include/ftb200.h"
+
+namespace {
+
+typedef _Float16 half_t;
+
+inline float bf16_to_float(uint16_t b)
+{
+    uint32_t u = (uint32_t)b << 16;
+    float    f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+inline float half_bits_to_float(uint16_t b)
+{
+    half_t h;
+    std::memcpy(&h, &b, 2);
+    return (float)h;
+}
+inline float round_half(float x)
+{
+    return (float)(half_t)x;
+}
+
+struct RowView {
+    int         dtype;
+    const void* base;
+    size_t      stride;
+    float       get(size_t row, size_t v) const
+    {
+        switch (dtype) {
+            case FTB200_F32: return ((const float*)base)[row * stride + v];
+            case FTB200_F16: return half_bits_to_float(((const uint16_t*)base)[row * stride + v]);
+            default: return bf16_to_float(((const uint16_t*)base)[row * stride + v]);
+        }
+    }
+};
+
+// The logits type of the reference is float or half; bf16 inputs are handled as float on the up-cast.
+struct TypeOps {
+    bool  is_half;
+    float max_t() const
+    {
+        return is_half ? 65504.0f : FLT_MAX;
+    }
+    float rnd(float x) const
+    {
+        return is_half ? round_half(x) : x;
+    }
+};
+
+// kernels/ban_bad_words.cu:35-85 for beam_width == 1.
+void ban_bad_words_row(std::vector<float>& x, const int* output_ids, int batch_size, size_t col, const int* words,
+                       int L, int vocab_padded, int step)
+{
+    const int* offs = words + L;
+    for (int i = 0; i < L; ++i) {
+        if (offs[i] < 0) {
+            continue;
+        }
+        const int item_end   = offs[i];
+        const int item_start = i > 0 ? offs[i - 1] : 0;
+        const int item_size  = item_end - item_start;
+        bool      ban        = item_size == 1;
+        if (item_size > 1 && step >= item_size - 1) {
+            ban = true;
+            for (int j = item_size - 2; j >= 0; --j) {
+                int prev = output_ids[(size_t)(step - (item_size - 1) + j) * batch_size + col];
+                if (prev != words[item_start + j]) {
+                    ban = false;
+                    break;
+                }
+            }
+        }
+        if (ban) {
+            int tok = words[item_end - 1];
+            if (0 < tok && tok < vocab_padded) {
+                x[tok] = -INFINITY;
+            }
+        }
+    }
+}
+
+// kernels/sampling_penalty_kernels.cu:117-179 (per-row temperature, bias, pad mask).
+void temperature_row(std::vector<float>& x, const TypeOps& T, const RowView* bias, float temperature, int vocab,
+                     int vocab_padded)
+{
+    const float inv = 1.0f / (temperature + 1e-6f);
+    for (int v = 0; v < vocab_padded; ++v) {
+        if (v < vocab) {
+            if (T.is_half) {
+                float h = x[v];
+                if (bias) {
+                    h = round_half(h + bias->get(0, v));
+                }
+                x[v] = round_half(h * round_half(inv));
+            }
+            else {
+                float y = x[v];
+                if (bias) {
+                    y = y + bias->get(0, v);
+                }
+                x[v] = y * inv;
+            }
+        }
+        else {
+            // the half2 kernel leaves pad columns as they are (:171-177); the scalar one writes -MAX.
+            // Both are overwritten by the end mask before selection.
+            x[v] = -T.max_t();
+        }
+    }
+}
+
+// kernels/sampling_penalty_kernels.cu:367-424: every occurrence is computed from the pre-penalty value.
+void repetition_row(std::vector<float>& x, const TypeOps& T, float theta, int type, const int* output_ids,
+                    int batch_size, size_t col, int input_len, int max_input_len, int step, int vocab_padded)
+{
+    std::vector<std::pair<int, float>> upd;
+    for (int t = 0; t < step; ++t) {
+        if (t >= input_len && t < max_input_len) {
+            continue;
+        }
+        int id = output_ids[(size_t)t * batch_size + col];
+        if (id < 0 || id >= vocab_padded) {
+            continue;
+        }
+        float logit = x[id], nv = logit;
+        if (type == FTB200_PENALTY_ADDITIVE) {
+            nv = logit - theta;
+        }
+        else if (type == FTB200_PENALTY_MULTIPLICATIVE) {
+            nv = logit < 0.0f ? logit * theta : logit / theta;
+        }
+        upd.push_back({id, T.rnd(nv)});
+    }
+    for (auto& u : upd) {
+        x[u.first] = u.second;
+    }
+}
+
+// kernels/sampling_topk_kernels.cu:67-94.
+void end_mask_row(std::vector<float>& x, const TypeOps& T, bool finished, int end_id, int vocab, int vocab_padded)
+{
+    for (int v = 0; v < vocab_padded; ++v) {
+        if (v >= vocab) {
+            x[v] = -T.max_t();
+        }
+        else if (finished) {
+            x[v] = v == end_id ? T.max_t() : -T.max_t();
+        }
+    }
+}
+
+// warpReduceSum / blockReduceSum of kernels/reduce_kernel_utils.cuh:73-103 over `n` threads.
+float butterfly_block_sum(const std::vector<float>& partial, int n)
+{
+    const int nwarps = (n + 31) / 32;
+    float     shared[32];
+    for (int i = 0; i < 32; ++i) {
+        shared[i] = 0.0f;
+    }
+    for (int w = 0; w < nwarps; ++w) {
+        float v[32], t[32];
+        for (int l = 0; l < 32; ++l) {
+            v[l] = w * 32 + l < n ? partial[w * 32 + l] : 0.0f;
+        }
+        for (int m = 16; m > 0; m >>= 1) {
+            for (int l = 0; l < 32; ++l) {
+                t[l] = v[l] + v[l ^ m];
+            }
+            std::memcpy(v, t, sizeof(v));
+        }
+        shared[w] = v[0];
+    }
+    float v[32], t[32];
+    for (int l = 0; l < 32; ++l) {
+        v[l] = ((float)l < (float)n / 32.f) ? shared[l] : 0.0f;
+    }
+    for (int m = 16; m > 0; m >>= 1) {
+        for (int l = 0; l < 32; ++l) {
+            t[l] = v[l] + v[l ^ m];
+        }
+        std::memcpy(v, t, sizeof(v));
+    }
+    return v[0];
+}
+
+// addBiasSoftMax, kernels/sampling_topp_kernels.cu:1294-1345 (bias is never passed by the layers).
+void softmax_row(std::vector<float>& x, const TypeOps& T, bool finished, int end_id, int n, int n_padded)
+{
+    const int nthr    = n < 1024 ? n : 1024;
+    float     max_val = -FLT_MAX;
+    for (int v = 0; v < n_padded; ++v) {
+        if (v < n) {
+            if (finished) {
+                x[v] = v == end_id ? T.max_t() : -T.max_t();
+            }
+        }
+        else {
+            x[v] = -T.max_t();
+        }
+        max_val = std::max(max_val, x[v]);
+    }
+    std::vector<float> partial(nthr, 0.0f);
+    for (int v = 0; v < n_padded; ++v) {
+        x[v] = T.rnd(expf(x[v] - max_val));
+        partial[v % nthr] += x[v];
+    }
+    const float s = butterfly_block_sum(partial, nthr);
+    for (int v = 0; v < n_padded; ++v) {
+        x[v] = T.rnd(x[v] / (s + 1e-6f));
+    }
+}
+
+struct Cand {
+    float val;
+    int   col;
+};
+
+// Two-stage top-k of kernels/sampling_topk_kernels.cu:130-312.  Stage 1: 8 CTAs per row, CTA `lane`
+// owns columns with (col / BS1) % 8 == lane, thread col % BS1; k arg-max passes, each removing the
+// winner.  Within a thread the first maximum wins (strict >, reduce_kernel_utils.cuh:329-336); across
+// threads cub::BlockReduce keeps the right-hand operand on ties (reduce_topk_op_2, :345-348), i.e. the
+// highest thread id.  Extracting k times with that rule equals taking the first k of the slice ordered
+// by (value desc, thread desc, column asc).  Stage 2 repeats the scheme over the 8*k slots with BS2
+// threads: (value desc, slot % BS2 desc, slot asc).  Values equal to -MAX are never selected.
+std::vector<Cand> topk_two_stage(const std::vector<float>& x, const TypeOps& T, int vocab_padded, int k, int max_top_k)
+{
+    const int bs1 = max_top_k <= 16 ? 128 : 256;
+    const int bs2 = max_top_k <= 32 ? 128 : 256;
+    struct Slot {
+        float val;
+        int   col;
+        int   slot;
+    };
+    std::vector<Slot> slots;
+    for (int lane = 0; lane < 8; ++lane) {
+        std::vector<Cand> mine;
+        for (int base = lane * bs1; base < vocab_padded; base += bs1 * 8) {
+            for (int t = 0; t < bs1 && base + t < vocab_padded; ++t) {
+                if (x[base + t] > -T.max_t()) {
+                    mine.push_back({x[base + t], base + t});
+                }
+            }
+        }
+        auto cmp = [&](const Cand& a, const Cand& b) {
+            if (a.val != b.val) {
+                return a.val > b.val;
+            }
+            int ta = a.col % bs1, tb = b.col % bs1;
+            if (ta != tb) {
+                return ta > tb;
+            }
+            return a.col < b.col;
+        };
+        size_t keep = std::min<size_t>(k, mine.size());
+        std::partial_sort(mine.begin(), mine.begin() + keep, mine.end(), cmp);
+        for (size_t j = 0; j < keep; ++j) {
+            slots.push_back({mine[j].val, mine[j].col, lane * k + (int)j});
+        }
+    }
+    auto cmp2 = [&](const Slot& a, const Slot& b) {
+        if (a.val != b.val) {
+            return a.val > b.val;
+        }
+        int ma = a.slot % bs2, mb = b.slot % bs2;
+        if (ma != mb) {
+            return ma > mb;
+        }
+        return a.slot < b.slot;
+    };
+    size_t keep = std::min<size_t>(k, slots.size());
+    std::partial_sort(slots.begin(), slots.begin() + keep, slots.end(), cmp2);
+    std::vector<Cand> out;
+    for (size_t j = 0; j < keep; ++j) {
+        out.push_back({slots[j].val, slots[j].col});
+    }
+    return out;
+}
+
+struct RowResult {
+    int   id;
+    bool  update_state;  // sequence_length / finished are rewritten
+    bool  has_lp;
+    float log_prob;      // added to cum_log_probs
+    float out_log_prob;  // written to output_log_probs
+};
+
+// topk_stage2_sampling's draw, kernels/sampling_topk_kernels.cu:282-311.
+RowResult topk_draw(const std::vector<Cand>& top, int k, float u, float top_p, bool probs)
+{
+    RowResult R{0, true, false, 0.f, 0.f};
+    if (top.empty()) {
+        return R;
+    }
+    std::vector<float> e(top.size());
+    float              s_sum = 0.0f, s_max = top[0].val;
+    for (size_t i = 0; i < top.size(); ++i) {
+        e[i] = probs ? top[i].val : expf(top[i].val - s_max);
+        s_sum += e[i];
+    }
+    float  rand_num = u * top_p * s_sum;
+    size_t pick     = top.size() - 1;
+    for (size_t i = 0; i < top.size(); ++i) {
+        rand_num = rand_num - e[i];
+        if (rand_num <= 0.0f || (int)i == k - 1) {
+            pick = i;
+            break;
+        }
+    }
+    R.id           = top[pick].col;
+    R.has_lp       = true;
+    R.log_prob     = logf(e[pick]);
+    R.out_log_prob = R.log_prob - logf(s_sum);
+    return R;
+}
+
+// topp_beam_topk_kernel + segmented sort + topp_sampling, kernels/sampling_topp_kernels.cu:801-1004.
+// The sort is a stable descending sort (equal probabilities stay in column order); the running sum is
+// cub::BlockScan<float,256>::InclusiveSum with a running prefix: 32 raking threads each sum 8
+// consecutive items left to right, a Kogge-Stone scan combines the 32 partials, and each item's result
+// is prefix + partials-before + its segment's running sum.
+RowResult topp_draw(const std::vector<float>& p, int vocab_padded, float u, float top_p)
+{
+    RowResult R{0, true, true, 0.f, 0.f};
+    // arg-max shortcut: TopK<T,1> keeps the larger value, then the smaller column
+    int best = 0;
+    for (int v = 1; v < vocab_padded; ++v) {
+        if (p[v] > p[best]) {
+            best = v;
+        }
+    }
+    if (p[best] >= top_p) {
+        R.id       = best;
+        R.log_prob = R.out_log_prob = logf(p[best]);
+        return R;
+    }
+    std::vector<int> order(vocab_padded);
+    for (int v = 0; v < vocab_padded; ++v) {
+        order[v] = v;
+    }
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return p[a] > p[b]; });
+    const float rand_num = u * top_p;
+    float       running  = 0.0f;
+    const int   end      = (vocab_padded + 255) / 256 * 256;
+    for (int c = 0; c < end; c += 256) {
+        float x[256], out[256], up[32], inc[32];
+        for (int t = 0; t < 256; ++t) {
+            x[t] = c + t < vocab_padded ? p[order[c + t]] : 0.0f;
+        }
+        for (int j = 0; j < 32; ++j) {
+            float s = x[8 * j];
+            for (int i = 1; i < 8; ++i) {
+                s = s + x[8 * j + i];
+            }
+            up[j] = inc[j] = s;
+        }
+        for (int off = 1; off < 32; off <<= 1) {
+            float t[32];
+            for (int j = 0; j < 32; ++j) {
+                t[j] = j >= off ? inc[j] + inc[j - off] : inc[j];
+            }
+            std::memcpy(inc, t, sizeof(inc));
+        }
+        for (int j = 0; j < 32; ++j) {
+            float o = j == 0 ? running : running + inc[j - 1];
+            for (int i = 0; i < 8; ++i) {
+                o              = o + x[8 * j + i];
+                out[8 * j + i] = o;
+            }
+        }
+        running = running + inc[31];
+        // first warp with an active lane; lane = 32 - popcount of its mask (:963, :984)
+        for (int w = 0; w < 8; ++w) {
+            int cnt = 0;
+            for (int l = 0; l < 32; ++l) {
+                cnt += rand_num <= out[32 * w + l] ? 1 : 0;
+            }
+            if (cnt > 0) {
+                int pos    = c + 32 * w + (32 - cnt);
+                int col    = pos < vocab_padded ? order[pos] : order[0];
+                R.id       = col;
+                R.log_prob = R.out_log_prob = logf(p[col]);
+                return R;
+            }
+        }
+    }
+    // never reached: the best token stays, nothing else is updated (:954)
+    R.id           = order[0];
+    R.update_state = false;
+    R.has_lp       = false;
+    return R;
+}
+
+}  // namespace
+
+extern "C" {
+
+/*
+ * One decode step on the CPU.  Same argument block as ftb200_decode_step_sampling, with HOST pointers;
+ * topk_states / topp_states point to float[local_batch_size] uniforms (the value curand_uniform
+ * would return for each row this step).  Follows DynamicDecodeLayer::forward for beam_width == 1:
+ * layers/DynamicDecodeLayer.cc:247-283, 389-445; BaseSamplingLayer::forward
+ * (layers/sampling_layers/BaseSamplingLayer.cc:255-359); TopKSamplingLayer::runSampling
+ * (TopKSamplingLayer.cu:189-267); TopPSamplingLayer::runSampling (TopPSamplingLayer.cu:256-342).
+ */
+int oracle_decode_step_sampling(const ftb200_sampling_params* p)
+{
+    const int     Vp = p->vocab_size_padded, V = p->vocab_size;
+    const TypeOps T{p->dtype == FTB200_F16};
+    const RowView L{p->dtype, p->logits, (size_t)Vp};
+    RowView       biasv{p->dtype, p->embedding_bias, (size_t)Vp};
+    const RowView* bias   = p->embedding_bias ? &biasv : nullptr;
+    const float*  u_topk  = (const float*)p->topk_states;
+    const float*  u_topp  = (const float*)p->topp_states;
+    const bool    want_lp = p->cum_log_probs || p->output_log_probs;
+
+    for (int r = 0; r < p->local_batch_size; ++r) {
+        int mode = 0;
+        if (u_topk && !(p->topk_skip && p->topk_skip[r])) {
+            mode = 1;
+        }
+        else if (u_topp && !(p->topp_skip && p->topp_skip[r])) {
+            mode = 2;
+        }
+        const size_t col    = (size_t)p->ite * p->local_batch_size + r;
+        int*         id_out = p->output_ids + (size_t)p->step * p->batch_size + col;
+        const bool   fin    = p->finished ? p->finished[r] != 0 : false;
+        const int    end_id = p->end_ids[r];
+
+        if (mode != 0) {
+            std::vector<float> x(Vp);
+            for (int v = 0; v < Vp; ++v) {
+                x[v] = L.get(r, v);
+            }
+            if (p->bad_words && p->bad_words_len > 0) {
+                const int* words =
+                    p->bad_words_shared ? p->bad_words : p->bad_words + (size_t)r * 2 * p->bad_words_len;
+                ban_bad_words_row(x, p->output_ids, p->batch_size, col, words, p->bad_words_len, Vp, p->step);
+            }
+            if (p->apply_temperature) {
+                temperature_row(x, T, bias, p->temperature[r], V, Vp);
+            }
+            if (p->apply_repetition && p->penalty_type != FTB200_PENALTY_NONE) {
+                const int input_len = p->input_lengths ? p->input_lengths[r] : p->max_input_length;
+                repetition_row(x, T, p->repetition_penalty[r], p->penalty_type, p->output_ids, p->batch_size, col,
+                               input_len, p->max_input_length, p->step, Vp);
+            }
+            if (p->apply_min_length) {
+                // kernels/sampling_penalty_kernels.cu:493-499
+                if (p->sequence_length[r] + 1 - p->max_input_length < p->min_lengths[r]) {
+                    x[end_id] = -T.max_t();
+                }
+            }
+            RowResult R{0, false, false, 0.f, 0.f};
+            if (mode == 1) {
+                end_mask_row(x, T, fin, end_id, V, Vp);
+                if (want_lp) {
+                    softmax_row(x, T, fin, end_id, V, Vp);
+                }
+                if (fin) {
+                    // kernels/sampling_topk_kernels.cu:249-252
+                    *id_out = end_id;
+                }
+                else {
+                    int k = (int)p->topk_ks[r];
+                    auto top = topk_two_stage(x, T, Vp, k, p->max_top_k);
+                    R        = topk_draw(top, k, u_topk[r], p->topk_ps[r], want_lp);
+                    R.has_lp = want_lp;
+                    *id_out  = R.id;
+                }
+            }
+            else {
+                softmax_row(x, T, fin, end_id, V, Vp);
+                R       = topp_draw(x, Vp, u_topp[r], p->topp_ps[r]);
+                *id_out = R.id;
+            }
+            if (mode == 2 || !fin) {
+                if (R.has_lp && want_lp) {
+                    if (p->cum_log_probs) {
+                        p->cum_log_probs[r] += R.log_prob;
+                    }
+                    if (p->output_log_probs) {
+                        p->output_log_probs[r] = R.out_log_prob;
+                    }
+                }
+                if (R.update_state && p->sequence_length && p->finished) {
+                    p->sequence_length[r] = fin ? p->sequence_length[r] : p->sequence_length[r] + 1;
+                    p->finished[r]        = *id_out == end_id ? 1 : 0;
+                }
+            }
+        }
+        // computeToppDecay, kernels/sampling_topp_kernels.cu:1381-1408
+        if (u_topp && p->topp_decay && p->topp_min && p->topp_reset_ids && p->topp_initial_ps) {
+            float tp = p->topp_ps[r];
+            if (*id_out == p->topp_reset_ids[r]) {
+                tp = p->topp_initial_ps[r];
+            }
+            else {
+                tp = std::max(tp * p->topp_decay[r], p->topp_min[r]);
+            }
+            p->topp_ps[r] = tp;
+        }
+    }
+    return 0;
+}
+
+/* setup_topk_runtime_args, layers/sampling_layers/TopKSamplingLayer.cu:28-77 (host arrays). */
+void oracle_setup_topk_runtime_args(int batch, uint32_t top_k, uint32_t* top_ks, int top_ks_size, float top_p,
+                                    float* top_ps, int top_ps_size, uint8_t* skip_decode)
+{
+    for (int i = 0; i < batch; ++i) {
+        uint32_t k = top_ks_size > 1 ? top_ks[i] : top_k;
+        float    q = top_ps_size > 1 ? top_ps[i] : top_p;
+        if (k == 0 && q == 0.0f) {
+            k = 1;
+        }
+        if (k > 0 && q == 0.0f) {
+            q = 1.0f;
+        }
+        top_ks[i]      = k > 1024u ? 1024u : k;
+        top_ps[i]      = q < 0.0f ? 0.0f : (q > 1.0f ? 1.0f : q);
+        skip_decode[i] = k == 0;
+    }
+}
+
+/* set_topp_runtime_args, layers/sampling_layers/TopPSamplingLayer.cu:30-109 (host arrays). */
+void oracle_setup_topp_runtime_args(int batch, uint32_t top_k, uint32_t* top_ks, int top_ks_size, float top_p,
+                                    float* top_ps, int top_ps_size, uint8_t* skip_decode, float* initial_top_p,
+                                    float* decay_buf, const float* decay, float* min_buf, const float* top_p_min,
+                                    int32_t* reset_buf, const uint32_t* reset_ids)
+{
+    for (int i = 0; i < batch; ++i) {
+        uint32_t k = top_ks_size > 1 ? top_ks[i] : top_k;
+        float    q = top_ps_size > 1 ? top_ps[i] : top_p;
+        if (k == 0 && q == 0.0f) {
+            k = 1;
+        }
+        top_ks[i]        = k;
+        top_ps[i]        = q < 0.0f ? 0.0f : (q > 1.0f ? 1.0f : q);
+        skip_decode[i]   = k > 0;
+        initial_top_p[i] = top_ps[i];
+        float d          = decay ? decay[i] : 1.0f;
+        decay_buf[i]     = (d > 1.0f || d <= 0.0f) ? 1.0f : d;
+        float m          = top_p_min ? top_p_min[i] : 1e-6f;
+        min_buf[i]       = (m > 1.0f || m <= 0.0f) ? 0.5f : m;
+        reset_buf[i]     = (int32_t)(reset_ids ? reset_ids[i] : (uint32_t)-1);
+    }
+}
+
+/* stop_words_criterion, kernels/stop_criteria_kernels.cu:24-81, beam_width == 1. */
+void oracle_stop_words(const int* output_ids, const int* stop_words, uint8_t* finished, int id_offset, int len,
+                       int batch_size, int local_batch, int step)
+{
+    for (int b = 0; b < local_batch; ++b) {
+        const int* words = stop_words + (size_t)b * 2 * len;
+        const int* offs  = words + len;
+        for (int i = 0; i < len; ++i) {
+            if (offs[i] < 0) {
+                continue;
+            }
+            const int item_end = offs[i], item_start = i > 0 ? offs[i - 1] : 0, item_size = item_end - item_start;
+            bool      stop = false;
+            if (step + 1 >= item_size) {
+                stop = true;
+                for (int j = item_size - 1; j >= 0; --j) {
+                    int prev = output_ids[(size_t)(step - (item_size - 1) + j) * batch_size + id_offset + b];
+                    if (prev != words[item_start + j]) {
+                        stop = false;
+                        break;
+                    }
+                }
+            }
+            if (stop) {
+                finished[b] = 1;
+            }
+        }
+    }
+}
+
+/* length_criterion, kernels/stop_criteria_kernels.cu:106-156: returns should_stop. */
+int oracle_length_criterion(uint8_t* finished, const uint32_t* sequence_limit_length, int batch, int beam, int step)
+{
+    int sum = 0;
+    for (int i = 0; i < batch * beam; ++i) {
+        finished[i] |= (uint32_t)step >= sequence_limit_length[i / beam];
+        sum += finished[i] ? 1 : 0;
+    }
+    return sum == batch * beam;
+}
+
+}  // extern "C"
