@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the per-step decode sampling path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload: configuration 3 of the baseline - batch 1024, vocab 128256, bf16 logits ~ N(0, 2.5^2), mixed
+per-row top-k in {0,1,40,1024} / top-p in {0,0.5,0.95}, repetition penalty 1.1 over a 512-token prompt
+plus everything generated so far, 8 bad words per row, end id 128001, length criterion.  Seeded synthetic
+logits stand in for a model (no dataset is involved).  A step is one pass of the path over the batch:
+the fused sampling kernel, the stop-criteria kernel and the host read of should_stop.
+
+One JSON line on stdout (rank 0):
+  value      sampled tokens/s with the logits resident in HBM (4 distinct 263 MB buffers rotate, so no
+             step finds its logits in the 126 MB L2), CUDA events around exactly K steps, max over ranks
+  e2e        same metric with the step's logits starting in pinned HOST memory and the sampled ids read
+             back to the host, copies inside the timed region
+  roofline   algorithmic bytes of one launch of the fused kernel / its mean CUDA-event duration,
+             against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle (oracle/ft_oracle.cpp) on a bounded sample, all host cores
+--impl reference times the unmodified FasterTransformer kernels (oracle/_ref, built for sm_100a from the
+reference sources) on the same workload through the reference's own DynamicDecodeLayer<float>; the
+reference has no bf16 path, so it is fed the lossless fp32 up-cast, as its own models do.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))  # ft_oracle / ft_reference drivers (checkers, not product)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+N_BUFFERS = 4
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index, period=0.004):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=1.0)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(x, world, device):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def cpu_baseline(w, rows=64):
+    """The CPU oracle on the first `rows` rows of step 0 of the workload, all host cores."""
+    from ft_oracle import OracleDynamicDecodeLayer, bf16_bits
+    rows = min(rows, w.batch)
+    args = {}
+    for k, v in w.runtime_args.items():
+        v = np.atleast_1d(np.asarray(v))
+        args[k] = v[:rows] if v.size == w.batch else v
+    orc = OracleDynamicDecodeLayer(w.vocab, w.vocab_padded, "bfloat16")
+    orc.setup(rows, 1, args)
+    g = np.random.default_rng(w.seed)
+    logits = (g.standard_normal((rows, w.vocab_padded), dtype=np.float32) * w.sigma)
+    out = {"output_ids": np.zeros((w.max_input_length + 2, rows), np.int32),
+           "finished": np.zeros(rows, np.bool_),
+           "sequence_length": np.full(rows, w.max_input_length, np.int32)}
+    out["output_ids"][: w.max_input_length] = w.prompt[:, :rows]
+    inp = {"logits": bf16_bits(logits), "step": w.max_input_length, "max_input_length": w.max_input_length,
+           "end_id": np.full(rows, w.end_id, np.int32),
+           "input_lengths": np.full(rows, w.max_input_length, np.int32),
+           "bad_words_list": None if w.bad_words is None else w.bad_words[:rows]}
+    u = 1.0 - g.random(rows, dtype=np.float32)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 10.0 or reps < 2:
+        orc.forward(out, inp, u, u)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": rows / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": "%d rows x 1 step of the same workload, %d repetitions, OpenMP over rows" % (rows, reps)}
+
+
+def make_pool(w, device, dtype, n):
+    pool = []
+    for i in range(n):
+        x = w.logits(10_000 + i, device)
+        pool.append(x if dtype == w.dtype else x.to(dtype))
+    return pool
+
+
+def run_ours(a, rank, world, local):
+    from fastertransformer_b200 import DynamicDecodeLayer
+    from fastertransformer_b200.workloads import algorithmic_bytes_per_step, make_workload
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    K, W = a.steps, a.warmup
+    e2e_steps = min(K, 16)
+    w = make_workload("c3", batch=a.batch, steps=W + K + e2e_steps + 40, seed=1237 + rank)
+    B = w.batch
+    layer = DynamicDecodeLayer(w.vocab, w.vocab_padded, w.dtype, device)
+    layer.setup(B, 1, w.runtime_args)
+    st = w.initial_state(device)
+    inputs = w.static_inputs(device)
+    pool = make_pool(w, device, w.dtype, N_BUFFERS)
+    torch.cuda.synchronize()
+
+    step_no = [w.max_input_length]
+
+    def one_step(logits):
+        layer.forward(st, dict(inputs, logits=logits, step=step_no[0]))
+        step_no[0] += 1
+
+    for i in range(W):
+        one_step(pool[i % N_BUFFERS])
+    torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    launches0 = layer.launches
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    first_step = step_no[0]
+    ev0.record()
+    for i in range(K):
+        # the event pair brackets the fused sampling launch; the criteria kernel follows it
+        kev[i][0].record()
+        one_step(pool[i % N_BUFFERS])
+        kev[i][1].record()
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    clocks = sampler.stop()
+    launches = layer.launches - launches0
+    ms_total = ev0.elapsed_time(ev1)
+    ms_total = max_over_ranks(ms_total, world, device)
+    step_ms = [p[0].elapsed_time(p[1]) for p in kev]
+
+    # kernel-only duration of the fused launch: events directly around the C-ABI call
+    layer.time_kernels = True
+    for i in range(min(K, 32)):
+        one_step(pool[i % N_BUFFERS])
+    torch.cuda.synchronize()
+    layer.time_kernels = False
+    kern_ms = [e0.elapsed_time(e1) for e0, e1 in layer.kernel_events]
+    kern_ms_mean = float(np.mean(kern_ms))
+
+    # end to end: logits start in pinned host memory, ids come back to the host, every step
+    host_pool = [torch.empty(B, w.vocab_padded, dtype=w.dtype).pin_memory() for _ in range(2)]
+    for h, d in zip(host_pool, pool):
+        h.copy_(d)
+    dev_logits = torch.empty_like(pool[0])
+    ids_host = torch.empty(B, dtype=torch.int32).pin_memory()
+    torch.cuda.synchronize()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        dev_logits.copy_(host_pool[i % 2], non_blocking=True)
+        s = step_no[0]
+        one_step(dev_logits)
+        ids_host.copy_(st["output_ids"][s], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, device)
+
+    peak, peak_kind = measured_peak()
+    alg_bytes = float(np.mean([algorithmic_bytes_per_step(w, first_step + i) for i in range(K)]))
+    achieved = alg_bytes / (kern_ms_mean * 1e-3) / 1e9
+    es = pool[0].element_size()
+    line = {
+        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256",
+        "value": world * B * K / (ms_total * 1e-3),
+        "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_total / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 logits, fp32 arithmetic", "data": "synthetic",
+        "config": {"workload": "c3: mixed per-row top-k/top-p, batch %d x vocab %d bf16, repetition 1.1, "
+                               "8 bad words/row, length criterion" % (B, w.vocab),
+                   "rows_per_gpu": B, "history_tokens": "%d..%d" % (first_step, first_step + K),
+                   "l2": "%d logits buffers of %.0f MB rotate (> 126 MB L2)" % (N_BUFFERS, B * w.vocab_padded * es / 1e6),
+                   "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": a.traffic, "peak_kind": peak_kind,
+                     "kernel": "decode_sampling_kernel<bf16>", "kernel_ms": kern_ms_mean,
+                     "algorithmic_bytes_per_launch": alg_bytes},
+        "e2e": {"value": world * B * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": B * w.vocab_padded * es, "d2h_bytes_per_step": B * 4 + 4,
+                "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "step_ms_median": float(np.median(step_ms)),
+    }
+    if rank == 0 and world == 1 and not a.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(w)
+    return line
+
+
+def run_reference(a, rank, world, local):
+    import ft_reference
+    from fastertransformer_b200.workloads import make_workload
+    if rank != 0:
+        return None
+    if not ft_reference.available():
+        return {"impl": "reference", "unavailable": "oracle/_ref/libft_decode_ref.so is not built on this box"}
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    K, W = a.steps, a.warmup
+    w = make_workload("c3", batch=a.batch, steps=W + K + 4)
+    B = w.batch
+    layer = ft_reference.RefDynamicDecodeLayer(w.vocab, w.vocab_padded, torch.float32, device)
+    layer.setup(B, 1, w.runtime_args)
+    st = w.initial_state(device)
+    inputs = w.static_inputs(device)
+    pool = make_pool(w, device, torch.float32, 2)
+    work = torch.empty_like(pool[0])
+    sampler = ClockSampler(local, period=0.02)
+    total_ms, n = 0.0, 0
+    for i in range(W + K):
+        if i == W:
+            sampler.start()
+        step = w.max_input_length + i
+        work.copy_(pool[i % 2])  # the reference overwrites its logits; a model would produce fresh ones
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layer.forward(st, dict(inputs, logits=work.view(B, 1, w.vocab_padded), step=step))
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= W:
+            total_ms += e0.elapsed_time(e1)
+            n += 1
+    clocks = sampler.stop()
+    val = B * n / (total_ms * 1e-3)
+    return {
+        "impl": "reference",
+        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256",
+        "value": val, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": total_ms / n,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32 (up-cast of the bf16 logits; the reference has no bf16 path)", "data": "synthetic",
+        "config": {"workload": "c3: mixed per-row top-k/top-p, batch %d x vocab %d, repetition 1.1, "
+                               "8 bad words/row, length criterion" % (B, w.vocab),
+                   "what": "unmodified FasterTransformer DynamicDecodeLayer<float> compiled for sm_100a "
+                           "(oracle/_ref), logits resident in HBM, CUDA events around each forward()"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                         "sample": "the reference's own CUDA kernels on the GPU, full batch, %d steps" % n},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "clocks": clocks,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch of the fused kernel from an ncu capture (profiles/)")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    if a.traffic is None:
+        p = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(p):
+            try:
+                a.traffic = float(json.load(open(p))["dram_bytes_per_launch_c3"])
+            except Exception:
+                a.traffic = None
+    rank, world, local = dist_setup(a.gpus)
+    if a.impl == "reference":
+        line = run_reference(a, rank, world, local)
+    else:
+        line = run_ours(a, rank, world, local)
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

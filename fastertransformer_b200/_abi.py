@@ -20,5 +20,6 @@ class SamplingParams(C.Structure):
         ("topp_reset_ids", C.c_void_p),
         ("sequence_length", C.c_void_p), ("finished", C.c_void_p), ("cum_log_probs", C.c_void_p),
         ("output_log_probs", C.c_void_p),
+        ("row_order", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]

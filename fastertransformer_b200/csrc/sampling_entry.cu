@@ -142,6 +142,7 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
     K.finished         = p->finished;
     K.cum_log_probs    = p->cum_log_probs;
     K.out_log_probs    = p->output_log_probs;
+    K.row_order        = p->row_order;
 
     // shared-memory plan: candidates, histogram, 1024 floats, vector flags, token hash
     const int epv      = p->dtype == FTB200_F32 ? 4 : 8;
@@ -157,7 +158,8 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
         ++lg;
     }
     K.hash_shift = 32 - lg;
-    size_t smem  = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 4;
+    size_t smem  = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 4
+                   + (size_t)(slots / 2) * 4 + 32 + (size_t)kThreads * 16 * 2;
     if (smem > 200 * 1024) {
         set_error("ftb200_decode_step_sampling: token history too long for the shared-memory hash");
         return FTB200_UNSUPPORTED;

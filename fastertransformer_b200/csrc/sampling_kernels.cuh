@@ -37,6 +37,10 @@ struct Smem {
     float* val2;   // [1024] exp values of the sorted top-k / soft-max partial sums
     u32*   flags;  // one bit per aligned vector: holds a token with a hash entry
     u32*   hash;   // open addressing, (id << 2) | flags
+    u32*   spec;   // indices of the aligned vectors that hold a token with a hash entry
+    u32*   nspec;  // length of spec
+    unsigned short* hitq;  // [kThreads * kUnroll] vectors of the current batch that passed the packed filter
+    u32*   nhit;   // [2] queue lengths, alternating per batch
 };
 
 __device__ __forceinline__ u32 hash_slot(int id, int shift)
@@ -65,51 +69,82 @@ static __device__ void hash_insert(const KParams& P, const Smem& S, const RowCtx
     const int epv = P.dtype == FTB200_F32 ? 4 : 8;
     int       rel = id - C.head;
     if (rel >= 0 && rel < C.nvec * epv) {
-        int j = rel / epv;
-        atomicOr(&S.flags[j >> 5], 1u << (j & 31));
+        int j   = rel / epv;
+        u32 bit = 1u << (j & 31);
+        atomicOr(&S.flags[j >> 5], bit);
     }
 }
 
-__device__ __forceinline__ u32 hash_lookup(const KParams& P, const Smem& S, int id)
+struct Xf;
+__device__ __forceinline__ u32 hash_lookup_raw(const u32* hash, int shift, int mask, int id)
 {
-    u32 h = hash_slot(id, P.hash_shift);
-    for (int probe = 0; probe < P.hash_slots; ++probe) {
-        u32 v = S.hash[h];
+    u32 h = hash_slot(id, shift);
+    for (int probe = 0; probe <= mask; ++probe) {
+        u32 v = hash[h];
         if (v == kHashEmpty) {
             return 0;
         }
         if ((v >> 2) == (u32)id) {
             return v & 3u;
         }
-        h = (h + 1) & (P.hash_slots - 1);
+        h = (h + 1) & mask;
     }
     return 0;
+}
+
+// The per-column arithmetic needs a handful of row constants.  They are gathered into one small value
+// type that every loop copies into registers once: reading them through the kernel-argument block or
+// through a reference inside a loop would cost a memory round trip per column.
+struct Xf {
+    const void* bias;
+    float       inv_t, theta, neg_max;
+    __half      inv_t_h;
+    int         apply_temp, apply_rep, penalty_type, vocab, hash_shift, hash_mask;
+    const u32*  hash;
+};
+
+__device__ __forceinline__ Xf make_xf(const KParams& P, const Smem& S, const RowCtx& C)
+{
+    Xf X;
+    X.bias         = P.bias;
+    X.inv_t        = C.inv_t;
+    X.theta        = C.theta;
+    X.neg_max      = C.neg_max;
+    X.inv_t_h      = C.inv_t_h;
+    X.apply_temp   = P.apply_temp;
+    X.apply_rep    = P.apply_rep;
+    X.penalty_type = P.penalty_type;
+    X.vocab        = P.vocab;
+    X.hash_shift   = P.hash_shift;
+    X.hash_mask    = P.hash_slots - 1;
+    X.hash         = S.hash;
+    return X;
 }
 
 // Temperature (+ bias) exactly as the reference's kernels compute it in the logits type
 // (sampling_penalty_kernels.cu:117-179): fp32 arithmetic for float, half arithmetic with the inverse
 // temperature rounded to half for half.  bf16 inputs take the fp32 route on the up-cast value.
 template<int DT>
-__device__ __forceinline__ float temp_value(const KParams& P, const RowCtx& C, u32 bits, int v)
+__device__ __forceinline__ float temp_value(const Xf& X, u32 bits, int v)
 {
     if (DT == FTB200_F16) {
         __half h = __ushort_as_half((unsigned short)bits);
-        if (P.apply_temp) {
-            if (P.bias != nullptr) {
-                h = __hadd(h, ((const __half*)P.bias)[v]);
+        if (X.apply_temp) {
+            if (X.bias != nullptr) {
+                h = __hadd(h, ((const __half*)X.bias)[v]);
             }
-            h = __hmul(h, C.inv_t_h);
+            h = __hmul(h, X.inv_t_h);
         }
         return __half2float(h);
     }
     float x = (DT == FTB200_F32) ? __uint_as_float(bits) : __uint_as_float(bits << 16);
-    if (P.apply_temp) {
-        if (P.bias != nullptr) {
-            float b = (DT == FTB200_F32) ? ((const float*)P.bias)[v] :
-                                           __bfloat162float(((const __nv_bfloat16*)P.bias)[v]);
+    if (X.apply_temp) {
+        if (X.bias != nullptr) {
+            float b = (DT == FTB200_F32) ? ((const float*)X.bias)[v] :
+                                           __bfloat162float(((const __nv_bfloat16*)X.bias)[v]);
             x       = x + b;
         }
-        x = x * C.inv_t;
+        x = x * X.inv_t;
     }
     return x;
 }
@@ -118,17 +153,17 @@ __device__ __forceinline__ float temp_value(const KParams& P, const RowCtx& C, u
 // repetition penalty from the pre-penalty value, min-length mask (sampling_penalty_kernels.cu:367-424,
 // :485-500; ban_bad_words.cu:77-85).  A dead token is reported as -inf.
 template<int DT>
-__device__ __forceinline__ float special_value(const KParams& P, const RowCtx& C, float y, u32 fl)
+__device__ __forceinline__ float special_value(const Xf& X, float y, u32 fl)
 {
     if (fl & kFlagDead) {
         return -INFINITY;
     }
-    if ((fl & kFlagHist) && P.apply_rep) {
-        if (P.penalty_type == FTB200_PENALTY_MULTIPLICATIVE) {
-            y = y < 0.0f ? y * C.theta : y / C.theta;
+    if ((fl & kFlagHist) && X.apply_rep) {
+        if (X.penalty_type == FTB200_PENALTY_MULTIPLICATIVE) {
+            y = y < 0.0f ? y * X.theta : y / X.theta;
         }
-        else if (P.penalty_type == FTB200_PENALTY_ADDITIVE) {
-            y = y - C.theta;
+        else if (X.penalty_type == FTB200_PENALTY_ADDITIVE) {
+            y = y - X.theta;
         }
         if (DT == FTB200_F16) {
             y = __half2float(__float2half_rn(y));
@@ -141,6 +176,7 @@ __device__ __forceinline__ float special_value(const KParams& P, const RowCtx& C
 template<int DT>
 __device__ __forceinline__ float elem_at(const KParams& P, const Smem& S, const RowCtx& C, int v)
 {
+    const Xf X = make_xf(P, S, C);
     if (v >= P.vocab) {
         return -INFINITY;
     }
@@ -151,7 +187,7 @@ __device__ __forceinline__ float elem_at(const KParams& P, const Smem& S, const 
     else {
         bits = __ldg((const unsigned short*)C.rowp + v);
     }
-    float     y   = temp_value<DT>(P, C, bits, v);
+    float     y   = temp_value<DT>(X, bits, v);
     const int epv = DT == FTB200_F32 ? 4 : 8;
     int       rel = v - C.head;
     bool      sp  = true;
@@ -160,67 +196,342 @@ __device__ __forceinline__ float elem_at(const KParams& P, const Smem& S, const 
         sp    = (S.flags[j >> 5] >> (j & 31)) & 1u;
     }
     if (sp) {
-        u32 fl = hash_lookup(P, S, v);
+        u32 fl = hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v);
         if (fl) {
-            y = special_value<DT>(P, C, y, fl);
+            y = special_value<DT>(X, y, fl);
         }
     }
     return y;
 }
 
-// Visit vectors [j0, j1) of the row (and the unaligned head / tail when `edges`), calling f(v, y)
-// for every column with its final value.  All loads of a thread's batch are issued before use.
-template<int DT, class F>
-__device__ __forceinline__ void
-stream_range(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1, bool edges, F&& f)
+// ---- streaming primitives ---------------------------------------------------------------------
+// A row is read as 16-byte vectors.  Vectors that hold a token with a hash entry (history, banned,
+// min-length) are skipped by the three loops below and visited by visit_specials(), together with
+// the unaligned head / tail columns, so the hot loops carry no per-column look-up and do not diverge.
+//
+// B200 moves ~0.2 bytes per issued lane-instruction at full HBM rate, i.e. a 16-bit logit may cost
+// about nine instructions.  The 16-bit loops therefore test two logits per instruction on the raw
+// bit patterns (packed compare / max) and only unpack the rare vector that passes.
+
+template<int DT>
+__device__ __forceinline__ bool packed_ok(const KParams& P, const RowCtx& C)
 {
-    constexpr int EPV = DT == FTB200_F32 ? 4 : 8;
-    const int     tid = threadIdx.x;
-    if (edges) {
-        for (int v = tid; v < C.head; v += kThreads) {
-            f(v, elem_at<DT>(P, S, C, v));
-        }
-        for (int v = C.head + C.nvec * EPV + tid; v < P.vocab_padded; v += kThreads) {
-            f(v, elem_at<DT>(P, S, C, v));
+    return DT != FTB200_F32 && P.bias == nullptr && C.inv_t > 0.0f;
+}
+
+// Largest raw 16-bit value r such that every column with final value >= thr_y has raw value >= r.
+// Temperature is monotone for inv_t > 0; the margin covers the rounding of the forward computation.
+template<int DT>
+__device__ __forceinline__ u32 raw_threshold_pair(const KParams& P, const RowCtx& C, float thr_y)
+{
+    float t = thr_y;
+    if (P.apply_temp && t > -FLT_MAX && t < FLT_MAX) {
+        t = t / C.inv_t;
+        t = t - fabsf(t) * (1.0f / 256.0f);
+    }
+    u32 r;
+    if (DT == FTB200_F16) {
+        t = fmaxf(t, -65504.0f);
+        r = (u32)__half_as_ushort(__float2half_rd(t));
+        if (thr_y <= -65504.0f) {
+            r = 0xfc00u;  // -inf
         }
     }
-    const uint4* vp = (const uint4*)(C.rowp + (size_t)C.head * (DT == FTB200_F32 ? 4 : 2));
-    for (int jb = j0; jb < j1; jb += kThreads * kUnroll) {
-        uint4 q[kUnroll];
+    else {
+        r = (u32)__bfloat16_as_ushort(__float2bfloat16_rd(t));
+        if (thr_y <= -FLT_MAX) {
+            r = 0xff80u;  // -inf
+        }
+    }
+    return r | (r << 16);
+}
+
+template<int DT>
+__device__ __forceinline__ u32 ge2_mask(u32 pair, u32 thr2)
+{
+    if (DT == FTB200_F16) {
+        return __hge2_mask(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&thr2));
+    }
+    return __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&pair),
+                       *reinterpret_cast<const __nv_bfloat162*>(&thr2));
+}
+
+template<int DT>
+__device__ __forceinline__ u32 max2(u32 a, u32 b)
+{
+    if (DT == FTB200_F16) {
+        __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<u32*>(&r);
+    }
+    __nv_bfloat162 r =
+        __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<u32*>(&r);
+}
+
+template<int DT>
+__device__ __forceinline__ const uint4* vec_base(const RowCtx& C)
+{
+    return (const uint4*)(C.rowp + (size_t)C.head * (DT == FTB200_F32 ? 4 : 2));
+}
+
+__device__ __forceinline__ u32 pick_word(const uint4& r, int i)
+{
+    return i < 2 ? (i == 0 ? r.x : r.y) : (i == 2 ? r.z : r.w);
+}
+
+template<int DT>
+__device__ __forceinline__ u32 raw_bits(const uint4& r, int e)
+{
+    return DT == FTB200_F32 ? pick_word(r, e) : ((pick_word(r, e >> 1) >> ((e & 1) * 16)) & 0xffffu);
+}
+
+// f(v, y) for every column of the unflagged vectors in [j0, j1): exact final value, no filter.
+template<int DT, class F>
+__device__ __noinline__ void stream_all(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1, F&& f)
+{
+    const Xf X = make_xf(P, S, C);
+    constexpr int EPV = DT == FTB200_F32 ? 4 : 8;
+    const int     tid = threadIdx.x;
+    const uint4*  vp  = vec_base<DT>(C);
+#pragma unroll 1
+    for (int j = j0 + tid; j < j1; j += kThreads) {
+        const bool  sp = (S.flags[j >> 5] >> (j & 31)) & 1u;
+        const uint4 r  = ld_nc_v4(vp + j);
+        const int   vb = C.head + j * EPV;
+#pragma unroll 1
+        for (int e = 0; e < EPV; ++e) {
+            int v = vb + e;
+            if (sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v)) {
+                continue;  // special columns are reported by visit_specials
+            }
+            f(v, v >= P.vocab ? -INFINITY : temp_value<DT>(X, raw_bits<DT>(r, e), v));
+        }
+    }
+}
+
+// Hot side of the filtered stream: kUnroll 16-byte loads per thread, then one packed compare per two
+// logits (16-bit types) or one multiply + compare per logit (fp32).  A vector with a passing column
+// only has its batch-relative index queued in shared memory.  Takes nothing but scalars so that the
+// whole loop lives in registers.
+constexpr int kHotUnroll = 16;  // 16-byte loads in flight per thread in the register-only loops
+
+template<int DT>
+__device__ __noinline__ void hot_filter(const uint4* vp, int jb, int j1, float thr_y, u32 thr2, float inv, bool temp,
+                                        unsigned short* hitq, u32* qn)
+{
+    const int tid = threadIdx.x;
+    uint4     q[kHotUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kHotUnroll; ++u) {
+        int j = jb + u * kThreads + tid;
+        if (j < j1) {
+            q[u] = ld_nc_v4(vp + j);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kHotUnroll; ++u) {
+        if (jb + u * kThreads + tid < j1) {
+            bool pass;
+            if (DT == FTB200_F32) {
+                float a = __uint_as_float(q[u].x), b = __uint_as_float(q[u].y);
+                float c = __uint_as_float(q[u].z), d = __uint_as_float(q[u].w);
+                if (temp) {
+                    a *= inv, b *= inv, c *= inv, d *= inv;  // the same multiply the exact path uses
+                }
+                pass = fmaxf(fmaxf(a, b), fmaxf(c, d)) >= thr_y;
+            }
+            else {
+                pass = ((ge2_mask<DT>(q[u].x, thr2) | ge2_mask<DT>(q[u].y, thr2))
+                        | (ge2_mask<DT>(q[u].z, thr2) | ge2_mask<DT>(q[u].w, thr2)))
+                       != 0;
+            }
+            if (pass) {
+                hitq[atomicAdd(qn, 1u)] = (unsigned short)(u * kThreads + tid);
+            }
+        }
+    }
+}
+
+// hit(v, y) for the columns of the unflagged vectors in [j0, j1) whose final value is >= thr().
+// CTA-collective: every thread of the CTA must call it (it synchronises).
+// Per batch: hot_filter() queues the vectors that may hold a passing column; after a barrier the queued
+// vectors are fetched again (they are still in L1/L2) and handled one per thread, so the rare exact work
+// runs dense instead of divergent.  thr() is read once per batch; a caller may raise it between batches.
+template<int DT, class Thr, class Hit>
+__device__ __noinline__ void
+stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1, Thr&& thr, Hit&& hit)
+{
+    const Xf X = make_xf(P, S, C);
+    constexpr int   EPV   = DT == FTB200_F32 ? 4 : 8;
+    const int       tid   = threadIdx.x;
+    const uint4*    vp    = vec_base<DT>(C);
+    const bool      fast  = DT == FTB200_F32 ? (P.bias == nullptr) : packed_ok<DT>(P, C);
+    const bool      temp  = P.apply_temp != 0;
+    const float     inv   = C.inv_t;
+    const int       head  = C.head;
+    const int       vocab = P.vocab;
+    const u32*      flags = S.flags;
+    unsigned short* hitq  = S.hitq;
+    u32*            nhit  = S.nhit;
+    int             par   = 0;
+    if (tid == 0) {
+        nhit[0] = 0;
+        nhit[1] = 0;
+    }
+    __syncthreads();
+    for (int jb = j0; jb < j1; jb += kThreads * kHotUnroll, par ^= 1) {
+        const float thr_y = thr();
+        if (fast) {
+            const u32 thr2 = DT == FTB200_F32 ? 0u : raw_threshold_pair<DT>(P, C, thr_y);
+            hot_filter<DT>(vp, jb, j1, thr_y, thr2, inv, temp, hitq, nhit + par);
+        }
+        __syncthreads();
+        // embedding bias or a non-positive temperature: every vector takes the exact path
+        const int n = fast ? (int)nhit[par] : (j1 - jb < kThreads * kHotUnroll ? j1 - jb : kThreads * kHotUnroll);
+        if (tid == 0) {
+            nhit[par ^ 1] = 0;
+        }
+#pragma unroll 1
+        for (int i = tid; i < n; i += kThreads) {
+            const int   j  = jb + (fast ? (int)hitq[i] : i);
+            const bool  sp = (flags[j >> 5] >> (j & 31)) & 1u;
+            const uint4 r  = ld_nc_v4(vp + j);
+            const int   vb = head + j * EPV;
+#pragma unroll 1
+            for (int e = 0; e < EPV; ++e) {
+                const int v = vb + e;
+                if (v < vocab) {
+                    float y = temp_value<DT>(X, raw_bits<DT>(r, e), v);
+                    if (y >= thr_y) {
+                        // special columns are reported by visit_specials with their final value
+                        if (!(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
+                            hit(v, y);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Hot side of the row maximum: packed (16-bit) or plain (fp32) running maximum over raw values.
+template<int DT>
+__device__ __noinline__ u32 hot_max(const uint4* vp, int jn)
+{
+    const int tid   = threadIdx.x;
+    float     best  = -INFINITY;
+    u32       best2 = DT == FTB200_F16 ? 0xfc00fc00u : 0xff80ff80u;
+    for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
+        uint4 q[kHotUnroll];
+#pragma unroll
+        for (int u = 0; u < kHotUnroll; ++u) {
             int j = jb + u * kThreads + tid;
-            if (j < j1) {
+            if (j < jn) {
                 q[u] = ld_nc_v4(vp + j);
             }
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            int j = jb + u * kThreads + tid;
-            if (j < j1) {
-                const bool sp = (S.flags[j >> 5] >> (j & 31)) & 1u;
-                const u32  w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
-                const int  vb   = C.head + j * EPV;
-#pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    u32 bits = (DT == FTB200_F32) ? w[e] : ((w[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
-                    int v    = vb + e;
-                    float y;
-                    if (v >= P.vocab) {
-                        y = -INFINITY;
-                    }
-                    else {
-                        y = temp_value<DT>(P, C, bits, v);
-                        if (sp) {
-                            u32 fl = hash_lookup(P, S, v);
-                            if (fl) {
-                                y = special_value<DT>(P, C, y, fl);
-                            }
-                        }
-                    }
-                    f(v, y);
+        for (int u = 0; u < kHotUnroll; ++u) {
+            if (jb + u * kThreads + tid < jn) {
+                if (DT == FTB200_F32) {
+                    best = fmaxf(best, fmaxf(fmaxf(__uint_as_float(q[u].x), __uint_as_float(q[u].y)),
+                                             fmaxf(__uint_as_float(q[u].z), __uint_as_float(q[u].w))));
+                }
+                else {
+                    best2 = max2<DT>(max2<DT>(best2, q[u].x), max2<DT>(q[u].y, max2<DT>(q[u].z, q[u].w)));
                 }
             }
+        }
+    }
+    return DT == FTB200_F32 ? __float_as_uint(best) : best2;
+}
+
+// Largest temperature-scaled value of the row (thread-local; -inf when none).  With include_flagged the
+// hot loop covers every column as if none were penalised or banned; without it the special columns
+// (those with a hash entry) are left out, at the price of a per-column look-up in flagged vectors.
+template<int DT>
+__device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const RowCtx& C, bool include_flagged)
+{
+    const Xf X = make_xf(P, S, C);
+    constexpr int EPV   = DT == FTB200_F32 ? 4 : 8;
+    const int     tid   = threadIdx.x;
+    const uint4*  vp    = vec_base<DT>(C);
+    const bool    pk    = packed_ok<DT>(P, C);
+    const bool    fast  = (DT == FTB200_F32 ? (P.bias == nullptr && C.inv_t > 0.0f) : pk) && include_flagged;
+    const int     nfull = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / EPV : 0);
+    float         best  = -INFINITY;
+    const int     jfast = fast ? nfull : 0;
+    if (jfast > 0) {
+        // temperature is monotone for inv_t > 0: the largest raw value gives the largest final value
+        const u32 m = hot_max<DT>(vp, jfast);
+        if (DT == FTB200_F32) {
+            const float raw = __uint_as_float(m);
+            best            = raw > -INFINITY ? temp_value<DT>(X, m, 0) : raw;
+        }
+        else {
+            best = fmaxf(temp_value<DT>(X, m & 0xffffu, 0), temp_value<DT>(X, m >> 16, 0));
+        }
+    }
+#pragma unroll 1
+    for (int j = jfast + tid; j < C.nvec; j += kThreads) {
+        const bool  sp = !include_flagged && ((S.flags[j >> 5] >> (j & 31)) & 1u);
+        const uint4 r  = ld_nc_v4(vp + j);
+        const int   vb = C.head + j * EPV;
+#pragma unroll 1
+        for (int e = 0; e < EPV; ++e) {
+            const int v = vb + e;
+            if (v < P.vocab && !(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
+                best = fmaxf(best, temp_value<DT>(X, raw_bits<DT>(r, e), v));
+            }
+        }
+    }
+    return best;
+}
+
+// f(v, y) for every special column (history token, banned word, min-length mask: the entries of the
+// hash table) with its final value, and for the unaligned head / tail columns of the row.
+// Columns whose final value is below thr_y are not reported (pass -inf to see every column).
+template<int DT, class F>
+__device__ __noinline__ void visit_specials(const KParams& P, const Smem& S, const RowCtx& C, float thr_y, F&& f)
+{
+    constexpr int EPV = DT == FTB200_F32 ? 4 : 8;
+    const Xf      X   = make_xf(P, S, C);
+    const int     tid = threadIdx.x;
+    const char*   rowp = C.rowp;
+    const int     nslots = P.hash_slots;
+#pragma unroll 1
+    for (int i = tid; i < nslots; i += kThreads) {
+        const u32 w = X.hash[i];
+        if (w == kHashEmpty) {
+            continue;
+        }
+        const int v = (int)(w >> 2);
+        float     y = -INFINITY;
+        if (v < X.vocab) {
+            const u32 bits = DT == FTB200_F32 ? __ldg((const u32*)rowp + v) : (u32)__ldg((const unsigned short*)rowp + v);
+            y              = special_value<DT>(X, temp_value<DT>(X, bits, v), w & 3u);
+        }
+        if (y >= thr_y) {
+            f(v, y);
+        }
+    }
+    // row edges that no 16-byte vector covers; special ones were reported above
+    const int tail0 = C.head + C.nvec * EPV;
+    const int nedge = C.head + (P.vocab_padded - tail0);
+#pragma unroll 1
+    for (int i = tid; i < nedge; i += kThreads) {
+        const int v = i < C.head ? i : tail0 + (i - C.head);
+        if (hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v)) {
+            continue;
+        }
+        float y = -INFINITY;
+        if (v < X.vocab) {
+            const u32 bits = DT == FTB200_F32 ? __ldg((const u32*)rowp + v) : (u32)__ldg((const unsigned short*)rowp + v);
+            y              = temp_value<DT>(X, bits, v);
+        }
+        if (y >= thr_y) {
+            f(v, y);
         }
     }
 }
@@ -577,16 +888,21 @@ static __device__ __noinline__ void topk_finish(const KParams& P, const Smem& S,
     if (tid < 8) {
         s_lane_base[tid] = 0;
     }
+    // e_i in parallel; the sum and the walk keep the reference's sequential order (:276-287)
+    {
+        const float s_max = k_eff > 0 ? fkey_inv(~(u32)(sorted[0] >> 32)) : 0.0f;
+        for (int i = tid; i < k_eff; i += kThreads) {
+            float y   = fkey_inv(~(u32)(sorted[i] >> 32));
+            S.val2[i] = use_exp ? __expf(y - s_max) : y;
+        }
+    }
+    __syncthreads();
     if (tid == 0) {
         s_pick = -1;
         if (k_eff > 0) {
-            const float s_max = fkey_inv(~(u32)(sorted[0] >> 32));
-            float       sum   = 0.0f;
+            float sum = 0.0f;
             for (int i = 0; i < k_eff; ++i) {
-                float y   = fkey_inv(~(u32)(sorted[i] >> 32));
-                float e   = use_exp ? __expf(y - s_max) : y;
-                S.val2[i] = e;
-                sum += e;
+                sum += S.val2[i];
             }
             float rand_num = u * top_p * sum;
             int   pick     = k_eff - 1;
@@ -662,20 +978,39 @@ static __device__ __noinline__ void topk_finish(const KParams& P, const Smem& S,
 template<int DT>
 __device__ __noinline__ void row_argmax(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O)
 {
-    const u32 bs1  = P.max_top_k <= 16 ? 128 : 256;
-    u64       best = 0;
-    stream_range<DT>(P, S, C, 0, C.nvec, true, [&](int v, float y) {
+    __shared__ u64 s_best;
+    const u32      bs1 = P.max_top_k <= 16 ? 128 : 256;
+    if (threadIdx.x == 0) {
+        s_best = 0;
+    }
+    __syncthreads();
+    const int sh1 = bs1 == 128 ? 7 : 8;
+    auto consider = [&](int v, float y) {
         if (y > C.neg_max) {
             // value, then CTA lane descending, thread descending, column ascending
-            u32 tie = ((((u32)v / bs1) & 7u) << 29) | (((u32)v % bs1) << 21) | (0x1fffffu - (u32)v);
-            u64 c   = ((u64)fkey(y) << 32) | tie;
-            best    = c > best ? c : best;
+            u32 tie = ((((u32)v >> sh1) & 7u) << 29) | (((u32)v & (bs1 - 1)) << 21) | (0x1fffffu - (u32)v);
+            const u64 c = ((u64)fkey(y) << 32) | tie;
+            if (c > *(volatile u64*)&s_best) {
+                atomicMax(&s_best, c);
+            }
         }
-    });
-    best = block_max_u64(best);
+    };
+    // the filter threshold is the CTA's running maximum: only a handful of columns per row reach
+    // the exact compare, so a warp almost never leaves the packed loop
+    auto running = [&]() {
+        const u64 b = *(volatile u64*)&s_best;
+        return b == 0 ? -INFINITY : fkey_inv((u32)(b >> 32));
+    };
+    // one vector per thread seeds the maximum; after that a hit is a rare event
+    const int jseed = C.nvec < kThreads ? C.nvec : kThreads;
+    stream_filtered<DT>(P, S, C, 0, jseed, running, consider);
+    stream_filtered<DT>(P, S, C, jseed, C.nvec, running, consider);
+    visit_specials<DT>(P, S, C, running(), consider);
+    __syncthreads();
     if (threadIdx.x == 0) {
-        int id    = best == 0 ? 0 : (int)(0x1fffffu - (u32)(best & 0x1fffffu));
-        *O.id_out = id;
+        const u64 best = s_best;
+        int       id   = best == 0 ? 0 : (int)(0x1fffffu - (u32)(best & 0x1fffffu));
+        *O.id_out      = id;
         write_lengths(P, O, id);
     }
     __syncthreads();
@@ -683,12 +1018,13 @@ __device__ __noinline__ void row_argmax(const KParams& P, const Smem& S, const R
 
 // ---- top-k, k > 1, no log-probs: one pass, running threshold, candidates in shared memory ----------
 template<int DT>
-__device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O, u64* gscratch, int k,
-                         float u, float top_p)
+__device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O,
+                                      u64* gscratch, int k, float u, float top_p)
 {
     __shared__ u32 s_n, s_ovf;
+    constexpr int  EPV = DT == FTB200_F32 ? 4 : 8;
     const int      tid = threadIdx.x;
-    constexpr int  VB  = kThreads * kUnroll;
+    constexpr int  VB  = kThreads * kHotUnroll;
 
     auto count_w = [&](int b) { return (double)S.hist[b]; };
     auto thr_of  = [&](int b) { return b < 0 ? 0u : ((u32)b << 20); };
@@ -705,55 +1041,67 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
     u64* cand = S.cand;
     int  n    = 0;
     bool slow = false;
-    {
-        // warm-up: histogram the first batch, derive a threshold, then collect that batch
-        const int j1 = C.nvec < VB ? C.nvec : VB;
-        stream_range<DT>(P, S, C, 0, j1, true, [&](int v, float y) {
-            if (y > C.neg_max) {
-                atomicAdd(&S.hist[fkey(y) >> 20], 1u);
-            }
-        });
-        __syncthreads();
-        u32 thr = thr_of(find_from_top(count_w, (double)k, nullptr));
-        stream_range<DT>(P, S, C, 0, j1, true, [&](int v, float y) {
-            if (y > C.neg_max) {
-                u32 key = fkey(y);
-                if (key >= thr) {
-                    u32 pos = atomicAdd(&s_n, 1u);
-                    if (pos < (u32)kCap) {
-                        cand[pos] = ((u64)(~key) << 32) | (u32)v;
-                    }
-                    else {
-                        s_ovf = 1;
-                    }
+    u32  thr  = 0;  // order-preserving key of the current cut; columns below it cannot be in the top k
+    auto histo = [&](int v, float y) {
+        if (y > C.neg_max) {
+            atomicAdd(&S.hist[fkey(y) >> 20], 1u);
+        }
+    };
+    auto push = [&](int v, float y) {
+        if (y > C.neg_max) {
+            u32 key = fkey(y);
+            if (key >= thr) {
+                u32 pos = atomicAdd(&s_n, 1u);
+                if (pos < (u32)kCap) {
+                    cand[pos] = ((u64)(~key) << 32) | (u32)v;
+                }
+                else {
+                    s_ovf = 1;
                 }
             }
-        });
+        }
+    };
+    auto histo_push = [&](int v, float y) {
+        if (y > C.neg_max) {
+            u32 key = fkey(y);
+            if (key >= thr) {
+                atomicAdd(&S.hist[key >> 20], 1u);
+                u32 pos = atomicAdd(&s_n, 1u);
+                if (pos < (u32)kCap) {
+                    cand[pos] = ((u64)(~key) << 32) | (u32)v;
+                }
+                else {
+                    s_ovf = 1;
+                }
+            }
+        }
+    };
+    auto thr_f = [&]() { return thr == 0 ? -INFINITY : fkey_inv(thr); };
+    {
+        // warm-up: histogram the first columns, derive a cut from them (a valid lower bound of the k-th
+        // value whatever the rest of the row holds), then collect those columns and the special ones
+        int warm = (k * 8 > 2048 ? k * 8 : 2048) / EPV;
+        warm     = (warm + kThreads - 1) / kThreads * kThreads;
+        const int j1 = C.nvec < warm ? C.nvec : warm;
+        stream_all<DT>(P, S, C, 0, j1, histo);
+        __syncthreads();
+        thr = thr_of(find_from_top(count_w, (double)k, nullptr));
+        stream_filtered<DT>(P, S, C, 0, j1, thr_f, push);
+        visit_specials<DT>(P, S, C, thr_f(), histo_push);
         __syncthreads();
         slow = s_ovf != 0;
-        // remaining batches: histogram and collect what passes the current threshold
-        for (int j0 = j1; j0 < C.nvec && !slow; j0 += VB) {
-            const int je = j0 + VB < C.nvec ? j0 + VB : C.nvec;
+        // the rest of the row: only columns at or above the cut are histogrammed and collected
+        // batches double in size (up to VB vectors), so each one sends about k columns down the
+        // exact path whatever k is, and the candidate buffer never sees a burst it cannot hold
+        for (int j0 = j1, je = 0; j0 < C.nvec && !slow; j0 = je) {
+            const int step = j0 < VB ? j0 : VB;
+            je             = j0 + step < C.nvec ? j0 + step : C.nvec;
             const u32 n0 = s_n;
             __syncthreads();
-            stream_range<DT>(P, S, C, j0, je, false, [&](int v, float y) {
-                if (y > C.neg_max) {
-                    u32 key = fkey(y);
-                    if (key >= thr) {
-                        atomicAdd(&S.hist[key >> 20], 1u);
-                        u32 pos = atomicAdd(&s_n, 1u);
-                        if (pos < (u32)kCap) {
-                            cand[pos] = ((u64)(~key) << 32) | (u32)v;
-                        }
-                        else {
-                            s_ovf = 1;
-                        }
-                    }
-                }
-            });
+            stream_filtered<DT>(P, S, C, j0, je, thr_f, histo_push);
             __syncthreads();
             if (s_ovf) {
-                // the batch did not fit: raise the threshold, shrink, and collect the batch again
+                // the batch did not fit: raise the cut, shrink, and collect the batch again
                 thr   = thr_of(find_from_top(count_w, (double)k, nullptr));
                 int m = compact_candidates(cand, (int)n0, thr);
                 __syncthreads();
@@ -762,24 +1110,13 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
                     s_ovf = 0;
                 }
                 __syncthreads();
-                stream_range<DT>(P, S, C, j0, je, false, [&](int v, float y) {
-                    if (y > C.neg_max) {
-                        u32 key = fkey(y);
-                        if (key >= thr) {
-                            u32 pos = atomicAdd(&s_n, 1u);
-                            if (pos < (u32)kCap) {
-                                cand[pos] = ((u64)(~key) << 32) | (u32)v;
-                            }
-                            else {
-                                s_ovf = 1;
-                            }
-                        }
-                    }
-                });
+                stream_filtered<DT>(P, S, C, j0, je, thr_f, push);
                 __syncthreads();
                 slow = s_ovf != 0;
             }
-            else if (s_n > (u32)(kCap / 2)) {
+            else if (s_n > (u32)(kCap / 2) || s_n - n0 > 96u) {
+                // raise the cut while a batch still sends a noticeable number of columns down the
+                // exact path
                 thr   = thr_of(find_from_top(count_w, (double)k, nullptr));
                 int m = compact_candidates(cand, (int)s_n, thr);
                 __syncthreads();
@@ -805,23 +1142,21 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
             s_n = 0;
         }
         __syncthreads();
-        stream_range<DT>(P, S, C, 0, C.nvec, true, [&](int v, float y) {
-            if (y > C.neg_max) {
-                atomicAdd(&S.hist[fkey(y) >> 20], 1u);
-            }
-        });
+        stream_all<DT>(P, S, C, 0, C.nvec, histo);
+        visit_specials<DT>(P, S, C, -INFINITY, histo);
         __syncthreads();
-        const u32 thr = thr_of(find_from_top(count_w, (double)k, nullptr));
-        cand          = gscratch;
-        stream_range<DT>(P, S, C, 0, C.nvec, true, [&](int v, float y) {
+        thr  = thr_of(find_from_top(count_w, (double)k, nullptr));
+        cand = gscratch;
+        auto push_all = [&](int v, float y) {
             if (y > C.neg_max) {
                 u32 key = fkey(y);
                 if (key >= thr) {
-                    u32 pos   = atomicAdd(&s_n, 1u);
-                    cand[pos] = ((u64)(~key) << 32) | (u32)v;
+                    cand[atomicAdd(&s_n, 1u)] = ((u64)(~key) << 32) | (u32)v;
                 }
             }
-        });
+        };
+        stream_filtered<DT>(P, S, C, 0, C.nvec, thr_f, push_all);
+        visit_specials<DT>(P, S, C, thr_f(), push_all);
         __syncthreads();
         n = (int)s_n;
     }
@@ -838,6 +1173,124 @@ __device__ __forceinline__ int lin_bucket(float y, float maxv)
     return kNB - 1 - q;
 }
 
+// Pass 2 of a soft-max row (reads the row again, from L2): e = T(__expf(y - max)) for every column,
+// summed per "virtual thread" exactly as addBiasSoftMax's min(V,1024)-thread strided loop does
+// (kernels/sampling_topp_kernels.cu:1331-1334), plus the bucket counts.  The per-virtual-thread partial
+// sums land in S.val2[0..nvt).
+template<int DT>
+__device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, const RowCtx& C, float maxv, int nvt)
+{
+    const Xf X = make_xf(P, S, C);
+    constexpr int ES  = DT == FTB200_F32 ? 4 : 2;
+    const int     tid = threadIdx.x;
+    u32*          hist = S.hist;
+    const u32*    flags = S.flags;
+    float*        val2 = S.val2;
+    const char*   rowp = C.rowp;
+    const int     vpad = P.vocab_padded, vocab = P.vocab, head = C.head, nvec = C.nvec;
+    const float   neg_max = C.neg_max;
+        float     acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const bool grouped = nvt == 1024 && (((size_t)rowp) % (4 * ES) == 0) && (head % 4 == 0);
+        if (grouped) {
+            // thread t owns virtual threads 4t..4t+3: one 4-element load per 1024-column chunk
+            constexpr int UN = 8;
+            for (int m0 = 0; m0 * 1024 < vpad; m0 += UN) {
+                u32 raw[UN][4];
+#pragma unroll
+                for (int uu = 0; uu < UN; ++uu) {
+                    const int v0 = (m0 + uu) * 1024 + 4 * tid;
+                    if (v0 + 3 < vpad) {
+                        if (DT == FTB200_F32) {
+                            uint4 q    = *(const uint4*)(rowp + (size_t)v0 * 4);
+                            raw[uu][0] = q.x, raw[uu][1] = q.y, raw[uu][2] = q.z, raw[uu][3] = q.w;
+                        }
+                        else {
+                            uint2 q    = *(const uint2*)(rowp + (size_t)v0 * 2);
+                            raw[uu][0] = q.x & 0xffffu, raw[uu][1] = q.x >> 16;
+                            raw[uu][2] = q.y & 0xffffu, raw[uu][3] = q.y >> 16;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int uu = 0; uu < UN; ++uu) {
+                    const int v0 = (m0 + uu) * 1024 + 4 * tid;
+                    if (v0 >= vpad) {
+                        continue;
+                    }
+                    const bool sampled = ((tid + m0 + uu) & 15) == 0;
+                    if (v0 + 3 < vpad) {
+                        bool sp = true;
+                        if (v0 >= head) {
+                            const int j = (v0 - head) / (DT == FTB200_F32 ? 4 : 8);
+                            sp          = j >= nvec || ((flags[j >> 5] >> (j & 31)) & 1u);
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int v = v0 + e;
+                            float     y = -INFINITY;
+                            if (v < vocab) {
+                                y = temp_value<DT>(X, raw[uu][e], v);
+                                if (sp) {
+                                    u32 fl = hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v);
+                                    if (fl) {
+                                        y = special_value<DT>(X, y, fl);
+                                    }
+                                }
+                            }
+                            if (y > neg_max) {
+                                float ex = round_to_T<DT>(__expf(y - maxv));
+                                acc[e] += ex;
+                                if (sampled) {
+                                    atomicAdd(&hist[lin_bucket(y, maxv)], 1u);
+                                }
+                            }
+                        }
+                    }
+                    else {
+                        for (int e = 0; e < 4 && v0 + e < vpad; ++e) {
+                            float y = elem_at<DT>(P, S, C, v0 + e);
+                            if (y > neg_max) {
+                                float ex = round_to_T<DT>(__expf(y - maxv));
+                                acc[e] += ex;
+                                if (sampled) {
+                                    atomicAdd(&hist[lin_bucket(y, maxv)], 1u);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            for (int e = 0; e < 4; ++e) {
+                val2[4 * tid + e] = acc[e];
+            }
+        }
+        else {
+            // thread t owns virtual threads t, t+256, t+512, t+768
+            for (int v0 = 0; v0 < vpad; v0 += nvt) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int vt = tid + q * kThreads;
+                    const int v  = v0 + vt;
+                    if (vt < nvt && v < vpad) {
+                        float y = elem_at<DT>(P, S, C, v);
+                        if (y > neg_max) {
+                            float ex = round_to_T<DT>(__expf(y - maxv));
+                            acc[q] += ex;
+                            if (((vt + v0 / nvt) & 15) == 0) {
+                                atomicAdd(&hist[lin_bucket(y, maxv)], 1u);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            for (int q = 0; q < 4; ++q) {
+                val2[tid + q * kThreads] = acc[q];
+            }
+        }
+}
+
 template<int DT>
 __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O, u64* gscratch,
                             bool is_topp, int k, float u, float top_p, bool want_lp)
@@ -849,15 +1302,46 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     __shared__ u32   s_nbig;
     const int        tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
 
-    // pass 1 (HBM): row maximum and its first column
-    u64 best = 0;
-    stream_range<DT>(P, S, C, 0, C.nvec, true, [&](int v, float y) {
+    // pass 1 (HBM): row maximum
+    __shared__ int s_argmax;
+    // The hot loop takes the maximum over every column as if no token were penalised or banned.  That
+    // is the maximum of the ordinary columns unless a special column holds a pre-penalty value that
+    // large; then the row is read again with the special columns left out.
+    __shared__ int s_redo;
+    if (tid == 0) {
+        s_redo = 0;
+    }
+    float tall = stream_max<DT>(P, S, C, true);
+    tall       = fkey_inv((u32)(block_max_u64((u64)fkey(tall) << 32) >> 32));
+    float tmax = -INFINITY;
+    {
+        const Xf X = make_xf(P, S, C);
+        bool     clash = false;
+        for (int i = tid; i < P.hash_slots; i += kThreads) {
+            const u32 w = X.hash[i];
+            if (w != kHashEmpty && (int)(w >> 2) < P.vocab) {
+                const int v    = (int)(w >> 2);
+                u32       bits = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
+                clash |= temp_value<DT>(X, bits, v) >= tall;
+            }
+        }
+        if (clash) {
+            s_redo = 1;
+        }
+    }
+    __syncthreads();
+    if (s_redo) {
+        tmax = stream_max<DT>(P, S, C, false);
+    }
+    else {
+        tmax = tall;
+    }
+    visit_specials<DT>(P, S, C, -INFINITY, [&](int v, float y) {
         if (y > C.neg_max) {
-            u64 c = ((u64)fkey(y) << 32) | (0xffffffffu - (u32)v);
-            best  = c > best ? c : best;
+            tmax = fmaxf(tmax, y);
         }
     });
-    best = block_max_u64(best);
+    const u64 best = block_max_u64(tmax > C.neg_max ? ((u64)fkey(tmax) << 32) | 1u : 0ull);
     if (best == 0) {
         if (tid == 0) {
             *O.id_out = 0;
@@ -866,144 +1350,121 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         __syncthreads();
         return;
     }
-    const float maxv   = fkey_inv((u32)(best >> 32));
-    const int   argmax = (int)(0xffffffffu - (u32)(best & 0xffffffffu));
+    const float maxv = fkey_inv((u32)(best >> 32));
+
+    // pass 2 (L2): exponentials, the denominator in the reference's summation order, and bucket counts
+    // of every 16th group of columns.  Shared-memory atomics retire about one lane per clock, so a
+    // full histogram would cost more than the rest of the row; the sample only has to place the cut.
+    for (int i = tid; i < kNB; i += kThreads) {
+        S.hist[i] = 0;
+    }
+    __syncthreads();
+    const int nvt = P.vocab < 1024 ? P.vocab : 1024;  // blockDim of addBiasSoftMax (:1364)
+    softmax_pass2<DT>(P, S, C, maxv, nvt);
+    __syncthreads();
+    if (wid == 0) {
+        float s = butterfly_block_sum(S.val2, nvt);
+        if (lane == 0) {
+            s_S = s;
+        }
+    }
+    __syncthreads();
+    const float denom = s_S + 1e-6f;
+
+    if (is_topp) {
+        // arg-max shortcut of topp_beam_topk_kernel (sampling_topp_kernels.cu:801-860)
+        const float p_max = round_to_T<DT>(round_to_T<DT>(1.0f) / denom);
+        if (p_max >= top_p) {
+            // first column holding the maximum (TopK<T,1>: larger value, then smaller column)
+            if (tid == 0) {
+                s_argmax = 0x7fffffff;
+            }
+            __syncthreads();
+            auto first_max = [&](int v, float y) {
+                if (y == maxv) {
+                    atomicMin(&s_argmax, v);
+                }
+            };
+            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return maxv; }, first_max);
+            visit_specials<DT>(P, S, C, maxv, first_max);
+            __syncthreads();
+            const int argmax = s_argmax;
+            if (tid == 0) {
+                *O.id_out = argmax;
+                if (want_lp) {
+                    float lprob = logf(p_max);
+                    if (P.cum_log_probs != nullptr) {
+                        P.cum_log_probs[O.r] += lprob;
+                    }
+                    if (P.out_log_probs != nullptr) {
+                        P.out_log_probs[O.r] = lprob;
+                    }
+                }
+                write_lengths(P, O, argmax);
+            }
+            __syncthreads();
+            return;
+        }
+    }
+    const float rand_num = u * top_p;
+    __shared__ int s_bthr;
+
+    // Provisional cut from the sample (x16), taken generously; the exact counts above it follow.
+    int b_cut;
+    {
+        int b_est;
+        if (is_topp) {
+            const float scale = 16.0f / denom;
+            auto        w     = [&](int b) {
+                const int q = kNB - 1 - b;
+                return (double)S.hist[b] * (double)(__expf(-((float)q + 0.5f) / (float)kLinScale) * scale);
+            };
+            b_est = find_from_top(w, (double)(rand_num * 1.25f + 0.02f), nullptr);
+        }
+        else {
+            auto w = [&](int b) { return 16.0 * (double)S.hist[b]; };
+            b_est  = find_from_top(w, 1.25 * (double)k + 64.0, nullptr);
+        }
+        if (tid == 0) {
+            int bt    = b_est < 0 ? 0 : b_est;
+            u32 extra = 0;
+            while (bt > 0 && extra < 8u) {
+                --bt;
+                extra += S.hist[bt];
+            }
+            s_bthr = bt;
+        }
+        __syncthreads();
+        b_cut = s_bthr;
+        __syncthreads();
+    }
 
     for (int attempt = 0; attempt < 2; ++attempt) {
-        const bool force_complete = attempt == 1;
-        // pass 2 (L2): exponentials, the denominator in the reference's summation order, bucket counts
+        if (attempt == 1) {
+            b_cut = 0;  // the provisional cut was too high: count and collect the whole row
+        }
+        // exact bucket counts of the columns above the provisional cut (filtered read from L2)
         for (int i = tid; i < kNB; i += kThreads) {
             S.hist[i] = 0;
         }
         __syncthreads();
-        const int nvt = P.vocab < 1024 ? P.vocab : 1024;  // blockDim of addBiasSoftMax (:1364)
-        float     acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const bool grouped = nvt == 1024 && (((size_t)C.rowp) % (4 * ES) == 0) && (C.head % 4 == 0);
-        if (grouped) {
-            // thread t owns virtual threads 4t..4t+3: one 4-element load per 1024-column chunk
-            constexpr int UN = 8;
-            for (int m0 = 0; m0 * 1024 < P.vocab_padded; m0 += UN) {
-                u32 raw[UN][4];
-#pragma unroll
-                for (int uu = 0; uu < UN; ++uu) {
-                    const int v0 = (m0 + uu) * 1024 + 4 * tid;
-                    if (v0 + 3 < P.vocab_padded) {
-                        if (DT == FTB200_F32) {
-                            uint4 q    = *(const uint4*)(C.rowp + (size_t)v0 * 4);
-                            raw[uu][0] = q.x, raw[uu][1] = q.y, raw[uu][2] = q.z, raw[uu][3] = q.w;
-                        }
-                        else {
-                            uint2 q    = *(const uint2*)(C.rowp + (size_t)v0 * 2);
-                            raw[uu][0] = q.x & 0xffffu, raw[uu][1] = q.x >> 16;
-                            raw[uu][2] = q.y & 0xffffu, raw[uu][3] = q.y >> 16;
-                        }
+        {
+            const float cut0 = b_cut == 0 ? -INFINITY :
+                                            maxv - (float)(kNB - b_cut) / (float)kLinScale - 1e-3f * fabsf(maxv) - 1e-3f;
+            auto count = [&](int v, float y) {
+                if (y > C.neg_max) {
+                    const int b = lin_bucket(y, maxv);
+                    if (b >= b_cut) {
+                        atomicAdd(&S.hist[b], 1u);
                     }
                 }
-#pragma unroll
-                for (int uu = 0; uu < UN; ++uu) {
-                    const int v0 = (m0 + uu) * 1024 + 4 * tid;
-                    if (v0 >= P.vocab_padded) {
-                        continue;
-                    }
-                    if (v0 + 3 < P.vocab_padded) {
-                        bool sp = true;
-                        if (v0 >= C.head) {
-                            const int j = (v0 - C.head) / (DT == FTB200_F32 ? 4 : 8);
-                            sp          = j >= C.nvec || ((S.flags[j >> 5] >> (j & 31)) & 1u);
-                        }
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int v = v0 + e;
-                            float     y = -INFINITY;
-                            if (v < P.vocab) {
-                                y = temp_value<DT>(P, C, raw[uu][e], v);
-                                if (sp) {
-                                    u32 fl = hash_lookup(P, S, v);
-                                    if (fl) {
-                                        y = special_value<DT>(P, C, y, fl);
-                                    }
-                                }
-                            }
-                            if (y > C.neg_max) {
-                                float ex = round_to_T<DT>(__expf(y - maxv));
-                                acc[e] += ex;
-                                atomicAdd(&S.hist[lin_bucket(y, maxv)], 1u);
-                            }
-                        }
-                    }
-                    else {
-                        for (int e = 0; e < 4 && v0 + e < P.vocab_padded; ++e) {
-                            float y = elem_at<DT>(P, S, C, v0 + e);
-                            if (y > C.neg_max) {
-                                float ex = round_to_T<DT>(__expf(y - maxv));
-                                acc[e] += ex;
-                                atomicAdd(&S.hist[lin_bucket(y, maxv)], 1u);
-                            }
-                        }
-                    }
-                }
-            }
+            };
+            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return cut0; }, count);
+            visit_specials<DT>(P, S, C, cut0, count);
             __syncthreads();
-            for (int e = 0; e < 4; ++e) {
-                S.val2[4 * tid + e] = acc[e];
-            }
         }
-        else {
-            // thread t owns virtual threads t, t+256, t+512, t+768
-            for (int v0 = 0; v0 < P.vocab_padded; v0 += nvt) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int vt = tid + q * kThreads;
-                    const int v  = v0 + vt;
-                    if (vt < nvt && v < P.vocab_padded) {
-                        float y = elem_at<DT>(P, S, C, v);
-                        if (y > C.neg_max) {
-                            float ex = round_to_T<DT>(__expf(y - maxv));
-                            acc[q] += ex;
-                            atomicAdd(&S.hist[lin_bucket(y, maxv)], 1u);
-                        }
-                    }
-                }
-            }
-            __syncthreads();
-            for (int q = 0; q < 4; ++q) {
-                S.val2[tid + q * kThreads] = acc[q];
-            }
-        }
-        __syncthreads();
-        if (wid == 0) {
-            float s = butterfly_block_sum(S.val2, nvt);
-            if (lane == 0) {
-                s_S = s;
-            }
-        }
-        __syncthreads();
-        const float denom = s_S + 1e-6f;
 
-        if (is_topp) {
-            // arg-max shortcut of topp_beam_topk_kernel (sampling_topp_kernels.cu:801-860)
-            const float p_max = round_to_T<DT>(round_to_T<DT>(1.0f) / denom);
-            if (p_max >= top_p) {
-                if (tid == 0) {
-                    *O.id_out = argmax;
-                    if (want_lp) {
-                        float lprob = logf(p_max);
-                        if (P.cum_log_probs != nullptr) {
-                            P.cum_log_probs[O.r] += lprob;
-                        }
-                        if (P.out_log_probs != nullptr) {
-                            P.out_log_probs[O.r] = lprob;
-                        }
-                    }
-                    write_lengths(P, O, argmax);
-                }
-                __syncthreads();
-                return;
-            }
-        }
-        const float rand_num = u * top_p;
-
-        // choose the lowest bucket to collect
+        // choose the lowest bucket to collect, now with a bound that holds
         int b_star;
         if (is_topp) {
             // lower bound of the probability mass of each bucket; 0.995 covers rounding of p to T
@@ -1021,9 +1482,24 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
             auto w = [&](int b) { return (double)S.hist[b]; };
             b_star = find_from_top(w, (double)k, nullptr);
         }
-        int b_thr = b_star - 1;
-        if (b_thr < 0 || force_complete) {
-            b_thr = 0;
+        // Collect below the deciding bucket until at least 64 more columns are in: the scan needs the
+        // 32 entries after the crossing, and the crossing must not fall into the lowest collected
+        // value class (which may continue below the cut).  16-bit logits leave many buckets empty.
+        if (tid == 0) {
+            int bt    = b_star < 0 ? b_cut : b_star;
+            u32 extra = 0;
+            while (bt > b_cut && extra < 64u) {
+                --bt;
+                extra += S.hist[bt];
+            }
+            // -1: the counted range does not reach far enough
+            s_bthr = (b_cut > 0 && (b_star < 0 || extra < 64u)) ? -1 : bt;
+        }
+        __syncthreads();
+        const int b_thr = s_bthr;
+        __syncthreads();
+        if (b_thr < 0) {
+            continue;
         }
         const bool complete = b_thr == 0;
 
@@ -1073,17 +1549,23 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         u64*       dest    = in_smem ? S.cand : gscratch;
 
         // pass 3 (L2): probabilities of the collected columns, written bucket by bucket
-        stream_range<DT>(P, S, C, 0, C.nvec, true, [&](int v, float y) {
-            if (y > C.neg_max) {
-                const int b = lin_bucket(y, maxv);
-                if (b >= b_thr) {
-                    float ex  = round_to_T<DT>(__expf(y - maxv));
-                    float pr  = round_to_T<DT>(ex / denom);
-                    u32   pos = atomicAdd(&S.hist[b], 1u);
-                    dest[pos] = ((u64)(~fkey(pr)) << 32) | (u32)v;
+        {
+            const float cut = b_thr == 0 ? -INFINITY :
+                                           maxv - (float)(kNB - b_thr) / (float)kLinScale - 1e-3f * fabsf(maxv) - 1e-3f;
+            auto collect = [&](int v, float y) {
+                if (y > C.neg_max) {
+                    const int b = lin_bucket(y, maxv);
+                    if (b >= b_thr) {
+                        float ex  = round_to_T<DT>(__expf(y - maxv));
+                        float pr  = round_to_T<DT>(ex / denom);
+                        u32   pos = atomicAdd(&S.hist[b], 1u);
+                        dest[pos] = ((u64)(~fkey(pr)) << 32) | (u32)v;
+                    }
                 }
-            }
-        });
+            };
+            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return cut; }, collect);
+            visit_specials<DT>(P, S, C, cut, collect);
+        }
         if (tid == 0) {
             s_nbig = 0;
         }
@@ -1341,7 +1823,7 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
 }
 
 template<int DT>
-__global__ void __launch_bounds__(kThreads, 3) decode_sampling_kernel(const __grid_constant__ KParams P)
+__global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __grid_constant__ KParams P)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int                                s_row;
@@ -1351,6 +1833,10 @@ __global__ void __launch_bounds__(kThreads, 3) decode_sampling_kernel(const __gr
     S.val2  = (float*)(S.hist + kNB);
     S.flags = (u32*)(S.val2 + 1024);
     S.hash  = S.flags + P.flag_words;
+    S.spec  = S.hash + P.hash_slots;
+    S.nspec = S.spec + P.hash_slots / 2;
+    S.nhit  = S.nspec + 1;
+    S.hitq  = (unsigned short*)(S.nhit + 3);
     u64* gscratch = P.scratch + (size_t)blockIdx.x * P.scratch_stride;
     for (;;) {
         __syncthreads();
@@ -1358,11 +1844,13 @@ __global__ void __launch_bounds__(kThreads, 3) decode_sampling_kernel(const __gr
             s_row = (int)atomicAdd(P.ticket, 1u);
         }
         __syncthreads();
-        const int r = s_row;
-        if (r >= P.local_batch) {
+        const int t = s_row;
+        if (t >= P.local_batch) {
             break;
         }
-        process_row<DT>(P, S, r, gscratch);
+        // rows are handed out costliest first when the caller supplied an order (longest-processing-
+        // time-first keeps the last CTAs from finishing alone with an expensive row)
+        process_row<DT>(P, S, P.row_order != nullptr ? P.row_order[t] : t, gscratch);
     }
 }
 

@@ -11,7 +11,7 @@ constexpr int kThreads   = 256;
 constexpr int kWarps     = kThreads / 32;
 constexpr int kNB        = 4096;  // histogram buckets
 constexpr int kCap       = 4096;  // candidate slots held in shared memory
-constexpr int kUnroll    = 4;     // 16-byte loads in flight per thread
+constexpr int kUnroll    = 8;     // 16-byte loads in flight per thread
 constexpr int kMaxTopK   = 1024;
 constexpr int kLinScale  = 64;    // linear buckets per logit unit below the row maximum
 constexpr int kWarpTile  = kCap / kWarps;
@@ -50,6 +50,7 @@ struct KParams {
     uint8_t* finished;
     float*   cum_log_probs;
     float*   out_log_probs;
+    const int* row_order;
     u32*     ticket;
     u64*     scratch;         // per-CTA candidate overflow area
     size_t   scratch_stride;  // u64 entries per CTA

@@ -42,6 +42,11 @@ class DynamicDecodeLayer:
         self.device = torch.device(device)
         self.stream = stream
         self._workspace = None
+        self._gate = {}
+        self.time_kernels = False   # when set, CUDA events bracket each fused launch (kernel_events)
+        self.kernel_events = []
+        self._count_dev = None
+        self._count_host = None
         self.launches = 0
 
     # ---- helpers -------------------------------------------------------------------------------
@@ -72,6 +77,7 @@ class DynamicDecodeLayer:
             raise NotImplementedError("beam search is served by fastertransformer_b200.beam_search")
         B, dev, st = int(batch_size), self.device, self._stream_ptr()
         self.batch_size = B
+        self._gate = {}
         a = runtime_args
         top_k = self._arg(a, "runtime_top_k")
         top_p = self._arg(a, "runtime_top_p")
@@ -144,6 +150,17 @@ class DynamicDecodeLayer:
                 _ptr(a.get("top_p_reset_ids")), st))
             self.topp.skip_host = self.topp.skip.cpu().numpy().astype(bool)
             self.topp.active = True
+        self._row_cost = self._estimate_row_cost()
+
+    def _estimate_row_cost(self):
+        """Relative cost of a row for the launch order: top-p rows cost most (three reads of the row and a
+        sort of the nucleus), then top-k by k."""
+        k = self.topk.top_ks.cpu().numpy().view(np.uint32).astype(np.float64)
+        cost = 1.0 + k / 128.0
+        if self.topp.active:
+            p = self.topp.top_ps.cpu().numpy().astype(np.float64)
+            cost = np.where(self.topk.skip_host, 10.0 + 8.0 * p, cost)
+        return cost
 
     # ---- forward (DynamicDecodeLayer.cc:191-474, sampling branch) ---------------------------------
     def forward(self, outputs, inputs):
@@ -154,13 +171,48 @@ class DynamicDecodeLayer:
         lbs = int(inputs.get("local_batch_size", B))
         mil = int(inputs["max_input_length"])
         lo, hi = ite * lbs, (ite + 1) * lbs
+        g = self._gate.get((lo, hi))
+        if g is None:
+            g = self._gate[(lo, hi)] = {
+                "topk_on": self.topk.active and not self.topk.skip_host[lo:hi].all(),
+                "topp_on": self.topp.active and not self.topp.skip_host[lo:hi].all(),
+                "temp": bool((self.temperature_host[lo:hi] != 1.0).any()),
+                "pen": bool((self.penalty_host[lo:hi] != self.penalty_default).any()),
+                "minlen": int(self.min_length_host[lo:hi].max()),
+                "order": torch.from_numpy(np.argsort(-self._row_cost[lo:hi], kind="stable").astype(np.int32))
+                .to(self.device),
+            }
+        self._g = g
+        topk_on, topp_on = g["topk_on"], g["topp_on"]
+        if topk_on or topp_on:
+            self._sample(outputs, inputs, logits, B, step, ite, lbs, mil, lo, hi, topk_on, topp_on)
+        return self._stop_criteria(outputs, inputs, B, step, lbs, lo)
+
+    def _stop_criteria(self, outputs, inputs, B, step, lbs, lo):
+        """Stop words, length limit and should_stop (DynamicDecodeLayer.cc:447-473)."""
+        sw = inputs.get("stop_words_list")
+        lim = inputs.get("sequence_limit_length")
+        if sw is None and lim is None:
+            return False
+        if self._count_dev is None:
+            self._count_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._count_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        L = 0 if sw is None else sw.shape[-1]
+        st = self._stream_ptr()
+        check(lib.ftb200_stop_criteria(
+            _ptr(outputs["output_ids"]), _ptr(outputs.get("parent_ids")),
+            None if sw is None else C.c_void_p(sw.data_ptr() + lo * 2 * L * 4), L, _ptr(outputs["finished"]),
+            _ptr(lim), lo, lbs, B, 1, step, _ptr(self._count_dev), C.c_void_p(self._count_host.data_ptr()), st))
+        self.launches += 1
+        if lim is None:
+            return False
+        stop = C.c_int(0)
+        check(lib.ftb200_wait_should_stop(C.c_void_p(self._count_host.data_ptr()), B, 1, st, 10000, C.byref(stop)))
+        return bool(stop.value)
+
+    def _sample(self, outputs, inputs, logits, B, step, ite, lbs, mil, lo, hi, topk_on, topp_on):
         Vp = self.vocab_size_padded
         es = logits.element_size()
-
-        topk_on = self.topk.active and not self.topk.skip_host[lo:hi].all()
-        topp_on = self.topp.active and not self.topp.skip_host[lo:hi].all()
-        if not (topk_on or topp_on):
-            return
 
         P = SamplingParams()
         P.dtype = _DT[logits.dtype]
@@ -182,13 +234,12 @@ class DynamicDecodeLayer:
             P.bad_words_len, P.bad_words_shared = L, int(shared)
         # host-side gating of the penalty kernels (BaseSamplingLayer.cc:302-349)
         P.temperature = self.temperature.data_ptr() + lo * 4
-        P.apply_temperature = int(bias is not None or bool((self.temperature_host[lo:hi] != 1.0).any()))
+        P.apply_temperature = int(bias is not None or self._g["temp"])
         P.repetition_penalty = self.penalty.data_ptr() + lo * 4
         P.penalty_type = self.penalty_type
-        P.apply_repetition = int(step > 1 and self.penalty_type != 2
-                                 and bool((self.penalty_host[lo:hi] != self.penalty_default).any()))
+        P.apply_repetition = int(step > 1 and self.penalty_type != 2 and self._g["pen"])
         P.min_lengths = self.min_length.data_ptr() + lo * 4
-        P.apply_min_length = int(bool((self.min_length_host[lo:hi] > step - mil).any()))
+        P.apply_min_length = int(self._g["minlen"] > step - mil)
 
         if topk_on:
             P.topk_states = self.topk.curand.data_ptr() + lo * CURAND_STATE_BYTES
@@ -217,12 +268,22 @@ class DynamicDecodeLayer:
             # [request_output_len, batch] sliced at (step - max_input_length) (DynamicDecodeLayer.cc:427-435)
             P.output_log_probs = olp.data_ptr() + ((step - mil) * B + lo) * 4
 
-        need = C.c_size_t(0)
-        check(lib.ftb200_sampling_workspace_bytes(P.dtype, lbs, Vp, C.byref(need)))
-        if self._workspace is None or self._workspace.numel() < need.value:
-            self._workspace = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+        P.row_order = self._g["order"].data_ptr()
+        if self._workspace is None or self._ws_key != (P.dtype, lbs, Vp):
+            need = C.c_size_t(0)
+            check(lib.ftb200_sampling_workspace_bytes(P.dtype, lbs, Vp, C.byref(need)))
+            if self._workspace is None or self._workspace.numel() < need.value:
+                self._workspace = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+            self._ws_key = (P.dtype, lbs, Vp)
         P.workspace = self._workspace.data_ptr()
         P.workspace_bytes = self._workspace.numel()
         P.stream = self._stream_ptr().value
-        check(lib.ftb200_decode_step_sampling(C.byref(P)))
-        self.launches += lib.ftb200_last_launch_count()
+        if self.time_kernels:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            check(lib.ftb200_decode_step_sampling(C.byref(P)))
+            e1.record()
+            self.kernel_events.append((e0, e1))
+        else:
+            check(lib.ftb200_decode_step_sampling(C.byref(P)))
+        self.launches += 1

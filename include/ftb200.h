@@ -146,6 +146,11 @@ typedef struct ftb200_sampling_params {
     float*   cum_log_probs;
     float*   output_log_probs; /* [local_batch_size] slice for this step */
 
+    /* ---- scheduling hint (device, [local_batch_size], a permutation of 0..local_batch_size-1; null = row
+     *      order).  Rows are started in this order; listing the expensive rows first (top-p, large k)
+     *      shortens the tail of the launch.  Results do not depend on it. ---- */
+    const int* row_order;
+
     /* ---- scratch ---- */
     void*  workspace;
     size_t workspace_bytes;
@@ -161,6 +166,36 @@ int ftb200_decode_step_sampling(const ftb200_sampling_params* p);
 
 /* Number of kernels the last ftb200_decode_step_sampling call on this thread launched. */
 int ftb200_last_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Bad-word ban as a stand-alone call (the fused step above already applies it; this entry serves
+ * callers that use the kernel by itself, e.g. the beam-search path).  Writes -inf into the logits.
+ * Replaces invokeBanBadWords, kernels/ban_bad_words.cu:88-120 (same argument meaning).
+ * ------------------------------------------------------------------------------------------ */
+int ftb200_ban_bad_words(void* logits, int dtype, const int* output_ids, const int* parent_ids, int batch_size,
+                         int local_batch_size, int beam_width, const int* bad_words, int share_words,
+                         int bad_words_len, int id_offset, int vocab_size_padded, int step, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Stop criteria after the ids of `step` are written: stop-word match, sequence-length limit, and the
+ * count of finished sequences.  One launch.
+ * Replaces invokeStopWordsCriterion (kernels/stop_criteria_kernels.cu:83-104) and
+ * invokeLengthCriterion (:129-157).  The reference spins on a pinned int without bound; here the count
+ * is copied to `finished_count_host` (pinned, 1 int) on the stream and ftb200_wait_should_stop waits for
+ * it with a deadline.
+ *   stop_words            [local_batch_size, 2, stop_words_len] for the local rows, or null
+ *   finished              bool[batch_size*beam_width], whole batch
+ *   sequence_limit_length uint32[batch_size], or null (then only stop words run and nothing is counted)
+ * ------------------------------------------------------------------------------------------ */
+int ftb200_stop_criteria(const int* output_ids, const int* parent_ids, const int* stop_words, int stop_words_len,
+                         uint8_t* finished, const uint32_t* sequence_limit_length, int id_offset,
+                         int local_batch_size, int batch_size, int beam_width, int step, int* finished_count_dev,
+                         int* finished_count_host, void* stream);
+
+/* Waits until the work enqueued on `stream` so far is done (at most timeout_ms, FTB200_TIMEOUT after
+ * that) and reports *should_stop = (finished_count_host[0] == batch_size*beam_width). */
+int ftb200_wait_should_stop(const int* finished_count_host, int batch_size, int beam_width, void* stream,
+                            int timeout_ms, int* should_stop);
 
 #ifdef __cplusplus
 }

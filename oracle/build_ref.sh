@@ -18,8 +18,9 @@ if [ ! -d "$REF/src/fastertransformer" ]; then
 fi
 
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
-# The reference's release configuration: fast math on (CMakeLists.txt:77, :200-201), C++17, bf16 enabled.
-FLAGS=(-gencode arch=compute_100a,code=sm_100a -std=c++17 -O3 --use_fast_math -DENABLE_BF16
+# The reference's release configuration: fast math on (CMakeLists.txt:77, :200-201), NDEBUG (CMAKE_BUILD_TYPE
+# Release: asserts off, log level INFO, utils/logger.h:84-88), C++17, bf16 enabled.
+FLAGS=(-gencode arch=compute_100a,code=sm_100a -std=c++17 -O3 --use_fast_math -DNDEBUG -DENABLE_BF16
        --expt-relaxed-constexpr --expt-extended-lambda -Xcompiler -fPIC -Xcompiler -w -w
        -I"$REF")
 

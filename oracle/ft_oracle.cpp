@@ -438,6 +438,8 @@ int oracle_decode_step_sampling(const ftb200_sampling_params* p)
     const float*  u_topp  = (const float*)p->topp_states;
     const bool    want_lp = p->cum_log_probs || p->output_log_probs;
 
+    // rows are independent: one OpenMP thread per row, as many threads as OMP_NUM_THREADS allows
+#pragma omp parallel for schedule(dynamic, 1)
     for (int r = 0; r < p->local_batch_size; ++r) {
         int mode = 0;
         if (u_topk && !(p->topk_skip && p->topk_skip[r])) {
