@@ -32,6 +32,8 @@ def _load():
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     l.ftb200_sampling_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
     l.ftb200_decode_step_sampling.argtypes = [C.POINTER(SamplingParams)]
+    l.ftb200_decode_step_sampling_static.argtypes = [C.POINTER(SamplingParams)]
+    l.ftb200_static_scratch_bytes.restype = C.c_size_t
     V, I = C.c_void_p, C.c_int
     l.ftb200_ban_bad_words.argtypes = [V, I, V, V, I, I, I, V, I, I, I, I, I, V]
     l.ftb200_stop_criteria.argtypes = [V, V, V, I, V, V, I, I, I, I, I, V, V, V]

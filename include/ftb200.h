@@ -197,6 +197,29 @@ int ftb200_stop_criteria(const int* output_ids, const int* parent_ids, const int
 int ftb200_wait_should_stop(const int* finished_count_host, int batch_size, int beam_width, void* stream,
                             int timeout_ms, int* should_stop);
 
+/* ------------------------------------------------------------------------------------------
+ * The fused decode-sampling step without a caller-provided workspace.
+ * No counterpart in the reference: FasterTransformer always draws its buffers from an IAllocator.
+ *
+ * For hosts that cannot allocate device memory at the point of call - a server whose memory pool owns the
+ * whole GPU, a plug-in callback that is forbidden to allocate, code inside a stream capture - the scratch
+ * of ftb200_decode_step_sampling is a fixed area of ftb200_static_scratch_bytes() (64 MiB) built into the
+ * library; every GPU that loads the library holds it until the process exits.  `workspace` and
+ * `workspace_bytes` of the argument block are ignored; everything else means what it means above and the
+ * results are the same.  No cudaMalloc, cudaFree or other allocating call is made.
+ *
+ *   - A shape whose ftb200_sampling_workspace_bytes() exceeds the area is refused with
+ *     FTB200_WORKSPACE_SMALL (about 63 rows per call at vocab 128256, 255 at 32000): slice the batch with
+ *     `ite` / `local_batch_size`.
+ *   - The first call on each device looks up the device address of the area (cudaGetSymbolAddress); make
+ *     that first call before any stream capture begins on that device.
+ *   - All calls on a device share the one area.  Calls that may overlap on the GPU (different streams, or
+ *     several host threads) race on it: serialise them, or give the overlapping ones their own workspace
+ *     through ftb200_decode_step_sampling.
+ * ------------------------------------------------------------------------------------------ */
+size_t ftb200_static_scratch_bytes(void);
+int    ftb200_decode_step_sampling_static(const ftb200_sampling_params* p);
+
 #ifdef __cplusplus
 }
 #endif
