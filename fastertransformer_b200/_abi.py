@@ -23,3 +23,30 @@ class SamplingParams(C.Structure):
         ("row_order", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
+
+
+class BeamHyps(C.Structure):
+    """ftb200_beam_hyps."""
+    _fields_ = [
+        ("output_ids_tgt", C.c_void_p), ("sequence_lengths_tgt", C.c_void_p), ("cum_log_probs", C.c_void_p),
+        ("normed_scores", C.c_void_p), ("log_probs", C.c_void_p), ("min_normed_scores", C.c_void_p),
+        ("num_beams", C.c_void_p), ("is_done", C.c_void_p), ("early_stopping", C.c_int),
+    ]
+
+
+class BeamParams(C.Structure):
+    """ftb200_beam_params."""
+    _fields_ = [
+        ("dtype", C.c_int), ("batch_size", C.c_int), ("local_batch_size", C.c_int), ("ite", C.c_int),
+        ("beam_width", C.c_int), ("vocab_size", C.c_int), ("vocab_size_padded", C.c_int), ("step", C.c_int),
+        ("max_input_length", C.c_int), ("max_seq_len", C.c_int),
+        ("logits", C.c_void_p), ("embedding_bias", C.c_void_p), ("end_ids", C.c_void_p),
+        ("input_lengths", C.c_void_p),
+        ("temperature", C.c_float), ("repetition_penalty", C.c_float), ("penalty_type", C.c_int),
+        ("min_length", C.c_int), ("diversity_rate", C.c_float), ("length_penalty", C.c_float),
+        ("output_ids", C.c_void_p), ("parent_ids", C.c_void_p), ("finished", C.c_void_p),
+        ("sequence_length", C.c_void_p), ("cum_log_probs", C.c_void_p), ("output_log_probs", C.c_void_p),
+        ("src_cache_indirection", C.c_void_p), ("tgt_cache_indirection", C.c_void_p),
+        ("beam_hyps", C.POINTER(BeamHyps)),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]

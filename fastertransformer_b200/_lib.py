@@ -12,7 +12,7 @@ class FtbError(RuntimeError):
         self.status = status
 
 
-from ._abi import SamplingParams  # noqa: E402,F401
+from ._abi import BeamHyps, BeamParams, SamplingParams  # noqa: E402,F401
 
 
 def _load():
@@ -34,6 +34,8 @@ def _load():
     l.ftb200_decode_step_sampling.argtypes = [C.POINTER(SamplingParams)]
     l.ftb200_decode_step_sampling_static.argtypes = [C.POINTER(SamplingParams)]
     l.ftb200_static_scratch_bytes.restype = C.c_size_t
+    l.ftb200_beam_workspace_bytes.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_size_t)]
+    l.ftb200_beam_search_step.argtypes = [C.POINTER(BeamParams)]
     V, I = C.c_void_p, C.c_int
     l.ftb200_ban_bad_words.argtypes = [V, I, V, V, I, I, I, V, I, I, I, I, I, V]
     l.ftb200_stop_criteria.argtypes = [V, V, V, I, V, V, I, I, I, I, I, V, V, V]

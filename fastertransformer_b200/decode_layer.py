@@ -10,7 +10,7 @@ import ctypes as C
 import numpy as np
 import torch
 
-from ._lib import SamplingParams, check, lib
+from ._lib import BeamHyps, BeamParams, SamplingParams, check, lib
 
 _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 CURAND_STATE_BYTES = 48  # sizeof(curandState_t), XORWOW
@@ -42,6 +42,7 @@ class DynamicDecodeLayer:
         self.device = torch.device(device)
         self.stream = stream
         self._workspace = None
+        self._beam_ws = None
         self._gate = {}
         self.time_kernels = False   # when set, CUDA events bracket each fused launch (kernel_events)
         self.kernel_events = []
@@ -73,8 +74,16 @@ class DynamicDecodeLayer:
 
     # ---- setup (DynamicDecodeLayer.cc:153-178 -> TopK/TopPSamplingLayer::setup) -------------------
     def setup(self, batch_size, beam_width, runtime_args):
+        self.beam_width = int(beam_width)
+        # hasDiffRuntimeArgs (DynamicDecodeLayer.cc:477-514): beam search then runs one batch entry at a time
+        self.has_diff_runtime_args = False
+        for key in ("beam_search_diversity_rate", "temperature", "len_penalty", "repetition_penalty",
+                    "presence_penalty", "min_length"):
+            v = self._arg(runtime_args, key)
+            if v is not None and v.size > 1 and bool((v != v[0]).any()):
+                self.has_diff_runtime_args = True
         if beam_width != 1:
-            raise NotImplementedError("beam search is served by fastertransformer_b200.beam_search")
+            return  # the beam layers have no set-up (BaseBeamSearchLayer.cu:123-127)
         B, dev, st = int(batch_size), self.device, self._stream_ptr()
         self.batch_size = B
         self._gate = {}
@@ -165,6 +174,8 @@ class DynamicDecodeLayer:
     # ---- forward (DynamicDecodeLayer.cc:191-474, sampling branch) ---------------------------------
     def forward(self, outputs, inputs):
         logits = inputs["logits"]
+        if logits.dim() == 3 and logits.shape[1] > 1:
+            return self._forward_beam(outputs, inputs)
         B = logits.shape[0]
         step = int(inputs["step"])
         ite = int(inputs.get("ite", 0))
@@ -188,7 +199,93 @@ class DynamicDecodeLayer:
             self._sample(outputs, inputs, logits, B, step, ite, lbs, mil, lo, hi, topk_on, topp_on)
         return self._stop_criteria(outputs, inputs, B, step, lbs, lo)
 
-    def _stop_criteria(self, outputs, inputs, B, step, lbs, lo):
+    # ---- beam search branch (DynamicDecodeLayer.cc:286-386 -> OnlineBeamSearchLayer::forward) -------
+    def _forward_beam(self, outputs, inputs):
+        logits = inputs["logits"]
+        B, K, Vp = logits.shape
+        step = int(inputs["step"])
+        ite = int(inputs.get("ite", 0))
+        lbs = int(inputs.get("local_batch_size", B))
+        mil = int(inputs["max_input_length"])
+        st = self._stream_ptr()
+        es = logits.element_size()
+        out_ids = outputs["output_ids"]
+        L = out_ids.shape[0]
+        if "cum_log_probs" not in outputs:
+            raise RuntimeError("[FT][ERROR] cum_log_probs should be provided in beam search.")
+        bw = inputs.get("bad_words_list")
+        if bw is not None:
+            shared = bw.dim() == 2 or bw.shape[0] == 1
+            Lw = bw.shape[-1]
+            check(lib.ftb200_ban_bad_words(
+                C.c_void_p(logits.data_ptr() + ite * lbs * K * Vp * es), _DT[logits.dtype],
+                _ptr(out_ids), _ptr(outputs["parent_ids"]), B, lbs, K,
+                C.c_void_p(bw.data_ptr() if shared else bw.data_ptr() + ite * lbs * 2 * Lw * 4), int(shared), Lw,
+                ite * lbs, Vp, step, st))
+            self.launches += 1
+
+        def scalar(key, default):
+            v = inputs.get(key)
+            return default if v is None else np.atleast_1d(np.asarray(v)).reshape(-1)[0]
+
+        sub = 1 if self.has_diff_runtime_args else lbs
+        n_sub = lbs // sub
+        need = C.c_size_t(0)
+        check(lib.ftb200_beam_workspace_bytes(sub, K, C.byref(need)))
+        if self._beam_ws is None or self._beam_ws.numel() < need.value:
+            self._beam_ws = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+        hyps = outputs.get("beam_hyps")
+        for d_ite in range(ite * n_sub, (ite + 1) * n_sub):
+            row0 = d_ite * sub * K          # first batch-beam row of this sub-batch
+            P = BeamParams()
+            P.dtype = _DT[logits.dtype]
+            P.batch_size, P.local_batch_size, P.ite, P.beam_width = B, sub, d_ite, K
+            P.vocab_size, P.vocab_size_padded = self.vocab_size, Vp
+            P.step, P.max_input_length, P.max_seq_len = step, mil, L
+            P.logits = logits.data_ptr() + row0 * Vp * es
+            bias = inputs.get("embedding_bias")
+            P.embedding_bias = None if bias is None else bias.data_ptr()
+            P.end_ids = inputs["end_id"].data_ptr() + d_ite * sub * 4
+            il = inputs.get("input_lengths")
+            P.input_lengths = None if il is None else il.data_ptr() + row0 * 4
+            P.temperature = float(scalar("temperature", 1.0))
+            if "repetition_penalty" in inputs and "presence_penalty" in inputs:
+                raise RuntimeError("[FT][ERROR] Found ambiguous parameters repetition_penalty and "
+                                   "presence_penalty which are mutually exclusive.")
+            if inputs.get("repetition_penalty") is not None:
+                P.penalty_type, P.repetition_penalty = 1, float(scalar("repetition_penalty", 1.0))
+            elif inputs.get("presence_penalty") is not None:
+                P.penalty_type, P.repetition_penalty = 0, float(scalar("presence_penalty", 0.0))
+            else:
+                P.penalty_type, P.repetition_penalty = 2, 1.0
+            P.min_length = int(scalar("min_length", 0))
+            P.diversity_rate = float(scalar("beam_search_diversity_rate", 0.0))
+            P.length_penalty = float(scalar("len_penalty", 0.0))
+            P.output_ids = out_ids.data_ptr()
+            P.parent_ids = outputs["parent_ids"].data_ptr()
+            P.finished = outputs["finished"].data_ptr() + row0
+            P.sequence_length = outputs["sequence_length"].data_ptr() + row0 * 4
+            P.cum_log_probs = outputs["cum_log_probs"].data_ptr() + row0 * 4
+            olp = outputs.get("output_log_probs")
+            P.output_log_probs = None if olp is None else olp.data_ptr()
+            src, tgt = inputs.get("src_cache_indirection"), outputs.get("tgt_cache_indirection")
+            P.src_cache_indirection = None if src is None else src.data_ptr()
+            P.tgt_cache_indirection = None if tgt is None else tgt.data_ptr()
+            if hyps is not None:
+                H = BeamHyps()
+                for f, _ in BeamHyps._fields_[:-1]:
+                    t = hyps.get(f)
+                    setattr(H, f, None if t is None else t.data_ptr())
+                H.early_stopping = int(hyps.get("early_stopping", True))
+                P.beam_hyps = C.pointer(H)
+            P.workspace = self._beam_ws.data_ptr()
+            P.workspace_bytes = self._beam_ws.numel()
+            P.stream = st.value
+            check(lib.ftb200_beam_search_step(C.byref(P)))
+            self.launches += 1
+        return self._stop_criteria(outputs, inputs, B, step, lbs, ite * lbs, beam=K)
+
+    def _stop_criteria(self, outputs, inputs, B, step, lbs, lo, beam=1):
         """Stop words, length limit and should_stop (DynamicDecodeLayer.cc:447-473)."""
         sw = inputs.get("stop_words_list")
         lim = inputs.get("sequence_limit_length")
@@ -202,12 +299,13 @@ class DynamicDecodeLayer:
         check(lib.ftb200_stop_criteria(
             _ptr(outputs["output_ids"]), _ptr(outputs.get("parent_ids")),
             None if sw is None else C.c_void_p(sw.data_ptr() + lo * 2 * L * 4), L, _ptr(outputs["finished"]),
-            _ptr(lim), lo, lbs, B, 1, step, _ptr(self._count_dev), C.c_void_p(self._count_host.data_ptr()), st))
+            _ptr(lim), lo * beam, lbs, B, beam, step, _ptr(self._count_dev),
+            C.c_void_p(self._count_host.data_ptr()), st))
         self.launches += 1
         if lim is None:
             return False
         stop = C.c_int(0)
-        check(lib.ftb200_wait_should_stop(C.c_void_p(self._count_host.data_ptr()), B, 1, st, 10000, C.byref(stop)))
+        check(lib.ftb200_wait_should_stop(C.c_void_p(self._count_host.data_ptr()), B, beam, st, 10000, C.byref(stop)))
         return bool(stop.value)
 
     def _sample(self, outputs, inputs, logits, B, step, ite, lbs, mil, lo, hi, topk_on, topp_on):

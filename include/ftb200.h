@@ -220,6 +220,69 @@ int ftb200_wait_should_stop(const int* finished_count_host, int batch_size, int 
 size_t ftb200_static_scratch_bytes(void);
 int    ftb200_decode_step_sampling_static(const ftb200_sampling_params* p);
 
+/* ------------------------------------------------------------------------------------------
+ * Beam search, one step (beam_width > 1), one launch.
+ *
+ * Replaces what OnlineBeamSearchLayer<T>::forward launches
+ * (layers/beam_search_layers/BaseBeamSearchLayer.cu:181-289, OnlineBeamSearchLayer.cu:88-175):
+ *   invokeAddBiasApplyPenalties   kernels/beam_search_penalty_kernels.cu:175-267
+ *   invokeTopkSoftMax             kernels/online_softmax_beamsearch_kernels.cu:549-699
+ *                                 (stage-1 / stage-2 online soft-max + top-2K, batch_topk_kernel)
+ *   invokeUpdate                  layers/beam_search_layers/OnlineBeamSearchLayer.cu:24-86
+ *   update_indir_cache_kernelLauncher   layers/beam_search_layers/BaseBeamSearchLayer.cu:23-79
+ * Temperature, penalty, min_length, diversity and length penalty are scalars per call, as in the
+ * reference (DynamicDecodeLayer.cc:286-386 loops over sub-batches when they differ per row).
+ * The logits are read, never written.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Mirrors BeamHypotheses, kernels/beam_search_topk_kernels.h:31-58 (device pointers; num_beams == null
+ * switches the archive of finished beams off). */
+typedef struct ftb200_beam_hyps {
+    int*     output_ids_tgt;       /* [batch, 2K, max_seq_len] */
+    int*     sequence_lengths_tgt; /* [batch, 2K] */
+    float*   cum_log_probs;        /* [batch, 2K] */
+    float*   normed_scores;        /* [batch, 2K] */
+    float*   log_probs;            /* [batch, 2K, max_seq_len] or null */
+    float*   min_normed_scores;    /* [batch] */
+    int*     num_beams;            /* [batch] or null */
+    uint8_t* is_done;              /* [batch] */
+    int      early_stopping;
+} ftb200_beam_hyps;
+
+typedef struct ftb200_beam_params {
+    int dtype, batch_size, local_batch_size, ite, beam_width;
+    int vocab_size, vocab_size_padded, step, max_input_length, max_seq_len;
+
+    const void* logits;         /* [local_batch_size, beam_width, vocab_size_padded] */
+    const void* embedding_bias; /* [vocab_size_padded] or null */
+    const int*  end_ids;        /* [local_batch_size] */
+    const int*  input_lengths;  /* [local_batch_size * beam_width] or null */
+
+    float temperature;
+    float repetition_penalty;
+    int   penalty_type;         /* ftb200_penalty_type */
+    int   min_length;
+    float diversity_rate;
+    float length_penalty;
+
+    int*     output_ids;        /* [max_seq_len, batch_size * beam_width], whole tensor */
+    int*     parent_ids;        /* [max_seq_len, batch_size * beam_width], whole tensor */
+    uint8_t* finished;          /* [local_batch_size * beam_width] */
+    int*     sequence_length;   /* [local_batch_size * beam_width] */
+    float*   cum_log_probs;     /* [local_batch_size * beam_width] */
+    float*   output_log_probs;  /* [max_seq_len, batch_size * beam_width] whole tensor, or null */
+    const int* src_cache_indirection; /* [local_batch_size, beam_width, max_seq_len] or null */
+    int*       tgt_cache_indirection; /* same shape, or null */
+    const ftb200_beam_hyps* beam_hyps; /* host pointer to the struct above, or null */
+
+    void*  workspace;
+    size_t workspace_bytes;
+    void*  stream;
+} ftb200_beam_params;
+
+int ftb200_beam_workspace_bytes(int local_batch_size, int beam_width, size_t* bytes);
+int ftb200_beam_search_step(const ftb200_beam_params* p);
+
 #ifdef __cplusplus
 }
 #endif

@@ -615,3 +615,299 @@ int oracle_length_criterion(uint8_t* finished, const uint32_t* sequence_limit_le
 }
 
 }  // extern "C"
+
+// ================================================================================================
+// Beam search step (beam_width > 1): OnlineBeamSearchLayer<T>::forward restated.
+// ================================================================================================
+namespace {
+
+struct MDc {
+    float m, d;
+};
+// reduce_md_op, kernels/online_softmax_beamsearch_kernels.cu:270-279
+MDc md_op(MDc a, MDc b)
+{
+    bool a_bigger = a.m > b.m;
+    MDc  hi = a_bigger ? a : b, lo = a_bigger ? b : a, r;
+    r.d = hi.d + lo.d * expf(lo.m - hi.m);
+    r.m = hi.m;
+    return r;
+}
+// cub::BlockReduce (warp-shuffle reductions): inside a warp lane l takes op(own, lane l+off) for
+// off = 1,2,4,8,16 while l+off stays inside the warp; warp results are folded left to right.
+MDc block_reduce_md(std::vector<MDc> v)
+{
+    const int n = (int)v.size();
+    std::vector<MDc> warp;
+    for (int w0 = 0; w0 < n; w0 += 32) {
+        MDc x[32];
+        int cnt = std::min(32, n - w0);
+        for (int l = 0; l < 32; ++l) {
+            x[l] = l < cnt ? v[w0 + l] : MDc{0, 0};
+        }
+        for (int off = 1; off < 32; off <<= 1) {
+            MDc t[32];
+            for (int l = 0; l < 32; ++l) {
+                t[l] = (l + off <= cnt - 1) ? md_op(x[l], x[l + off]) : x[l];
+            }
+            std::memcpy(x, t, sizeof(x));
+        }
+        warp.push_back(x[0]);
+    }
+    MDc r = warp[0];
+    for (size_t w = 1; w < warp.size(); ++w) {
+        r = md_op(r, warp[w]);
+    }
+    return r;
+}
+
+}  // namespace
+
+extern "C" int oracle_beam_search_step(const ftb200_beam_params* p)
+{
+    const int     K = p->beam_width, V = p->vocab_size_padded, twoK = 2 * K, LB = p->local_batch_size;
+    const TypeOps T{p->dtype == FTB200_F16};
+    const RowView L{p->dtype, p->logits, (size_t)V};
+    RowView       biasv{p->dtype, p->embedding_bias, (size_t)V};
+    const bool    apply_temp = p->embedding_bias || p->temperature != 1.0f || p->vocab_size != V;
+    const int     bbsize = p->batch_size * K;
+    const int     rows = LB * K;
+    const int     launcher_maxk = K <= 4 ? 4 : K <= 8 ? 8 : K <= 16 ? 16 : K <= 32 ? 32 : 64;
+    const int     block_sz = launcher_maxk < 16 ? (launcher_maxk < 8 ? 256 : 128) : 64;
+    int           voc_parts = 4;
+    if (rows < 256) {
+        voc_parts = std::min(128, (240 + rows - 1) / rows);
+    }
+    std::vector<int>   cand_id((size_t)rows * twoK);
+    std::vector<float> cand_val((size_t)rows * twoK);
+    const std::vector<uint8_t> fin0(p->finished, p->finished + rows);
+    const std::vector<int>     seq0(p->sequence_length, p->sequence_length + rows);
+
+    for (int bb = 0; bb < rows; ++bb) {
+        const int b = bb / K, end_id = p->end_ids[b];
+        std::vector<float> x(V);
+        for (int v = 0; v < V; ++v) {
+            x[v] = L.get(bb, v);
+        }
+        // invokeAddBiasApplyPenalties, kernels/beam_search_penalty_kernels.cu:175-267
+        if (apply_temp) {
+            const float inv = 1.0f / (p->temperature + 1e-6f);
+            for (int v = 0; v < V; ++v) {
+                if (v < p->vocab_size) {
+                    float bv = p->embedding_bias ? biasv.get(0, v) : 0.0f;
+                    x[v]     = T.is_half ? round_half(round_half(x[v] + bv) * round_half(inv)) : (x[v] + bv) * inv;
+                }
+                else {
+                    x[v] = -T.max_t();
+                }
+            }
+        }
+        if (p->penalty_type != FTB200_PENALTY_NONE && p->step > 0
+            && p->repetition_penalty != (p->penalty_type == FTB200_PENALTY_MULTIPLICATIVE ? 1.0f : 0.0f)) {
+            const int   input_len = p->input_lengths ? p->input_lengths[bb] : p->max_input_length;
+            const float pen       = T.rnd(p->repetition_penalty);
+            std::vector<std::pair<int, float>> upd;
+            auto add = [&](int id) {
+                float lg = x[id];
+                float nv = p->penalty_type == FTB200_PENALTY_ADDITIVE ? lg - pen : (lg > 0.0f ? lg / pen : lg * pen);
+                upd.push_back({id, T.rnd(nv)});
+            };
+            const int* cur     = p->output_ids + (size_t)(p->step - 1) * bbsize + (size_t)p->ite * LB * K;
+            const int* parents = p->parent_ids + (size_t)p->ite * K * LB;
+            add(cur[bb]);
+            int parent_beam = bb % K;
+            for (int i = p->step - 2; i >= 0; --i) {
+                if (i >= input_len && i < p->max_input_length) {
+                    continue;
+                }
+                parent_beam = parents[(size_t)i * bbsize + b * K + parent_beam];
+                add(p->output_ids[(size_t)i * bbsize + b * K + parent_beam]);
+            }
+            for (auto& u : upd) {
+                x[u.first] = u.second;
+            }
+        }
+        if (p->step - p->max_input_length < p->min_length
+            && p->sequence_length[bb] + 1 - p->max_input_length < p->min_length) {
+            x[end_id] = -T.max_t();
+        }
+        // stage 1 + stage 2, kernels/online_softmax_beamsearch_kernels.cu:366-514
+        const bool fin = p->finished[bb];
+        if (fin) {
+            for (int v = 0; v < V; ++v) {
+                x[v] = v == end_id ? T.max_t() : -T.max_t();
+            }
+        }
+        const int        v_local = (V + voc_parts - 1) / voc_parts;
+        std::vector<MDc> parts;
+        for (int part = 0; part < voc_parts; ++part) {
+            const int s0 = v_local * part, s1 = std::min(V, s0 + v_local);
+            std::vector<MDc> thr(block_sz, MDc{-T.max_t(), 0.0f});
+            for (int t = 0; t < block_sz; ++t) {
+                for (int v = s0 + t; v < s1; v += block_sz) {
+                    thr[t] = md_op(thr[t], MDc{x[v], 1.0f});
+                }
+            }
+            parts.push_back(block_reduce_md(thr));
+        }
+        const int stage2_threads = voc_parts <= 32 ? 32 : voc_parts <= 64 ? 64 : 128;
+        std::vector<MDc> st2(stage2_threads, MDc{-T.max_t(), 0.0f});
+        for (int i = 0; i < voc_parts; ++i) {
+            st2[i] = parts[i];
+        }
+        const MDc total = block_reduce_md(st2);
+        std::vector<int> order(V);
+        for (int v = 0; v < V; ++v) {
+            order[v] = v;
+        }
+        std::partial_sort(order.begin(), order.begin() + std::min(twoK, V), order.end(), [&](int a, int c) {
+            return x[a] != x[c] ? x[a] > x[c] : a < c;
+        });
+        const float d_total_log = logf(total.d);
+        for (int i = 0; i < twoK; ++i) {
+            const int v                      = i < V ? order[i] : -1;
+            cand_id[(size_t)bb * twoK + i]  = v < 0 ? -1 : bb * V + v;
+            cand_val[(size_t)bb * twoK + i] = v < 0 ? -INFINITY : T.rnd(x[v] - total.m - d_total_log + p->cum_log_probs[bb]);
+        }
+    }
+
+    // batch_topk_kernel, :99-262
+    const ftb200_beam_hyps* H = (p->beam_hyps && p->beam_hyps->num_beams) ? p->beam_hyps : nullptr;
+    const int top_n = twoK <= 8 ? 8 : twoK <= 16 ? 16 : twoK <= 32 ? 32 : twoK <= 64 ? 64 : 128;
+    for (int b = 0; b < LB; ++b) {
+        const int    ncand = K * twoK, gbi = p->ite * LB + b, end_id = p->end_ids[b];
+        const int*   x     = &cand_id[(size_t)b * ncand];
+        const float* y     = &cand_val[(size_t)b * ncand];
+        int*   z     = p->output_ids + (size_t)p->step * bbsize + (size_t)p->ite * LB * K + b * K;
+        int*   par   = p->parent_ids + (size_t)p->step * bbsize + (size_t)p->ite * LB * K + b * K;
+        float* v_cum = p->cum_log_probs + b * K;
+        float* olp   = p->output_log_probs ? p->output_log_probs + (size_t)p->step * bbsize + (size_t)p->ite * LB * K : nullptr;
+        std::vector<float> old_cum(v_cum, v_cum + K);
+        bool skip = false;
+        if (H) {
+            if (H->num_beams[gbi] == 0) {
+                H->min_normed_scores[gbi] = FLT_MAX;
+            }
+            else if (H->num_beams[gbi] == K) {
+                skip = true;
+            }
+        }
+        if (!skip) {
+            const int len = fin0[b] ? seq0[b] : seq0[b] + 1;
+            std::vector<float> e(ncand);
+            std::vector<int>   ord;
+            for (int i = 0; i < ncand; ++i) {
+                float s = y[i];
+                if (p->length_penalty != 0.0f && len != 1) {
+                    s = T.rnd(s / T.rnd(powf((float)len, p->length_penalty)));
+                }
+                e[i] = T.rnd(s + T.rnd(T.rnd(p->diversity_rate) * T.rnd((float)(i % K))));
+                if (x[i] >= 0) {
+                    ord.push_back(i);
+                }
+            }
+            std::sort(ord.begin(), ord.end(), [&](int a, int c) { return e[a] != e[c] ? e[a] > e[c] : a < c; });
+            int selected = 0;
+            for (int i = 0; i < top_n && i < (int)ord.size(); ++i) {
+                const int   ci = ord[i], word = x[ci];
+                const float normed = e[ci];
+                if (H && word % V == end_id) {
+                    if (i < K) {
+                        const int num_beam = H->num_beams[gbi];
+                        int       beam_idx = num_beam;
+                        if (num_beam == K) {
+                            if (normed < H->min_normed_scores[gbi]) {
+                                break;
+                            }
+                            for (int j = 0; j < K; ++j) {
+                                if (H->normed_scores[gbi * twoK + j] == H->min_normed_scores[gbi]) {
+                                    beam_idx = j;
+                                    H->num_beams[gbi]--;
+                                    H->min_normed_scores[gbi]        = FLT_MAX;
+                                    H->normed_scores[gbi * twoK + j] = normed;
+                                    for (int l = 0; l < K; ++l) {
+                                        H->min_normed_scores[gbi] = std::min(H->min_normed_scores[gbi], H->normed_scores[gbi * twoK + l]);
+                                    }
+                                    break;
+                                }
+                            }
+                        }
+                        const size_t tgt = ((size_t)gbi * twoK + beam_idx) * p->max_seq_len;
+                        H->output_ids_tgt[tgt + p->step] = end_id;
+                        if (H->log_probs) {
+                            H->log_probs[tgt + p->step] = y[ci] - old_cum[(word / V) % K];
+                        }
+                        int prev_id = (word / V) % K;
+                        for (int j = p->step - 1; j >= 0; --j) {
+                            const size_t src = (size_t)j * bbsize + (size_t)p->ite * LB * K + b * K + prev_id;
+                            H->output_ids_tgt[tgt + j] = p->output_ids[src];
+                            if (H->log_probs && p->output_log_probs) {
+                                H->log_probs[tgt + j] = p->output_log_probs[src];
+                            }
+                            prev_id = p->parent_ids[src];
+                        }
+                        const int tb                = gbi * twoK + beam_idx;
+                        H->sequence_lengths_tgt[tb] = p->step;
+                        H->normed_scores[tb]        = normed;
+                        H->min_normed_scores[gbi]   = std::min(H->min_normed_scores[gbi], normed);
+                        H->num_beams[gbi]++;
+                        H->cum_log_probs[tb] = y[ci];
+                    }
+                }
+                else if ((H && i < twoK) || (!H && i < K)) {
+                    z[selected] = word;
+                    if (olp) {
+                        olp[b * K + selected] = y[ci] - old_cum[(word / V) % K];
+                    }
+                    v_cum[selected] = y[ci];
+                    ++selected;
+                }
+                if (selected >= K) {
+                    break;
+                }
+            }
+            if (H) {
+                if (H->num_beams[b] < K) {
+                    H->is_done[b] = 0;
+                }
+                else if (H->early_stopping) {
+                    H->is_done[b] = 1;
+                }
+            }
+        }
+        // update_kernel, layers/beam_search_layers/OnlineBeamSearchLayer.cu:24-58
+        std::vector<int> newseq(K);
+        for (int k = 0; k < K; ++k) {
+            const int idx = b * K + k;
+            newseq[k]     = p->finished[idx] ? p->sequence_length[idx] : p->sequence_length[idx] + 1;
+        }
+        for (int k = 0; k < K; ++k) {
+            const int idx = b * K + k, word = z[k], beam_id = (word / V) % K, word_id = word % V;
+            p->sequence_length[idx] = newseq[beam_id];
+            p->finished[idx]        = word_id == end_id;
+            par[k]                  = beam_id;
+            z[k]                    = word_id;
+        }
+        if (H && H->num_beams[gbi] == K) {
+            for (int k = 0; k < K; ++k) {
+                p->finished[b * K + k] = 1;
+            }
+        }
+        // update_indir_cache_kernel, layers/beam_search_layers/BaseBeamSearchLayer.cu:23-50
+        if (p->tgt_cache_indirection && p->src_cache_indirection) {
+            const int Lq = p->max_seq_len, start = std::max(0, p->step + 1 - Lq), num = std::min(p->step + 1, Lq);
+            for (int k = 0; k < K; ++k) {
+                if (p->finished[b * K + k]) {
+                    continue;
+                }
+                for (int t = start; t < start + num; ++t) {
+                    const int    tc   = t % Lq;
+                    const size_t base = (size_t)b * K * Lq;
+                    p->tgt_cache_indirection[base + (size_t)k * Lq + tc] =
+                        t == p->step ? k : p->src_cache_indirection[base + (size_t)par[k] * Lq + tc];
+                }
+            }
+        }
+    }
+    return 0;
+}

@@ -1,0 +1,91 @@
+"""GPU parity of the one-launch beam-search step against the unmodified reference
+(OnlineBeamSearchLayer through DynamicDecodeLayer, compiled for sm_100a) and the CPU restatement.
+ids, parents, finished, lengths and the cache indirection must be identical; cum_log_probs within 1e-3
+(the soft-max denominator is summed in a different order)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import ft_reference
+
+pytestmark = pytest.mark.gpu
+
+
+def make_state(B, K, V, L, mil, dtype, device, seed):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    st = {
+        "output_ids": torch.zeros(L, B, K, dtype=torch.int32, device=device),
+        "parent_ids": torch.zeros(L, B, K, dtype=torch.int32, device=device),
+        "finished": torch.zeros(B * K, dtype=torch.bool, device=device),
+        "sequence_length": torch.full((B * K,), mil, dtype=torch.int32, device=device),
+        "cum_log_probs": (torch.randn(B * K, generator=g, device=device) - 5.0).float(),
+        "tgt_cache_indirection": torch.zeros(B, K, L, dtype=torch.int32, device=device),
+    }
+    st["output_ids"][:mil] = torch.randint(3, V, (mil, B, 1), generator=g, device=device, dtype=torch.int32)
+    return st
+
+
+def run_beam(layer, is_ref, B, K, V, L, mil, steps, dtype, device, args, seed, end_id=2):
+    st = make_state(B, K, V, L, mil, dtype, device, seed)
+    src = torch.zeros(B, K, L, dtype=torch.int32, device=device)
+    layer.setup(B, K, args)
+    rec = []
+    g = torch.Generator(device=device)
+    for s in range(steps):
+        step = mil + s
+        g.manual_seed(seed * 7919 + step)
+        logits = (torch.randn(B, K, V, generator=g, device=device) * 2.0).to(dtype)
+        if s >= 2:
+            logits[::3, :, end_id] += 9.0     # make some beams finish
+        inp = dict(args)
+        inp.update({"logits": logits.clone(), "step": step, "max_input_length": mil, "ite": 0, "local_batch_size": B,
+                    "end_id": torch.full((B,), end_id, dtype=torch.int32, device=device),
+                    "input_lengths": torch.full((B, K), mil, dtype=torch.int32, device=device),
+                    "src_cache_indirection": src})
+        layer.forward(st, inp)
+        torch.cuda.synchronize()
+        src, st["tgt_cache_indirection"] = st["tgt_cache_indirection"], src
+        rec.append({k: v.clone().cpu().numpy() for k, v in st.items()})
+    return rec
+
+
+@pytest.mark.parametrize("B,K,V,dtype", [(8, 4, 32000, torch.float16), (5, 2, 1031, torch.float32),
+                                         (3, 3, 4096, torch.float32), (2, 8, 5000, torch.float16)])
+@pytest.mark.parametrize("args", [dict(), dict(len_penalty=np.asarray([1.0], np.float32)),
+                                  dict(temperature=np.asarray([0.8], np.float32),
+                                       repetition_penalty=np.asarray([1.3], np.float32),
+                                       min_length=np.asarray([3], np.int32),
+                                       beam_search_diversity_rate=np.asarray([0.2], np.float32))],
+                         ids=["plain", "lenpen", "penalties"])
+def test_beam_step_against_reference(B, K, V, dtype, args, cuda_device):
+    if not ft_reference.available():
+        pytest.skip("oracle/_ref/libft_decode_ref.so not built")
+    from fastertransformer_b200 import DynamicDecodeLayer
+    L, mil, steps = 12, 4, 6
+    ref = run_beam(ft_reference.RefDynamicDecodeLayer(V, V, dtype, cuda_device), True, B, K, V, L, mil, steps, dtype,
+                   cuda_device, args, 11)
+    mine = run_beam(DynamicDecodeLayer(V, V, dtype, cuda_device), False, B, K, V, L, mil, steps, dtype, cuda_device,
+                    args, 11)
+    for s, (a, b) in enumerate(zip(mine, ref)):
+        for key in ("output_ids", "parent_ids", "finished", "sequence_length"):
+            assert (a[key] == b[key]).all(), (s, key, np.argwhere(a[key] != b[key])[:4])
+        np.testing.assert_allclose(a["cum_log_probs"], b["cum_log_probs"], rtol=1e-3, atol=2e-3)
+
+
+def test_beam_config4_shape(cuda_device):
+    """Config 4: batch 64, beam 4, vocab 32000, fp16, length penalty 1.0, end id 2."""
+    if not ft_reference.available():
+        pytest.skip("oracle/_ref/libft_decode_ref.so not built")
+    from fastertransformer_b200 import DynamicDecodeLayer
+    B, K, V, L, mil, steps, dtype = 64, 4, 32000, 10, 2, 6, torch.float16
+    args = dict(len_penalty=np.asarray([1.0], np.float32))
+    ref = run_beam(ft_reference.RefDynamicDecodeLayer(V, V, dtype, cuda_device), True, B, K, V, L, mil, steps, dtype,
+                   cuda_device, args, 5)
+    mine = run_beam(DynamicDecodeLayer(V, V, dtype, cuda_device), False, B, K, V, L, mil, steps, dtype, cuda_device,
+                    args, 5)
+    for a, b in zip(mine, ref):
+        for key in ("output_ids", "parent_ids", "finished", "sequence_length", "tgt_cache_indirection"):
+            assert (a[key] == b[key]).all(), key
