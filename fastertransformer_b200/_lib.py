@@ -36,6 +36,8 @@ def _load():
     l.ftb200_static_scratch_bytes.restype = C.c_size_t
     l.ftb200_beam_workspace_bytes.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_size_t)]
     l.ftb200_beam_search_step.argtypes = [C.POINTER(BeamParams)]
+    l.ftb200_vocab_parallel_local.argtypes = [C.POINTER(SamplingParams), C.c_int, C.c_int, C.c_void_p]
+    l.ftb200_vocab_parallel_merge.argtypes = [C.POINTER(SamplingParams), C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     V, I = C.c_void_p, C.c_int
     l.ftb200_ban_bad_words.argtypes = [V, I, V, V, I, I, I, V, I, I, I, I, I, V]
     l.ftb200_stop_criteria.argtypes = [V, V, V, I, V, V, I, I, I, I, I, V, V, V]

@@ -4,4 +4,5 @@
 namespace ftb200 {
 template int sampling_occupancy<FTB200_BF16>(size_t, int*);
 template int sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
+template int vp_merge_launch<FTB200_BF16>(const KParams&, const u64*, int, int*, int, cudaStream_t);
 }  // namespace ftb200

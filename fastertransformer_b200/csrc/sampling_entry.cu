@@ -13,6 +13,11 @@ extern template int sampling_occupancy<FTB200_BF16>(size_t, int*);
 extern template int sampling_launch<FTB200_F32>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
+template<int DT>
+int vp_merge_launch(const KParams& K, const u64* gathered, int nranks, int* overflow, int grid, cudaStream_t st);
+extern template int vp_merge_launch<FTB200_F32>(const KParams&, const u64*, int, int*, int, cudaStream_t);
+extern template int vp_merge_launch<FTB200_F16>(const KParams&, const u64*, int, int*, int, cudaStream_t);
+extern template int vp_merge_launch<FTB200_BF16>(const KParams&, const u64*, int, int*, int, cudaStream_t);
 
 static int sm_count()
 {
@@ -28,7 +33,7 @@ static int sm_count()
     return n;
 }
 
-constexpr int kMaxCtasPerSm = 4;
+constexpr int kMaxCtasPerSm = 2;
 
 static size_t scratch_stride_for(int vocab_padded)
 {
@@ -53,9 +58,10 @@ extern "C" int ftb200_sampling_workspace_bytes(int dtype, int local_batch_size, 
     return FTB200_OK;
 }
 
-extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
+// Argument checks, translation to the kernel argument block, shared-memory plan and grid size, shared by
+// the entry points below.  `need_workspace` is false for the vocabulary-parallel merge.
+static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& smem, int& grid, bool need_workspace)
 {
-    reset_launch_count();
     if (p == nullptr || p->logits == nullptr || p->end_ids == nullptr || p->output_ids == nullptr) {
         set_error("ftb200_decode_step_sampling: null logits / end_ids / output_ids");
         return FTB200_INVALID_ARG;
@@ -92,17 +98,16 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
         set_error("ftb200_decode_step_sampling: a penalty is switched on without its per-row array");
         return FTB200_INVALID_ARG;
     }
-    if (p->local_batch_size == 0) {
-        return FTB200_OK;
-    }
     size_t need = 0;
     ftb200_sampling_workspace_bytes(p->dtype, p->local_batch_size, p->vocab_size_padded, &need);
-    if (p->workspace == nullptr || p->workspace_bytes < need) {
+    if (need_workspace && (p->workspace == nullptr || p->workspace_bytes < need)) {
         set_error("ftb200_decode_step_sampling: workspace too small, need " + std::to_string(need) + " bytes");
         return FTB200_WORKSPACE_SMALL;
     }
 
-    KParams K;
+    K.vp_out       = nullptr;
+    K.vp_cap       = 0;
+    K.vocab_offset = 0;
     K.dtype            = p->dtype;
     K.batch_size       = p->batch_size;
     K.local_batch      = p->local_batch_size;
@@ -158,7 +163,7 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
         ++lg;
     }
     K.hash_shift = 32 - lg;
-    size_t smem  = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 4
+    smem         = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 4
                    + (size_t)(slots / 2) * 4 + 32 + (size_t)kThreads * 16 * 2;
     if (smem > 200 * 1024) {
         set_error("ftb200_decode_step_sampling: token history too long for the shared-memory hash");
@@ -181,20 +186,107 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
     if (per_sm > kMaxCtasPerSm) {
         per_sm = kMaxCtasPerSm;
     }
-    int grid = sm_count() * per_sm;
+    grid = sm_count() * per_sm;
     if (grid > p->local_batch_size) {
         grid = p->local_batch_size;
     }
     K.ticket         = (u32*)p->workspace;
     K.scratch        = (u64*)((char*)p->workspace + 256);
     K.scratch_stride = scratch_stride_for(p->vocab_size_padded);
+    return FTB200_OK;
+}
 
+extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
+{
+    reset_launch_count();
+    KParams K;
+    size_t  smem = 0;
+    int     grid = 0;
+    int     rc   = plan_sampling(p, K, smem, grid, true);
+    if (rc != FTB200_OK) {
+        return rc;
+    }
+    if (p->local_batch_size == 0) {
+        return FTB200_OK;
+    }
     cudaStream_t st = (cudaStream_t)p->stream;
     FTB_CUDA_CHECK(cudaMemsetAsync(K.ticket, 0, 256, st));
     switch (p->dtype) {
         case FTB200_F32: rc = sampling_launch<FTB200_F32>(K, grid, smem, st); break;
         case FTB200_F16: rc = sampling_launch<FTB200_F16>(K, grid, smem, st); break;
         default: rc = sampling_launch<FTB200_BF16>(K, grid, smem, st); break;
+    }
+    if (rc == FTB200_OK) {
+        note_launch(1);
+    }
+    return rc;
+}
+
+// ---- vocabulary-parallel sampling (the logits of a row are split over several GPUs by column) ------
+extern "C" int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int vocab_offset, int cap,
+                                           uint64_t* records)
+{
+    reset_launch_count();
+    if (records == nullptr || cap < 1 || cap > kCap || vocab_offset < 0) {
+        set_error("ftb200_vocab_parallel_local: invalid argument");
+        return FTB200_INVALID_ARG;
+    }
+    if (p != nullptr && (p->topk_states == nullptr || p->topp_states != nullptr || p->cum_log_probs != nullptr
+                         || p->output_log_probs != nullptr)) {
+        set_error("ftb200_vocab_parallel_local: only top-k rows without log-probs are exchanged as candidates");
+        return FTB200_UNSUPPORTED;
+    }
+    KParams K;
+    size_t  smem = 0;
+    int     grid = 0;
+    int     rc   = plan_sampling(p, K, smem, grid, true);
+    if (rc != FTB200_OK) {
+        return rc;
+    }
+    if (p->local_batch_size == 0) {
+        return FTB200_OK;
+    }
+    K.vp_out       = (u64*)records;
+    K.vp_cap       = cap;
+    K.vocab_offset = vocab_offset;
+    cudaStream_t st = (cudaStream_t)p->stream;
+    FTB_CUDA_CHECK(cudaMemsetAsync(K.ticket, 0, 256, st));
+    switch (p->dtype) {
+        case FTB200_F32: rc = sampling_launch<FTB200_F32>(K, grid, smem, st); break;
+        case FTB200_F16: rc = sampling_launch<FTB200_F16>(K, grid, smem, st); break;
+        default: rc = sampling_launch<FTB200_BF16>(K, grid, smem, st); break;
+    }
+    if (rc == FTB200_OK) {
+        note_launch(1);
+    }
+    return rc;
+}
+
+extern "C" int ftb200_vocab_parallel_merge(const ftb200_sampling_params* p, const uint64_t* gathered, int n_ranks,
+                                           int cap, int* overflow_count)
+{
+    reset_launch_count();
+    if (gathered == nullptr || overflow_count == nullptr || n_ranks < 1 || cap < 1 || cap > kCap) {
+        set_error("ftb200_vocab_parallel_merge: invalid argument");
+        return FTB200_INVALID_ARG;
+    }
+    KParams K;
+    size_t  smem = 0;
+    int     grid = 0;
+    int     rc   = plan_sampling(p, K, smem, grid, false);
+    if (rc != FTB200_OK) {
+        return rc;
+    }
+    if (p->local_batch_size == 0) {
+        return FTB200_OK;
+    }
+    K.vp_cap        = cap;
+    cudaStream_t st = (cudaStream_t)p->stream;
+    grid            = sm_count() * 2 < p->local_batch_size ? sm_count() * 2 : p->local_batch_size;
+    switch (p->dtype) {
+        case FTB200_F32: rc = vp_merge_launch<FTB200_F32>(K, (const u64*)gathered, n_ranks, overflow_count, grid, st); break;
+        case FTB200_F16: rc = vp_merge_launch<FTB200_F16>(K, (const u64*)gathered, n_ranks, overflow_count, grid, st); break;
+        default: rc = vp_merge_launch<FTB200_BF16>(K, (const u64*)gathered, n_ranks, overflow_count, grid, st); break;
     }
     if (rc == FTB200_OK) {
         note_launch(1);

@@ -50,6 +50,7 @@ __device__ __forceinline__ u32 hash_slot(int id, int shift)
 
 static __device__ void hash_insert(const KParams& P, const Smem& S, const RowCtx& C, int id, u32 flag)
 {
+    id -= P.vocab_offset;  // token id -> column of this (shard of the) vocabulary
     if (id < 0 || id >= P.vocab_padded) {
         return;
     }
@@ -765,7 +766,7 @@ __device__ __noinline__ void build_row(const KParams& P, const Smem& S, RowCtx& 
             }
             if (ban) {
                 const int tok = base[item_end - 1];
-                if (0 < tok && tok < P.vocab_padded) {
+                if (0 < tok && (P.vp_out != nullptr || tok < P.vocab_padded)) {
                     hash_insert(P, S, C, tok, kFlagDead);
                 }
             }
@@ -1162,6 +1163,37 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
     }
     group_sort_u64(cand, n, tid, kThreads, CtaSync());
     __syncthreads();
+    if (P.vp_out != nullptr) {
+        // Vocabulary-parallel local pass: hand over every column whose value reaches this shard's k-th
+        // value, whole tie class included.  The global k-th value cannot be smaller than a shard's, so
+        // the union over the shards holds every column the global selection and its tie order can touch.
+        __shared__ int s_m;
+        const int      k_eff = k < n ? k : n;
+        if (tid == 0) {
+            s_m = k_eff;
+        }
+        __syncthreads();
+        if (k_eff > 0) {
+            const u32 kv = (u32)(cand[k_eff - 1] >> 32);
+            for (int i = k_eff + tid; i < n; i += kThreads) {
+                if ((u32)(cand[i] >> 32) == kv) {
+                    atomicMax(&s_m, i + 1);
+                }
+            }
+        }
+        __syncthreads();
+        const int m   = s_m;
+        u64*      out = P.vp_out + (size_t)O.r * (P.vp_cap + 1);
+        if (tid == 0) {
+            out[0] = m > P.vp_cap ? ~0ull : (u64)m;  // ~0: more ties than the exchange record holds
+        }
+        for (int i = tid; i < m && i < P.vp_cap; i += kThreads) {
+            const u64 e = cand[i];
+            out[1 + i]  = (e & 0xffffffff00000000ull) | (u64)((u32)(e & 0xffffffffu) + (u32)P.vocab_offset);
+        }
+        __syncthreads();
+        return;
+    }
     topk_finish(P, S, O, cand, n, k, u, top_p, true, false);
 }
 
@@ -1750,6 +1782,21 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
     const bool want_lp = P.cum_log_probs != nullptr || P.out_log_probs != nullptr;
     __syncthreads();  // every thread has read finished[r] before thread 0 may rewrite it
 
+    if (P.vp_out != nullptr) {
+        // vocabulary-parallel local pass: candidates only; the merge draws
+        if (mode == 1 && !fin) {
+            RowCtx C;
+            build_row<DT>(P, S, C, r);
+            int k = (int)P.topk_ks[r];
+            k     = k < 1 ? 1 : (k > kMaxTopK ? kMaxTopK : k);
+            row_topk<DT>(P, S, C, O, gscratch, k, 0.0f, 1.0f);
+        }
+        else if (tid == 0) {
+            P.vp_out[(size_t)r * (P.vp_cap + 1)] = 0;
+        }
+        __syncthreads();
+        return;
+    }
     if (mode == 1 && fin) {
         // sampling_topk_kernels.cu:249-252: end id, no draw, length unchanged
         if (tid == 0) {
@@ -1854,6 +1901,94 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
     }
 }
 
+
+// Vocabulary-parallel merge: one CTA per row.  `gathered` holds, rank after rank, the records the local
+// passes emitted ([rank][row][1 + cap]: count, then (~key(value) << 32 | global column) entries).  The
+// union is sorted and handed to the same draw and tie-order code as the single-GPU path, so every rank
+// arrives at the id the reference would sample from the full row.
+template<int DT>
+__global__ void __launch_bounds__(kThreads, 2)
+vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nranks, int* overflow)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ float                              s_u;
+    __shared__ u32                                s_n;
+    Smem                                          S;
+    S.cand  = (u64*)smem_raw;
+    S.hist  = (u32*)(S.cand + kCap);
+    S.val2  = (float*)(S.hist + kNB);
+    S.flags = nullptr, S.hash = nullptr, S.spec = nullptr, S.nspec = nullptr, S.hitq = nullptr, S.nhit = nullptr;
+    const int tid = threadIdx.x;
+    for (int r = blockIdx.x; r < P.local_batch; r += gridDim.x) {
+        __syncthreads();
+        if (P.topk_skip != nullptr && P.topk_skip[r]) {
+            continue;
+        }
+        RowOut O;
+        O.r      = r;
+        O.end_id = P.end_ids[r];
+        O.id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
+        const bool fin = P.finished != nullptr ? P.finished[r] != 0 : false;
+        __syncthreads();
+        if (fin) {
+            if (tid == 0) {
+                *O.id_out = O.end_id;
+            }
+            continue;
+        }
+        if (tid == 0) {
+            s_u = draw_uniform(P.topk_states, r);
+            s_n = 0;
+        }
+        __syncthreads();
+        bool bad = false;
+        for (int q = 0; q < nranks; ++q) {
+            const u64* rec = gathered + ((size_t)q * P.local_batch + r) * (P.vp_cap + 1);
+            const u64  c   = rec[0];
+            if (c == ~0ull) {
+                bad = true;
+                continue;
+            }
+            const u32 base = s_n;
+            __syncthreads();
+            if (base + (u32)c > (u32)kCap) {
+                bad = true;
+            }
+            else {
+                for (u32 i = tid; i < (u32)c; i += kThreads) {
+                    S.cand[base + i] = rec[1 + i];
+                }
+                if (tid == 0) {
+                    s_n = base + (u32)c;
+                }
+            }
+            __syncthreads();
+        }
+        if (bad) {
+            if (tid == 0) {
+                atomicAdd(overflow, 1);
+                *O.id_out = -1;
+            }
+            continue;
+        }
+        const int n = (int)s_n;
+        group_sort_u64(S.cand, n, tid, kThreads, CtaSync());
+        __syncthreads();
+        int k = (int)P.topk_ks[r];
+        k     = k < 1 ? 1 : (k > kMaxTopK ? kMaxTopK : k);
+        topk_finish(P, S, O, S.cand, n, k, s_u, P.topk_ps[r], true, false);
+    }
+}
+
+template<int DT>
+int vp_merge_launch(const KParams& K, const u64* gathered, int nranks, int* overflow, int grid, cudaStream_t st)
+{
+    const size_t smem = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4;
+    FTB_CUDA_CHECK(cudaFuncSetAttribute(vp_merge_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    vp_merge_kernel<DT><<<grid, kThreads, smem, st>>>(K, gathered, nranks, overflow);
+    FTB_CUDA_CHECK(cudaGetLastError());
+    return FTB200_OK;
+}
 
 // ---- per-dtype launch glue (instantiated once per logits type, each in its own translation unit) ----
 template<int DT>

@@ -51,6 +51,9 @@ struct KParams {
     float*   cum_log_probs;
     float*   out_log_probs;
     const int* row_order;
+    u64*     vp_out;        // vocabulary-parallel local pass: [local_batch][1 + vp_cap] records, else null
+    int      vp_cap;
+    int      vocab_offset;  // first token id of this shard of the vocabulary (0 when not sharded)
     u32*     ticket;
     u64*     scratch;         // per-CTA candidate overflow area
     size_t   scratch_stride;  // u64 entries per CTA

@@ -1,0 +1,111 @@
+"""Vocabulary-parallel top-k sampling over a column-sharded lm_head (host side).
+
+Each rank holds logits[:, rank*V/n : (rank+1)*V/n].  Instead of FasterTransformer's all-gather of the full
+fp32 logits followed by redundant sampling on every rank (models/multi_gpu_gpt/ParallelGpt.cc:1394-1435),
+each rank selects candidates on its shard, ONE all-gather exchanges a few hundred bytes per row, and every
+rank merges and draws with identical curand states - same id on every rank, equal to the single-GPU result.
+
+`VocabParallelSampler` reuses DynamicDecodeLayer for the set-up (runtime arguments, curand states).  The
+exchange goes through torch.distributed (NCCL) when a process group is given; `forward_shards` runs all
+shards on one device, which is how the single-GPU tests check the merge.
+"""
+import ctypes as C
+
+import torch
+
+from ._lib import SamplingParams, check, lib
+from .decode_layer import CURAND_STATE_BYTES, DynamicDecodeLayer, _DT
+
+
+class VocabParallelSampler(DynamicDecodeLayer):
+    def __init__(self, vocab_size, shard_size, n_shards, dtype, device, cap_extra=64, group=None):
+        super().__init__(vocab_size, shard_size * n_shards, dtype, device)
+        self.shard_size, self.n_shards, self.cap_extra, self.group = shard_size, n_shards, cap_extra, group
+        self._records = None
+        self._gathered = None
+        self._overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def _params(self, outputs, inputs, logits, vocab, vocab_padded):
+        B = logits.shape[0]
+        step, mil = int(inputs["step"]), int(inputs["max_input_length"])
+        if self.topp.active and not self.topp.skip_host.all():
+            raise RuntimeError("[FT][ERROR] vocabulary-parallel sampling handles top-k rows only")
+        P = SamplingParams()
+        P.dtype = _DT[logits.dtype]
+        P.batch_size = P.local_batch_size = B
+        P.vocab_size, P.vocab_size_padded = vocab, vocab_padded
+        P.step, P.max_input_length = step, mil
+        P.logits = logits.data_ptr()
+        P.end_ids = inputs["end_id"].data_ptr()
+        il = inputs.get("input_lengths")
+        P.input_lengths = None if il is None else il.data_ptr()
+        P.output_ids = outputs["output_ids"].data_ptr()
+        bw = inputs.get("bad_words_list")
+        if bw is not None:
+            P.bad_words, P.bad_words_len = bw.data_ptr(), bw.shape[-1]
+            P.bad_words_shared = int(bw.dim() == 2 or bw.shape[0] == 1)
+        P.temperature = self.temperature.data_ptr()
+        P.apply_temperature = int(bool((self.temperature_host != 1.0).any()))
+        P.repetition_penalty = self.penalty.data_ptr()
+        P.penalty_type = self.penalty_type
+        P.apply_repetition = int(step > 1 and self.penalty_type != 2
+                                 and bool((self.penalty_host != self.penalty_default).any()))
+        P.min_lengths = self.min_length.data_ptr()
+        P.apply_min_length = int(bool((self.min_length_host > step - mil).any()))
+        P.topk_states = self.topk.curand.data_ptr()
+        P.topk_ks, P.topk_ps = self.topk.top_ks.data_ptr(), self.topk.top_ps.data_ptr()
+        P.topk_skip, P.max_top_k = self.topk.skip.data_ptr(), self.max_top_k
+        for key, width in (("sequence_length", 4), ("finished", 1)):
+            t = outputs.get(key)
+            setattr(P, key, None if t is None else t.data_ptr())
+        need = C.c_size_t(0)
+        check(lib.ftb200_sampling_workspace_bytes(P.dtype, B, vocab_padded, C.byref(need)))
+        if self._workspace is None or self._workspace.numel() < need.value:
+            self._workspace = torch.empty(need.value, dtype=torch.uint8, device=self.device)
+        P.workspace, P.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
+        P.stream = self._stream_ptr().value
+        return P
+
+    @property
+    def cap(self):
+        return self.max_top_k + self.cap_extra
+
+    def local_pass(self, outputs, inputs, shard_logits, shard_index, records):
+        """Candidates of one shard -> records [batch, 1 + cap] (int64 view of the 64-bit words)."""
+        off = shard_index * self.shard_size
+        vocab = max(0, min(self.shard_size, self.vocab_size - off))
+        P = self._params(outputs, inputs, shard_logits, max(vocab, 1), self.shard_size)
+        check(lib.ftb200_vocab_parallel_local(C.byref(P), off, self.cap, C.c_void_p(records.data_ptr())))
+        self.launches += 1
+
+    def merge(self, outputs, inputs, gathered, logits_like):
+        P = self._params(outputs, inputs, logits_like, self.vocab_size, self.shard_size * self.n_shards)
+        check(lib.ftb200_vocab_parallel_merge(C.byref(P), C.c_void_p(gathered.data_ptr()), self.n_shards, self.cap,
+                                              C.c_void_p(self._overflow.data_ptr())))
+        self.launches += 1
+
+    def _buffers(self, B):
+        shape = (B, 1 + self.cap)
+        if self._records is None or tuple(self._records.shape) != shape:
+            self._records = torch.zeros(shape, dtype=torch.int64, device=self.device)
+            self._gathered = torch.zeros((self.n_shards,) + shape, dtype=torch.int64, device=self.device)
+        return self._records, self._gathered
+
+    def forward_rank(self, outputs, inputs, shard_logits, rank):
+        """One rank of a tensor-parallel group: local pass, one all-gather, merge."""
+        import torch.distributed as dist
+        rec, gathered = self._buffers(shard_logits.shape[0])
+        self.local_pass(outputs, inputs, shard_logits, rank, rec)
+        dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1), group=self.group)
+        self.merge(outputs, inputs, gathered, shard_logits)
+
+    def forward_shards(self, outputs, inputs, shards):
+        """All shards on this device (no communication): the arithmetic of forward_rank on every rank."""
+        rec, gathered = self._buffers(shards[0].shape[0])
+        for i, sh in enumerate(shards):
+            self.local_pass(outputs, inputs, sh, i, rec)
+            gathered[i].copy_(rec)
+        self.merge(outputs, inputs, gathered, shards[0])
+
+    def overflow_count(self):
+        return int(self._overflow.item())

@@ -283,6 +283,26 @@ typedef struct ftb200_beam_params {
 int ftb200_beam_workspace_bytes(int local_batch_size, int beam_width, size_t* bytes);
 int ftb200_beam_search_step(const ftb200_beam_params* p);
 
+/* ------------------------------------------------------------------------------------------
+ * Vocabulary-parallel top-k sampling: each GPU holds a column shard [local_batch, V/n] of the logits
+ * (the tensor-parallel lm_head before FT's all-gather, models/multi_gpu_gpt/ParallelGpt.cc:1394-1435).
+ * Instead of gathering the full fp32 logits and sampling redundantly on every rank, each rank
+ *   1. ftb200_vocab_parallel_local: runs the fused penalties + top-k selection on its shard and emits,
+ *      per row, one record of (1 + cap) 64-bit words: the count, then (value, global column) entries
+ *      for every column whose value reaches the shard's k-th value (whole tie class included);
+ *   2. exchanges the records with ONE all-gather (ncclAllGather of local_batch*(1+cap)*8 bytes);
+ *   3. ftb200_vocab_parallel_merge: merges the n records of a row and draws with the row's curand
+ *      state.  All ranks hold the same states, so all ranks produce the same id - no broadcast.
+ * The ids equal what ftb200_decode_step_sampling returns on the gathered row (and therefore the
+ * reference's).  `p` is the same argument block; in step 1 `logits`/`vocab_size`/`vocab_size_padded`
+ * describe the shard and token ids (history, bad words, end id) stay global; `vocab_offset` is the
+ * shard's first column.  Top-k rows without log-probs only.  A row with more than `cap` columns in play
+ * on some shard is reported through *overflow_count (device int, incremented) and gets id -1.
+ * ------------------------------------------------------------------------------------------ */
+int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int vocab_offset, int cap, uint64_t* records);
+int ftb200_vocab_parallel_merge(const ftb200_sampling_params* p, const uint64_t* gathered, int n_ranks, int cap,
+                                int* overflow_count);
+
 #ifdef __cplusplus
 }
 #endif
