@@ -271,6 +271,131 @@ def run_ours(a, rank, world, local):
     return line
 
 
+def run_beam(a, rank, world, local, reference=False):
+    """Config 4: beam search via online-softmax top-k. Batch 64 x beam 4 x vocab 32000 fp16, length penalty 1.0,
+    cum_log_probs ~ N(-5, 1), end id 2; the batch is the unit that shards over GPUs (weak scaling here)."""
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    B, K, V, mil = 64, 4, 32000, 4
+    steps, W = a.steps, a.warmup
+    L = mil + steps + W + 2
+    if reference:
+        import ft_reference
+        if rank != 0:
+            return None
+        if not ft_reference.available():
+            return {"impl": "reference", "unavailable": "oracle/_ref/libft_decode_ref.so is not built on this box"}
+        layer = ft_reference.RefDynamicDecodeLayer(V, V, torch.float16, device)
+    else:
+        from fastertransformer_b200 import DynamicDecodeLayer
+        layer = DynamicDecodeLayer(V, V, torch.float16, device)
+    g = torch.Generator(device=device)
+    g.manual_seed(4 + rank)
+    st = {"output_ids": torch.zeros(L, B, K, dtype=torch.int32, device=device),
+          "parent_ids": torch.zeros(L, B, K, dtype=torch.int32, device=device),
+          "finished": torch.zeros(B * K, dtype=torch.bool, device=device),
+          "sequence_length": torch.full((B * K,), mil, dtype=torch.int32, device=device),
+          "cum_log_probs": torch.randn(B * K, generator=g, device=device) - 5.0,
+          "tgt_cache_indirection": torch.zeros(B, K, L, dtype=torch.int32, device=device)}
+    src = torch.zeros(B, K, L, dtype=torch.int32, device=device)
+    args = {"len_penalty": np.asarray([1.0], np.float32)}
+    layer.setup(B, K, args)
+    pool = [(torch.randn(B, K, V, generator=g, device=device) * 2.0).half() for _ in range(4)]
+    work = torch.empty_like(pool[0])
+    end = torch.full((B,), 2, dtype=torch.int32, device=device)
+    il = torch.full((B, K), mil, dtype=torch.int32, device=device)
+    total_ms, n = 0.0, 0
+    for i in range(W + steps):
+        work.copy_(pool[i % 4])
+        inp = dict(args, logits=work, step=mil + i, max_input_length=mil, ite=0, local_batch_size=B, end_id=end,
+                   input_lengths=il, src_cache_indirection=src)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layer.forward(st, inp)
+        e1.record()
+        torch.cuda.synchronize()
+        src, st["tgt_cache_indirection"] = st["tgt_cache_indirection"], src
+        if i >= W:
+            total_ms += e0.elapsed_time(e1)
+            n += 1
+    total_ms = max_over_ranks(total_ms, world, device)
+    peak, peak_kind = measured_peak()
+    alg = B * K * V * 2.0
+    line = {"metric": "beam-search tokens/sec (config 4: batch 64 x beam 4 x vocab 32000 fp16)",
+            "value": world * B * K * n / (total_ms * 1e-3), "unit": "beam-tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": W, "ms_per_step": total_ms / n, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp16 logits, fp32 soft-max statistics", "data": "synthetic",
+            "config": {"workload": "c4: online-softmax beam top-k, batch 64 x beam 4 x vocab 32000, len_penalty 1.0"},
+            "roofline": {"bound": "hbm", "achieved": alg / (total_ms / n * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (total_ms / n * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                         "note": "16 MB per step: launch- and latency-bound, reported for completeness"}}
+    if reference:
+        line["impl"] = "reference"
+    return line
+
+
+def run_vocab_parallel(a, rank, world, local):
+    """Config 5: batch 2048, vocab 256000 as `world` column shards, bf16 N(0, 3^2), k=64, p=0.92, T=0.7.
+    Each rank reads its shard once, one NCCL all-gather moves (64+64+1)*8 bytes per row per rank, every rank
+    merges and draws.  With one GPU all shards run on it (no communication) so that the arithmetic can be timed."""
+    from fastertransformer_b200.vocab_parallel import VocabParallelSampler
+    import torch.distributed as dist
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    B, V, k, mil = 2048, 256000, 64, 4
+    n_shards = world if world > 1 else 8
+    shard = V // n_shards
+    steps, W = a.steps, a.warmup
+    args = {"runtime_top_k": np.asarray([k], np.uint32), "runtime_top_p": np.asarray([0.92], np.float32),
+            "temperature": np.asarray([0.7], np.float32), "random_seed": np.asarray([3], np.uint64)}
+    vp = VocabParallelSampler(V, shard, n_shards, torch.bfloat16, device)
+    vp.setup(B, 1, args)
+    g = torch.Generator(device=device)
+    g.manual_seed(500 + rank)
+    my_shards = [rank] if world > 1 else list(range(n_shards))
+    pool = [[(torch.randn(B, shard, generator=g, device=device) * 3.0).bfloat16() for _ in my_shards] for _ in range(2)]
+    st = {"output_ids": torch.zeros(mil + steps + W + 1, B, dtype=torch.int32, device=device),
+          "finished": torch.zeros(B, dtype=torch.bool, device=device),
+          "sequence_length": torch.full((B,), mil, dtype=torch.int32, device=device)}
+    end = torch.full((B,), V - 1, dtype=torch.int32, device=device)
+    for i in range(W):
+        inp = {"step": mil + i, "max_input_length": mil, "end_id": end}
+        vp.forward_rank(st, inp, pool[i % 2][0], rank) if world > 1 else vp.forward_shards(st, inp, pool[i % 2])
+    torch.cuda.synchronize()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(W, W + steps):
+        inp = {"step": mil + i, "max_input_length": mil, "end_id": end}
+        vp.forward_rank(st, inp, pool[i % 2][0], rank) if world > 1 else vp.forward_shards(st, inp, pool[i % 2])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1), world, device)
+    if world > 1:
+        ids = st["output_ids"][mil + W].clone()
+        ref = ids.clone()
+        dist.broadcast(ref, 0)
+        same = int(torch.equal(ids, ref))
+        t = torch.tensor([same], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        same = int(t.item())
+    else:
+        same = 1
+    peak, peak_kind = measured_peak()
+    alg = B * shard * 2.0 * (1 if world > 1 else n_shards)
+    return {"metric": "vocabulary-parallel sampled tokens/sec (config 5: batch 2048, vocab 256000)",
+            "value": B * steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": W,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 logits", "data": "synthetic",
+            "config": {"workload": "c5: vocab 256000 in %d shards of %d, batch 2048, k=64, p=0.92, T=0.7" % (n_shards, shard),
+                       "allgather_bytes_per_rank": B * (1 + vp.cap) * 8, "ids_identical_on_all_ranks": bool(same),
+                       "overflow_rows": vp.overflow_count()},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms / steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind},
+            "gpu_launches": vp.launches}
+
+
 def run_reference(a, rank, world, local):
     import ft_reference
     from fastertransformer_b200.workloads import make_workload
@@ -331,6 +456,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--workload", default="c3", choices=["c3", "c4", "c5"],
+                    help="c3 (default, the headline) | c4 beam search | c5 vocabulary-parallel")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the fused kernel from an ncu capture (profiles/)")
@@ -344,7 +471,11 @@ def main():
             except Exception:
                 a.traffic = None
     rank, world, local = dist_setup(a.gpus)
-    if a.impl == "reference":
+    if a.workload == "c4":
+        line = run_beam(a, rank, world, local, reference=a.impl == "reference")
+    elif a.workload == "c5":
+        line = run_vocab_parallel(a, rank, world, local)
+    elif a.impl == "reference":
         line = run_reference(a, rank, world, local)
     else:
         line = run_ours(a, rank, world, local)
