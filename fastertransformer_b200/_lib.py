@@ -34,6 +34,7 @@ def _load():
     l.ftb200_decode_step_sampling.argtypes = [C.POINTER(SamplingParams)]
     l.ftb200_decode_step_sampling_static.argtypes = [C.POINTER(SamplingParams)]
     l.ftb200_static_scratch_bytes.restype = C.c_size_t
+    l.ftb200_set_row_trace.argtypes = [C.c_void_p]
     l.ftb200_beam_workspace_bytes.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_size_t)]
     l.ftb200_beam_search_step.argtypes = [C.POINTER(BeamParams)]
     l.ftb200_vocab_parallel_local.argtypes = [C.POINTER(SamplingParams), C.c_int, C.c_int, C.c_void_p]

@@ -51,6 +51,13 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p)
     return r;
 }
 
+__device__ __forceinline__ uint2 ld_nc_v2(const void* p)
+{
+    uint2 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
+
 // ---- in-place ascending sort of u64 keys by a cooperating thread group ---------------------------
 // Bitonic network in its "all ascending" form (first sub-step of every merge compares mirrored
 // positions), which tolerates any n: positions >= n behave as +infinity and are never touched.

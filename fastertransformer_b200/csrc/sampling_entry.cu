@@ -35,6 +35,8 @@ static int sm_count()
 
 constexpr int kMaxCtasPerSm = 2;
 
+static u64* g_row_trace = nullptr;  // diagnostic timeline buffer, see ftb200_set_row_trace
+
 static size_t scratch_stride_for(int vocab_padded)
 {
     return ((size_t)vocab_padded + 255) / 256 * 256;
@@ -148,10 +150,11 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
     K.cum_log_probs    = p->cum_log_probs;
     K.out_log_probs    = p->output_log_probs;
     K.row_order        = p->row_order;
+    K.trace            = g_row_trace;
 
     // shared-memory plan: candidates, histogram, 1024 floats, vector flags, token hash
     const int epv      = p->dtype == FTB200_F32 ? 4 : 8;
-    K.flag_words       = (p->vocab_size_padded / epv + 32) / 32;
+    K.flag_words       = ((p->vocab_size_padded / epv + 32) / 32 + 1) & ~1;  // even: what follows stays 8-byte aligned
     int specials       = (K.apply_rep ? p->step : 0) + (K.bad_words ? p->bad_words_len : 0) + 2;
     int slots          = 64;
     while (slots < 2 * specials) {
@@ -193,6 +196,12 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
     K.ticket         = (u32*)p->workspace;
     K.scratch        = (u64*)((char*)p->workspace + 256);
     K.scratch_stride = scratch_stride_for(p->vocab_size_padded);
+    return FTB200_OK;
+}
+
+extern "C" int ftb200_set_row_trace(uint64_t* device_buf)
+{
+    g_row_trace = (u64*)device_buf;
     return FTB200_OK;
 }
 

@@ -16,6 +16,8 @@
 #pragma once
 #include <curand_kernel.h>
 
+#include <type_traits>
+
 #include "sampling_params.cuh"
 
 namespace ftb200 {
@@ -42,6 +44,22 @@ struct Smem {
     unsigned short* hitq;  // [kThreads * kUnroll] vectors of the current batch that passed the packed filter
     u32*   nhit;   // [2] queue lengths, alternating per batch
 };
+
+__device__ __forceinline__ u64 global_timer_ns()
+{
+    u64 t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Diagnostic timeline: trace_mark(i) stores the time at which thread 0 passed mark i of the current row.
+constexpr int kTraceWords = 32;  // per row ticket: row, CTA, start, end, 28 marks
+static __device__ void trace_mark(u64* rec, int i)
+{
+    if (rec != nullptr && threadIdx.x == 0) {
+        rec[4 + i] = global_timer_ns();
+    }
+}
 
 __device__ __forceinline__ u32 hash_slot(int id, int shift)
 {
@@ -353,7 +371,8 @@ __device__ __noinline__ void hot_filter(const uint4* vp, int jb, int j1, float t
     }
 }
 
-// hit(v, y) for the columns of the unflagged vectors in [j0, j1) whose final value is >= thr().
+// hit(v, y) - or hit(v, y, raw bits) - for the columns of the unflagged vectors in [j0, j1) whose final
+// value is >= thr().
 // CTA-collective: every thread of the CTA must call it (it synchronises).
 // Per batch: hot_filter() queues the vectors that may hold a passing column; after a barrier the queued
 // vectors are fetched again (they are still in L1/L2) and handled one per thread, so the rare exact work
@@ -406,7 +425,12 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
                     if (y >= thr_y) {
                         // special columns are reported by visit_specials with their final value
                         if (!(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
-                            hit(v, y);
+                            if constexpr (std::is_invocable_v<Hit, int, float, u32>) {
+                                hit(v, y, raw_bits<DT>(r, e));  // callers that bin by bit pattern
+                            }
+                            else {
+                                hit(v, y);
+                            }
                         }
                     }
                 }
@@ -451,8 +475,19 @@ __device__ __noinline__ u32 hot_max(const uint4* vp, int jn)
 // Largest temperature-scaled value of the row (thread-local; -inf when none).  With include_flagged the
 // hot loop covers every column as if none were penalised or banned; without it the special columns
 // (those with a hash entry) are left out, at the price of a per-column look-up in flagged vectors.
+// Order-preserving 16-bit key of a half / bfloat16 bit pattern (sign-magnitude -> unsigned order).
+__device__ __forceinline__ u32 key16(u32 h)
+{
+    return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+}
+__device__ __forceinline__ u32 key16_inv(u32 k)
+{
+    return (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
+}
+
 template<int DT>
-__device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const RowCtx& C, bool include_flagged)
+__device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const RowCtx& C, bool include_flagged,
+                                         u32* raw_key_max = nullptr)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int EPV   = DT == FTB200_F32 ? 4 : 8;
@@ -462,6 +497,7 @@ __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const 
     const bool    fast  = (DT == FTB200_F32 ? (P.bias == nullptr && C.inv_t > 0.0f) : pk) && include_flagged;
     const int     nfull = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / EPV : 0);
     float         best  = -INFINITY;
+    u32           kraw  = 0;
     const int     jfast = fast ? nfull : 0;
     if (jfast > 0) {
         // temperature is monotone for inv_t > 0: the largest raw value gives the largest final value
@@ -472,6 +508,8 @@ __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const 
         }
         else {
             best = fmaxf(temp_value<DT>(X, m & 0xffffu, 0), temp_value<DT>(X, m >> 16, 0));
+            const u32 ka = key16(m & 0xffffu), kb = key16(m >> 16);
+            kraw         = ka > kb ? ka : kb;
         }
     }
 #pragma unroll 1
@@ -483,9 +521,17 @@ __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const 
         for (int e = 0; e < EPV; ++e) {
             const int v = vb + e;
             if (v < P.vocab && !(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
-                best = fmaxf(best, temp_value<DT>(X, raw_bits<DT>(r, e), v));
+                const u32 rb = raw_bits<DT>(r, e);
+                best         = fmaxf(best, temp_value<DT>(X, rb, v));
+                if (DT != FTB200_F32) {
+                    const u32 k = key16(rb);
+                    kraw        = k > kraw ? k : kraw;
+                }
             }
         }
+    }
+    if (raw_key_max != nullptr) {
+        *raw_key_max = kraw;
     }
     return best;
 }
@@ -865,6 +911,7 @@ struct RowOut {
     int*     id_out;
     int      r;
     int      end_id;
+    u64*     trace;  // this row's record of the diagnostic timeline, or null
 };
 
 __device__ __forceinline__ void write_lengths(const KParams& P, const RowOut& O, int id)
@@ -1205,12 +1252,152 @@ __device__ __forceinline__ int lin_bucket(float y, float maxv)
     return kNB - 1 - q;
 }
 
+// ---- ordered soft-max pass, lean form ----------------------------------------------------------------
+// Thread t owns the reference's "virtual threads" 4t..4t+3; per 1024-column chunk it loads its four
+// columns, takes the exponentials and adds them to four running sums, strictly in chunk order.  The
+// special columns (history tokens, banned words, min-length mask) never enter the loop as a look-up:
+// before the loop each one is filed, with its final value, in a short per-thread list ordered by chunk,
+// and the loop only compares the chunk number with the head of its list.
+constexpr int kPatchSlots = 16;  // special columns one thread may own; more -> general loop
+
+template<int DT>
+__device__ __noinline__ bool build_patches(const KParams& P, const Smem& S, const RowCtx& C, int nfull, u32* pkey,
+                                           float* pval, u32* pcnt)
+{
+    __shared__ int s_over;
+    const Xf       X   = make_xf(P, S, C);
+    const int      tid = threadIdx.x;
+    pcnt[tid]          = 0;
+    if (tid == 0) {
+        s_over = 0;
+    }
+    __syncthreads();
+    const int limit = nfull * 1024;
+    for (int i = tid; i < P.hash_slots; i += kThreads) {
+        const u32 w = X.hash[i];
+        if (w == kHashEmpty) {
+            continue;
+        }
+        const int v = (int)(w >> 2);
+        if (v >= limit) {
+            continue;
+        }
+        const u32 bits = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
+        const float y  = special_value<DT>(X, temp_value<DT>(X, bits, v), w & 3u);
+        const int   t  = (v & 1023) >> 2;
+        const u32   at = atomicAdd(&pcnt[t], 1u);
+        if (at < (u32)kPatchSlots) {
+            pkey[at * kThreads + t] = (u32)(((v >> 10) << 2) | (v & 3));
+            pval[at * kThreads + t] = y;
+        }
+        else {
+            s_over = 1;
+        }
+    }
+    __syncthreads();
+    if (s_over) {
+        return false;
+    }
+    // each thread orders its own list by chunk
+    const int n = (int)pcnt[tid];
+    for (int a = 1; a < n; ++a) {
+        const u32   k = pkey[a * kThreads + tid];
+        const float y = pval[a * kThreads + tid];
+        int         b = a - 1;
+        while (b >= 0 && pkey[b * kThreads + tid] > k) {
+            pkey[(b + 1) * kThreads + tid] = pkey[b * kThreads + tid];
+            pval[(b + 1) * kThreads + tid] = pval[b * kThreads + tid];
+            --b;
+        }
+        pkey[(b + 1) * kThreads + tid] = k;
+        pval[(b + 1) * kThreads + tid] = y;
+    }
+    return true;
+}
+
+template<int DT, bool TEMP>
+__device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv, float inv_t, __half inv_t_h,
+                                        const u32* pkey, const float* pval, int pn, u32* hist, float* acc_out)
+{
+    constexpr int ES  = DT == FTB200_F32 ? 4 : 2;
+    constexpr int UN  = 8;
+    const int     tid = threadIdx.x, wid = tid >> 5;
+    float         a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int           pi = 0;
+    u32           nk = pn > 0 ? pkey[tid] : 0xffffffffu;
+    const char*   base = rowp + (size_t)tid * 4 * ES;
+    auto value = [&](u32 bits) {
+        if (DT == FTB200_F16) {
+            __half h = __ushort_as_half((unsigned short)bits);
+            if (TEMP) {
+                h = __hmul(h, inv_t_h);
+            }
+            return __half2float(h);
+        }
+        float x = DT == FTB200_F32 ? __uint_as_float(bits) : __uint_as_float(bits << 16);
+        if (TEMP) {
+            x = x * inv_t;
+        }
+        return x;
+    };
+    for (int m0 = 0; m0 < nfull; m0 += UN) {
+        u32 raw[UN][4];
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            if (m0 + uu < nfull) {
+                const char* q = base + (size_t)(m0 + uu) * 1024 * ES;
+                if (DT == FTB200_F32) {
+                    const uint4 r = ld_nc_v4(q);
+                    raw[uu][0] = r.x, raw[uu][1] = r.y, raw[uu][2] = r.z, raw[uu][3] = r.w;
+                }
+                else {
+                    const uint2 r = ld_nc_v2(q);
+                    raw[uu][0] = r.x & 0xffffu, raw[uu][1] = r.x >> 16;
+                    raw[uu][2] = r.y & 0xffffu, raw[uu][3] = r.y >> 16;
+                }
+            }
+        }
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            const int m = m0 + uu;
+            if (m < nfull) {
+                float y0 = value(raw[uu][0]), y1 = value(raw[uu][1]);
+                float y2 = value(raw[uu][2]), y3 = value(raw[uu][3]);
+                if ((int)(nk >> 2) == m) {
+                    do {
+                        const float yy = pval[pi * kThreads + tid];
+                        const u32   e  = nk & 3u;
+                        y0             = e == 0 ? yy : y0;
+                        y1             = e == 1 ? yy : y1;
+                        y2             = e == 2 ? yy : y2;
+                        y3             = e == 3 ? yy : y3;
+                        ++pi;
+                        nk = pi < pn ? pkey[pi * kThreads + tid] : 0xffffffffu;
+                    } while ((int)(nk >> 2) == m);
+                }
+                // a column at or below -MAX adds exactly zero, as in the reference's loop
+                a0 += round_to_T<DT>(__expf(y0 - maxv));
+                a1 += round_to_T<DT>(__expf(y1 - maxv));
+                a2 += round_to_T<DT>(__expf(y2 - maxv));
+                a3 += round_to_T<DT>(__expf(y3 - maxv));
+                if (((m + 2 * wid) & 15) == 0) {  // warp-uniform 1-in-16 sample for the provisional cut
+                    atomicAdd(&hist[lin_bucket(y0, maxv)], y0 > -FLT_MAX ? 1u : 0u);
+                    atomicAdd(&hist[lin_bucket(y1, maxv)], y1 > -FLT_MAX ? 1u : 0u);
+                    atomicAdd(&hist[lin_bucket(y2, maxv)], y2 > -FLT_MAX ? 1u : 0u);
+                    atomicAdd(&hist[lin_bucket(y3, maxv)], y3 > -FLT_MAX ? 1u : 0u);
+                }
+            }
+        }
+    }
+    acc_out[0] = a0, acc_out[1] = a1, acc_out[2] = a2, acc_out[3] = a3;
+}
+
 // Pass 2 of a soft-max row (reads the row again, from L2): e = T(__expf(y - max)) for every column,
 // summed per "virtual thread" exactly as addBiasSoftMax's min(V,1024)-thread strided loop does
 // (kernels/sampling_topp_kernels.cu:1331-1334), plus the bucket counts.  The per-virtual-thread partial
 // sums land in S.val2[0..nvt).
 template<int DT>
-__device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, const RowCtx& C, float maxv, int nvt)
+__device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, const RowCtx& C, float maxv, int nvt, u64* dbg = nullptr)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int ES  = DT == FTB200_F32 ? 4 : 2;
@@ -1223,10 +1410,30 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
     const float   neg_max = C.neg_max;
         float     acc[4] = {0.f, 0.f, 0.f, 0.f};
         const bool grouped = nvt == 1024 && (((size_t)rowp) % (4 * ES) == 0) && (head % 4 == 0);
+        int        mstart  = 0;
+        if (grouped && P.bias == nullptr) {
+            // chunks that lie entirely inside the vocabulary take the lean loop
+            const int nfull = (vocab < vpad ? vocab : vpad) / 1024;
+            u32*      pkey  = (u32*)S.cand;
+            float*    pval  = (float*)(pkey + kPatchSlots * kThreads);
+            u32*      pcnt  = (u32*)S.hitq;
+            if (nfull > 0 && build_patches<DT>(P, S, C, nfull, pkey, pval, pcnt)) {
+                trace_mark(dbg, 12);
+                const int pn = (int)pcnt[tid];
+                if (P.apply_temp) {
+                    pass2_lean<DT, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                }
+                else {
+                    pass2_lean<DT, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                }
+                mstart = nfull;
+                trace_mark(dbg, 13);
+            }
+        }
         if (grouped) {
             // thread t owns virtual threads 4t..4t+3: one 4-element load per 1024-column chunk
             constexpr int UN = 8;
-            for (int m0 = 0; m0 * 1024 < vpad; m0 += UN) {
+            for (int m0 = mstart; m0 * 1024 < vpad; m0 += UN) {
                 u32 raw[UN][4];
 #pragma unroll
                 for (int uu = 0; uu < UN; ++uu) {
@@ -1323,6 +1530,447 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
         }
 }
 
+// ---- top-p over value classes (16-bit logits) --------------------------------------------------------
+// A half / bfloat16 row holds few distinct values: every ordinary column with the same bit pattern has
+// the same probability.  The sorted probability sequence the reference scans is therefore a short list
+// of runs (probability, count): one per bit pattern above the cut, plus one per special column.  The
+// scan is replayed over the runs in cub::BlockScan's order - no candidate list, no sort of the row -
+// and only the value class that holds the crossing is collected, to find its J-th column (the
+// reference's stable sort leaves equal probabilities in column order).
+// Returns 1 when the row is finished, 0 when the caller has to take the general path.
+constexpr int kMaxRuns  = 4096;  // runs held in shared memory
+constexpr int kMaxSpecs = 1024;  // special / edge columns above the cut
+
+template<int DT>
+__device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O,
+                                             float maxv, float denom, float rand_num, float cut0, u32 kmax16,
+                                             bool want_lp)
+{
+    __shared__ u32   s_ns, s_fail, s_wsum[kWarps], s_ncls;
+    __shared__ int   s_c1, s_sel, s_imin, s_imax;
+    __shared__ float s_R;
+    const Xf         X   = make_xf(P, S, C);
+    const int        tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const bool       complete = !(cut0 > -INFINITY);
+    u64*             spec     = (u64*)S.hitq;            // [kMaxSpecs] (~key(prob) << 32) | column
+    float*           run_pr   = (float*)S.cand;          // [kMaxRuns] runs, probability descending
+    u32*             run_st   = (u32*)S.cand + kMaxRuns; // [kMaxRuns] length, then first position of each run
+    u32*             cls      = (u32*)S.cand;            // columns of the crossing class (after the replay)
+    u32*             rank     = S.hist;                  // per pattern: count, then number of non-empty patterns before it
+    float*           agg      = S.val2;                  // [1024] per-chunk aggregates
+
+    auto prob_of = [&](float y) {
+        const float ex = round_to_T<DT>(__expf(y - maxv));
+        return round_to_T<DT>(ex / denom);
+    };
+    auto prob_of_bin = [&](int idx) { return prob_of(temp_value<DT>(X, key16_inv(kmax16 - (u32)idx), 0)); };
+    __syncthreads();  // a previous call's flags have been read by every thread
+    for (int i = tid; i < kNB; i += kThreads) {
+        S.hist[i] = 0;
+    }
+    if (tid == 0) {
+        s_ns   = 0;
+        s_fail = 0;
+    }
+    __syncthreads();
+    // pass 3 (L2, filtered): exact count of every bit pattern at or above the cut
+    {
+        u32* hist = S.hist;
+        auto count = [&](int v, float y, u32 raw) {
+            if (y > C.neg_max) {
+                const u32 idx = kmax16 - key16(raw);
+                if (idx < (u32)kNB) {
+                    atomicAdd(&hist[idx], 1u);
+                }
+                else {
+                    s_fail = 1;
+                }
+            }
+        };
+        stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return cut0; }, count);
+        trace_mark(O.trace, 20);
+        // (the filtered stream is done with its hit queue: the list of specials may live there)
+        visit_specials<DT>(P, S, C, cut0, [&](int v, float y) {
+            if (y > C.neg_max) {
+                const u32 pos = atomicAdd(&s_ns, 1u);
+                if (pos < (u32)kMaxSpecs) {
+                    spec[pos] = ((u64)(~fkey(prob_of(y))) << 32) | (u32)v;
+                }
+                else {
+                    s_fail = 1;
+                }
+            }
+        });
+    }
+    __syncthreads();
+    trace_mark(O.trace, 5);
+    if (s_fail) {
+        return 0;
+    }
+    const int ns = (int)s_ns;
+    group_sort_u64(spec, ns, tid, kThreads, CtaSync());
+    __syncthreads();
+    trace_mark(O.trace, 22);
+
+    // Runs: the non-empty patterns in descending value with the specials merged in by probability (equal
+    // probabilities: patterns first - the order inside a class of equal values changes no partial sum).
+    constexpr int PER = kNB / kThreads;
+    int           nA;
+    {
+        u32 cnt[PER], mine = 0;
+        for (int i = 0; i < PER; ++i) {
+            cnt[i] = S.hist[tid * PER + i];
+            mine += cnt[i] != 0 ? 1u : 0u;
+        }
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        if (lane == 31) {
+            s_wsum[wid] = incl;
+        }
+        __syncthreads();
+        u32 base = 0, tot = 0;
+        for (int i = 0; i < kWarps; ++i) {
+            if (i < wid) {
+                base += s_wsum[i];
+            }
+            tot += s_wsum[i];
+        }
+        nA = (int)tot;
+        if (nA + ns > kMaxRuns) {
+            return 0;  // uniform: every thread sees the same totals
+        }
+        u32 at = base + incl - mine;
+        for (int i = 0; i < PER; ++i) {
+            const int idx = tid * PER + i;
+            rank[idx]     = at;
+            if (cnt[i] != 0) {
+                const float pr = prob_of_bin(idx);
+                const u32   kp = ~fkey(pr);  // ascending in this key = descending probability
+                int         lo = 0, hi = ns; // number of specials with a strictly larger probability
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if ((u32)(spec[mid] >> 32) < kp) {
+                        lo = mid + 1;
+                    }
+                    else {
+                        hi = mid;
+                    }
+                }
+                run_pr[at + lo] = pr;
+                run_st[at + lo] = cnt[i];
+                ++at;
+            }
+        }
+    }
+    __syncthreads();
+    for (int j = tid; j < ns; j += kThreads) {
+        const u32 kp = (u32)(spec[j] >> 32);
+        int       lo = 0, hi = kNB;  // first pattern with a probability below this one
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if ((u32)mid <= kmax16 && ~fkey(prob_of_bin(mid)) <= kp) {
+                lo = mid + 1;
+            }
+            else {
+                hi = mid;
+            }
+        }
+        const int nb     = lo < kNB ? (int)rank[lo] : nA;  // non-empty patterns with a probability >= this one
+        run_pr[j + nb]   = fkey_inv(~kp);
+        run_st[j + nb]   = 1u;
+    }
+    __syncthreads();
+    const int M = nA + ns;
+    // the exponential has to be monotone over the patterns for the order of the runs to be the sorted order
+    for (int i = tid; i + 1 < M; i += kThreads) {
+        if (run_pr[i] < run_pr[i + 1]) {
+            s_fail = 1;
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        return 0;
+    }
+    // exclusive scan of the run lengths -> first position of each run
+    u32 N;
+    {
+        constexpr int RPT = kMaxRuns / kThreads;
+        u32           c[RPT], mine = 0;
+        for (int i = 0; i < RPT; ++i) {
+            const int r = tid * RPT + i;
+            c[i]        = r < M ? run_st[r] : 0u;
+            mine += c[i];
+        }
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        __syncthreads();
+        if (lane == 31) {
+            s_wsum[wid] = incl;
+        }
+        __syncthreads();
+        u32 base = 0, tot = 0;
+        for (int i = 0; i < kWarps; ++i) {
+            if (i < wid) {
+                base += s_wsum[i];
+            }
+            tot += s_wsum[i];
+        }
+        N      = tot;
+        u32 at = base + incl - mine;
+        for (int i = 0; i < RPT; ++i) {
+            const int r = tid * RPT + i;
+            if (r < M) {
+                run_st[r] = at;
+                at += c[i];
+            }
+        }
+    }
+    __syncthreads();
+    trace_mark(O.trace, 6);
+    const int nch = (int)((N + 255u) / 256u);
+    if (nch > 1024 || N == 0) {
+        return 0;
+    }
+    // run that holds position p
+    auto run_of = [&](u32 p) {
+        int lo = 0, hi = M - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (run_st[mid] <= p) {
+                lo = mid;
+            }
+            else {
+                hi = mid - 1;
+            }
+        }
+        return lo;
+    };
+    // the 8 consecutive values of this lane in chunk c
+    auto load8 = [&](int c, float* x) {
+        const u32 p0 = (u32)c * 256u + (u32)lane * 8u;
+        int       i  = p0 < N ? run_of(p0) : 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const u32 p = p0 + (u32)e;
+            if (p < N) {
+                if (i + 1 < M && run_st[i + 1] <= p) {
+                    ++i;
+                }
+                x[e] = run_pr[i];
+            }
+            else {
+                x[e] = 0.0f;
+            }
+        }
+    };
+    // aggregate of every 256-value chunk in cub::BlockScan's raking order (32 segments of 8, Kogge-Stone
+    // across the segment totals); the chunks are independent of the running prefix
+    for (int c = wid; c < nch; c += kWarps) {
+        float x[8];
+        load8(c, x);
+        float up = x[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            up = up + x[i];
+        }
+        float inc = up;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            float t = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) {
+                inc = inc + t;
+            }
+        }
+        if (lane == 31) {
+            agg[c] = inc;
+        }
+    }
+    __syncthreads();
+    trace_mark(O.trace, 25);
+    // running prefix chunk by chunk, as the reference's prefix functor accumulates it; stop a little early
+    // (partial sums inside a chunk differ from prefix + aggregate only in the last bits)
+    if (tid == 0) {
+        float     R    = 0.0f;
+        int       c1   = nch;
+        const float stop = rand_num * (1.0f - 1e-4f);
+        for (int c = 0; c < nch; ++c) {
+            const float R2 = R + agg[c];
+            if (R2 >= stop) {
+                c1 = c;
+                break;
+            }
+            R = R2;
+        }
+        s_c1 = c1;
+        s_R  = R;
+    }
+    __syncthreads();
+    if (s_c1 >= nch) {
+        return 0;  // the cut was too high (or the draw is never reached): general path
+    }
+    if (wid == 0) {
+        float R   = s_R;
+        int   sel = -2;
+        for (int c = s_c1; c < nch; ++c) {
+            float x[8];
+            load8(c, x);
+            float up = x[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) {
+                up = up + x[i];
+            }
+            float inc = up;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                float t = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) {
+                    inc = inc + t;
+                }
+            }
+            const float ag  = __shfl_sync(0xffffffffu, inc, 31);
+            const float ex  = __shfl_up_sync(0xffffffffu, inc, 1);
+            float       o   = lane == 0 ? R : R + ex;
+            u32         cnt = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                o = o + x[i];
+                cnt += rand_num <= o ? 1u : 0u;
+            }
+            // a warp of the reference covers 4 of these lanes (32 consecutive probabilities)
+            u32 c4 = cnt;
+            c4 += __shfl_xor_sync(0xffffffffu, c4, 1);
+            c4 += __shfl_xor_sync(0xffffffffu, c4, 2);
+            const u32 any = __ballot_sync(0xffffffffu, c4 > 0);
+            if (any) {
+                const int g  = (__ffs(any) - 1) >> 2;
+                const u32 pc = __shfl_sync(0xffffffffu, c4, g * 4);
+                if (!complete && (u32)(c * 256 + g * 32 + 31) >= N) {
+                    sel = -2;  // the 32 probabilities of that warp are not all known
+                }
+                else {
+                    sel = c * 256 + g * 32 + (32 - (int)pc);
+                }
+                break;
+            }
+            R = R + ag;
+        }
+        if (lane == 0) {
+            s_sel = sel;
+        }
+    }
+    __syncthreads();
+    const int sel = s_sel;
+    trace_mark(O.trace, 7);
+    if (sel < 0 || (u32)sel >= N) {
+        return 0;
+    }
+    // the class of the crossing: every column whose probability equals that of position sel
+    const int   i_at  = run_of((u32)sel);
+    const float p_sel = run_pr[i_at];
+    const u32   k_sel = fkey(p_sel);
+    if (tid == 0) {
+        s_ncls = 0;
+        s_imin = 0x7fffffff;
+        s_imax = -1;
+    }
+    __syncthreads();
+    // first run of the class -> rank of the crossing inside the class
+    {
+        int lo = 0, hi = i_at;  // first run with probability == p_sel (runs are descending)
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (fkey(run_pr[mid]) > k_sel) {
+                lo = mid + 1;
+            }
+            else {
+                hi = mid;
+            }
+        }
+        if (tid == 0) {
+            s_c1 = sel - (int)run_st[lo];
+        }
+    }
+    // bit patterns that map to this probability
+    for (int i = 0; i < PER; ++i) {
+        const int idx = tid * PER + i;
+        if ((u32)idx <= kmax16) {
+            const u32 raw = key16_inv(kmax16 - (u32)idx);
+            if (fkey(prob_of(temp_value<DT>(X, raw, 0))) == k_sel) {
+                atomicMin(&s_imin, idx);
+                atomicMax(&s_imax, idx);
+            }
+        }
+    }
+    __syncthreads();  // the runs have been read for the last time: the class list takes their place
+    for (int j = tid; j < ns; j += kThreads) {
+        if ((u32)(spec[j] >> 32) == ~k_sel) {
+            const u32 pos = atomicAdd(&s_ncls, 1u);
+            cls[pos]      = (u32)(spec[j] & 0xffffffffu);
+        }
+    }
+    __syncthreads();
+    const int J = s_c1;
+    trace_mark(O.trace, 27);
+    if (s_imax >= 0) {
+        const u32   k_hi  = kmax16 - (u32)s_imin, k_lo = kmax16 - (u32)s_imax;
+        const float y_lo  = temp_value<DT>(X, key16_inv(k_lo), 0);
+        auto        member = [&](int v, float y, u32 raw) {
+            const u32 k = key16(raw);
+            if (k >= k_lo && k <= k_hi) {
+                const u32 pos = atomicAdd(&s_ncls, 1u);
+                if (pos < (u32)(2 * kMaxRuns)) {
+                    cls[pos] = (u32)v;
+                }
+            }
+        };
+        stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_lo; }, member);
+    }
+    __syncthreads();
+    const int ncls = (int)s_ncls;
+    trace_mark(O.trace, 8);
+    if (ncls > 1024 || J >= ncls) {
+        return 0;  // an unusually large class of equal values: general path
+    }
+    // J-th smallest column of the class
+    for (int a = tid; a < ncls; a += kThreads) {
+        const u32 ca = cls[a];
+        u32       rk = 0;
+        for (int b = 0; b < ncls; ++b) {
+            rk += cls[b] < ca ? 1u : 0u;
+        }
+        if ((int)rk == J) {
+            s_sel = (int)ca;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int id = s_sel;
+        *O.id_out    = id;
+        if (want_lp) {
+            const float lprob = logf(p_sel);
+            if (P.cum_log_probs != nullptr) {
+                P.cum_log_probs[O.r] += lprob;
+            }
+            if (P.out_log_probs != nullptr) {
+                P.out_log_probs[O.r] = lprob;
+            }
+        }
+        write_lengths(P, O, id);
+    }
+    __syncthreads();
+    return 1;
+}
+
 template<int DT>
 __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O, u64* gscratch,
                             bool is_topp, int k, float u, float top_p, bool want_lp)
@@ -1343,8 +1991,16 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     if (tid == 0) {
         s_redo = 0;
     }
-    float tall = stream_max<DT>(P, S, C, true);
-    tall       = fkey_inv((u32)(block_max_u64((u64)fkey(tall) << 32) >> 32));
+    trace_mark(O.trace, 0);
+    u32   kraw = 0;
+    float tall = stream_max<DT>(P, S, C, true, &kraw);
+    trace_mark(O.trace, 1);
+    {
+        // largest value and largest 16-bit pattern (as an ordered key) in one reduction
+        const u64 m = block_max_u64(((u64)fkey(tall) << 32) | kraw);
+        tall        = fkey_inv((u32)(m >> 32));
+        kraw        = (u32)(m & 0xffffffffu);
+    }
     float tmax = -INFINITY;
     {
         const Xf X = make_xf(P, S, C);
@@ -1361,6 +2017,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
             s_redo = 1;
         }
     }
+    trace_mark(O.trace, 15);
     __syncthreads();
     if (s_redo) {
         tmax = stream_max<DT>(P, S, C, false);
@@ -1383,6 +2040,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         return;
     }
     const float maxv = fkey_inv((u32)(best >> 32));
+    trace_mark(O.trace, 2);
 
     // pass 2 (L2): exponentials, the denominator in the reference's summation order, and bucket counts
     // of every 16th group of columns.  Shared-memory atomics retire about one lane per clock, so a
@@ -1392,8 +2050,9 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     }
     __syncthreads();
     const int nvt = P.vocab < 1024 ? P.vocab : 1024;  // blockDim of addBiasSoftMax (:1364)
-    softmax_pass2<DT>(P, S, C, maxv, nvt);
+    softmax_pass2<DT>(P, S, C, maxv, nvt, O.trace);
     __syncthreads();
+    trace_mark(O.trace, 3);
     if (wid == 0) {
         float s = butterfly_block_sum(S.val2, nvt);
         if (lane == 0) {
@@ -1401,6 +2060,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         }
     }
     __syncthreads();
+    trace_mark(O.trace, 17);
     const float denom = s_S + 1e-6f;
 
     if (is_topp) {
@@ -1452,6 +2112,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
                 return (double)S.hist[b] * (double)(__expf(-((float)q + 0.5f) / (float)kLinScale) * scale);
             };
             b_est = find_from_top(w, (double)(rand_num * 1.25f + 0.02f), nullptr);
+            trace_mark(O.trace, 19);
         }
         else {
             auto w = [&](int b) { return 16.0 * (double)S.hist[b]; };
@@ -1469,6 +2130,24 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         __syncthreads();
         b_cut = s_bthr;
         __syncthreads();
+    }
+
+    trace_mark(O.trace, 4);
+    if (is_topp && DT != FTB200_F32 && packed_ok<DT>(P, C)) {
+        // value-class path: first with the provisional cut, then with every pattern the class window holds
+        const u32   k_bot = kraw >= (u32)(kNB - 1) ? kraw - (u32)(kNB - 1) : 0u;
+        const float cut_b = k_bot == 0u ? -INFINITY : temp_value<DT>(make_xf(P, S, C), key16_inv(k_bot), 0);
+        float       cut_a = b_cut == 0 ? -INFINITY :
+                                         maxv - (float)(kNB - b_cut) / (float)kLinScale - 1e-3f * fabsf(maxv) - 1e-3f;
+        cut_a             = fmaxf(cut_a, cut_b);
+        if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_a, kraw, want_lp)) {
+            return;
+        }
+        if (cut_b < cut_a && row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_b, kraw, want_lp)) {
+            return;
+        }
+        __syncthreads();
+        trace_mark(O.trace, 11);
     }
 
     for (int attempt = 0; attempt < 2; ++attempt) {
@@ -1762,7 +2441,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
 }
 
 template<int DT>
-__device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratch)
+__device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratch, u64* trace)
 {
     __shared__ float s_u;
     const int        tid = threadIdx.x;
@@ -1777,6 +2456,7 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
     O.r      = r;
     O.end_id = P.end_ids[r];
     O.id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
+    O.trace  = trace;
 
     const bool fin     = P.finished != nullptr ? P.finished[r] != 0 : false;
     const bool want_lp = P.cum_log_probs != nullptr || P.out_log_probs != nullptr;
@@ -1897,7 +2577,15 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
         }
         // rows are handed out costliest first when the caller supplied an order (longest-processing-
         // time-first keeps the last CTAs from finishing alone with an expensive row)
-        process_row<DT>(P, S, P.row_order != nullptr ? P.row_order[t] : t, gscratch);
+        const int r   = P.row_order != nullptr ? P.row_order[t] : t;
+        u64*      rec = P.trace != nullptr ? P.trace + (size_t)t * kTraceWords : nullptr;
+        if (rec != nullptr && threadIdx.x == 0) {
+            rec[0] = (u64)r, rec[1] = (u64)blockIdx.x, rec[2] = global_timer_ns();
+        }
+        process_row<DT>(P, S, r, gscratch, rec);
+        if (rec != nullptr && threadIdx.x == 0) {
+            rec[3] = global_timer_ns();
+        }
     }
 }
 
@@ -1928,6 +2616,7 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
         O.r      = r;
         O.end_id = P.end_ids[r];
         O.id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
+        O.trace  = nullptr;
         const bool fin = P.finished != nullptr ? P.finished[r] != 0 : false;
         __syncthreads();
         if (fin) {

@@ -55,6 +55,7 @@ struct KParams {
     int      vp_cap;
     int      vocab_offset;  // first token id of this shard of the vocabulary (0 when not sharded)
     u32*     ticket;
+    u64*     trace;           // optional per-row timeline: {row, CTA, start ns, end ns} per ticket, else null
     u64*     scratch;         // per-CTA candidate overflow area
     size_t   scratch_stride;  // u64 entries per CTA
     int      hash_slots, hash_shift, flag_words;

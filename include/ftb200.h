@@ -167,6 +167,13 @@ int ftb200_decode_step_sampling(const ftb200_sampling_params* p);
 /* Number of kernels the last ftb200_decode_step_sampling call on this thread launched. */
 int ftb200_last_launch_count(void);
 
+/* Diagnostic, no counterpart in the reference: when `device_buf` is not null every later
+ * ftb200_decode_step_sampling call writes, per row ticket t, 32 uint64 at device_buf[32t..]:
+ * {row, CTA, start, end, 28 phase marks} with the times in nanoseconds of the GPU's global timer
+ * (a mark the row did not pass is left untouched).  The buffer must hold 256 bytes per row of the
+ * call.  Pass null to switch the trace off (the default). */
+int ftb200_set_row_trace(uint64_t* device_buf);
+
 /* ------------------------------------------------------------------------------------------
  * Bad-word ban as a stand-alone call (the fused step above already applies it; this entry serves
  * callers that use the kernel by itself, e.g. the beam-search path).  Writes -inf into the logits.
