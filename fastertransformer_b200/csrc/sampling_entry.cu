@@ -152,7 +152,7 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
     K.row_order        = p->row_order;
     K.trace            = g_row_trace;
 
-    // shared-memory plan: candidates, histogram, 1024 floats, vector flags, token hash
+    // shared-memory plan: candidates, histogram, 1024 floats, vector flags, token hash with two values per slot
     const int epv      = p->dtype == FTB200_F32 ? 4 : 8;
     K.flag_words       = ((p->vocab_size_padded / epv + 32) / 32 + 1) & ~1;  // even: what follows stays 8-byte aligned
     int specials       = (K.apply_rep ? p->step : 0) + (K.bad_words ? p->bad_words_len : 0) + 2;
@@ -166,8 +166,8 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
         ++lg;
     }
     K.hash_shift = 32 - lg;
-    smem         = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 4
-                   + (size_t)(slots / 2) * 4 + 32 + (size_t)kThreads * 16 * 2;
+    smem         = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 12 + 32
+                   + (size_t)kThreads * 16 * 2;
     if (smem > 200 * 1024) {
         set_error("ftb200_decode_step_sampling: token history too long for the shared-memory hash");
         return FTB200_UNSUPPORTED;

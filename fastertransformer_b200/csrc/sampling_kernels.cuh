@@ -39,8 +39,8 @@ struct Smem {
     float* val2;   // [1024] exp values of the sorted top-k / soft-max partial sums
     u32*   flags;  // one bit per aligned vector: holds a token with a hash entry
     u32*   hash;   // open addressing, (id << 2) | flags
-    u32*   spec;   // indices of the aligned vectors that hold a token with a hash entry
-    u32*   nspec;  // length of spec
+    float* spre;   // per hash slot: value of that column after temperature, before penalty / ban
+    float* sfin;   // per hash slot: final value of that column (-inf when banned or outside the vocabulary)
     unsigned short* hitq;  // [kThreads * kUnroll] vectors of the current batch that passed the packed filter
     u32*   nhit;   // [2] queue lengths, alternating per batch
 };
@@ -332,7 +332,7 @@ __device__ __noinline__ void stream_all(const KParams& P, const Smem& S, const R
 // logits (16-bit types) or one multiply + compare per logit (fp32).  A vector with a passing column
 // only has its batch-relative index queued in shared memory.  Takes nothing but scalars so that the
 // whole loop lives in registers.
-constexpr int kHotUnroll = 16;  // 16-byte loads in flight per thread in the register-only loops
+constexpr int kHotUnroll = 8;   // 16-byte loads in flight per thread in the register-only loops
 
 template<int DT>
 __device__ __noinline__ void hot_filter(const uint4* vp, int jb, int j1, float thr_y, u32 thr2, float inv, bool temp,
@@ -553,12 +553,8 @@ __device__ __noinline__ void visit_specials(const KParams& P, const Smem& S, con
         if (w == kHashEmpty) {
             continue;
         }
-        const int v = (int)(w >> 2);
-        float     y = -INFINITY;
-        if (v < X.vocab) {
-            const u32 bits = DT == FTB200_F32 ? __ldg((const u32*)rowp + v) : (u32)__ldg((const unsigned short*)rowp + v);
-            y              = special_value<DT>(X, temp_value<DT>(X, bits, v), w & 3u);
-        }
+        const int   v = (int)(w >> 2);
+        const float y = S.sfin[i];
         if (y >= thr_y) {
             f(v, y);
         }
@@ -754,18 +750,21 @@ __device__ __noinline__ void build_row(const KParams& P, const Smem& S, RowCtx& 
     constexpr int EPV = DT == FTB200_F32 ? 4 : 8;
     const int     tid = threadIdx.x;
 
-    C.rowp          = (const char*)P.logits + (size_t)r * P.vocab_padded * ES;
-    const size_t ad = (size_t)C.rowp;
-    int          hd = (int)(((16 - (ad & 15)) & 15) / ES);
-    C.head          = hd < P.vocab_padded ? hd : P.vocab_padded;
-    C.nvec          = (P.vocab_padded - C.head) / EPV;
-    C.inv_t         = 1.0f;
-    if (P.apply_temp) {
-        C.inv_t = 1.0f / (P.temperature[r] + 1e-6f);
+    if (tid == 0) {  // C is shared by the CTA; the barrier below publishes it
+        C.rowp          = (const char*)P.logits + (size_t)r * P.vocab_padded * ES;
+        const size_t ad = (size_t)C.rowp;
+        int          hd = (int)(((16 - (ad & 15)) & 15) / ES);
+        C.head          = hd < P.vocab_padded ? hd : P.vocab_padded;
+        C.nvec          = (P.vocab_padded - C.head) / EPV;
+        float inv_t     = 1.0f;
+        if (P.apply_temp) {
+            inv_t = 1.0f / (P.temperature[r] + 1e-6f);
+        }
+        C.inv_t   = inv_t;
+        C.inv_t_h = __float2half_rn(inv_t);
+        C.theta   = P.apply_rep ? P.rep_penalty[r] : 1.0f;
+        C.neg_max = DT == FTB200_F16 ? -65504.0f : -FLT_MAX;
     }
-    C.inv_t_h = __float2half_rn(C.inv_t);
-    C.theta   = P.apply_rep ? P.rep_penalty[r] : 1.0f;
-    C.neg_max = DT == FTB200_F16 ? -65504.0f : -FLT_MAX;
 
     for (int i = tid; i < P.hash_slots; i += kThreads) {
         S.hash[i] = kHashEmpty;
@@ -822,6 +821,39 @@ __device__ __noinline__ void build_row(const KParams& P, const Smem& S, RowCtx& 
     if (P.apply_minlen && tid == 0) {
         if (P.seq_len[r] + 1 - P.max_input_len < P.min_lengths[r]) {
             hash_insert(P, S, C, P.end_ids[r], kFlagDead);
+        }
+    }
+    __syncthreads();
+    // Values of the special columns, fetched once per row with all loads of a thread in flight together:
+    // every later visit of the specials reads shared memory only.
+    {
+        const Xf      X  = make_xf(P, S, C);
+        constexpr int SB = 8;
+        for (int i0 = tid; i0 < P.hash_slots; i0 += kThreads * SB) {
+            u32 w[SB], bits[SB];
+#pragma unroll
+            for (int q = 0; q < SB; ++q) {
+                const int i = i0 + q * kThreads;
+                w[q]        = i < P.hash_slots ? S.hash[i] : kHashEmpty;
+                bits[q]     = 0;
+                if (w[q] != kHashEmpty && (int)(w[q] >> 2) < P.vocab) {
+                    const int v = (int)(w[q] >> 2);
+                    bits[q] = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < SB; ++q) {
+                const int i = i0 + q * kThreads;
+                if (i < P.hash_slots) {
+                    float pre = -INFINITY, fin = -INFINITY;
+                    if (w[q] != kHashEmpty && (int)(w[q] >> 2) < P.vocab) {
+                        pre = temp_value<DT>(X, bits[q], (int)(w[q] >> 2));
+                        fin = special_value<DT>(X, pre, w[q] & 3u);
+                    }
+                    S.spre[i] = pre;
+                    S.sfin[i] = fin;
+                }
+            }
         }
     }
     __syncthreads();
@@ -1064,6 +1096,256 @@ __device__ __noinline__ void row_argmax(const KParams& P, const Smem& S, const R
     __syncthreads();
 }
 
+// Common end of the top-k rows: sort the candidates (value descending), then either hand them to the
+// vocabulary-parallel exchange or draw.
+static __device__ __noinline__ void topk_tail(const KParams& P, const Smem& S, const RowOut& O, u64* cand, int n, int k, float u,
+                                              float top_p)
+{
+    const int tid = threadIdx.x;
+    group_sort_u64(cand, n, tid, kThreads, CtaSync());
+    __syncthreads();
+    if (P.vp_out != nullptr) {
+        // Vocabulary-parallel local pass: hand over every column whose value reaches this shard's k-th
+        // value, whole tie class included.  The global k-th value cannot be smaller than a shard's, so
+        // the union over the shards holds every column the global selection and its tie order can touch.
+        __shared__ int s_m;
+        const int      k_eff = k < n ? k : n;
+        if (tid == 0) {
+            s_m = k_eff;
+        }
+        __syncthreads();
+        if (k_eff > 0) {
+            const u32 kv = (u32)(cand[k_eff - 1] >> 32);
+            for (int i = k_eff + tid; i < n; i += kThreads) {
+                if ((u32)(cand[i] >> 32) == kv) {
+                    atomicMax(&s_m, i + 1);
+                }
+            }
+        }
+        __syncthreads();
+        const int m   = s_m;
+        u64*      out = P.vp_out + (size_t)O.r * (P.vp_cap + 1);
+        if (tid == 0) {
+            out[0] = m > P.vp_cap ? ~0ull : (u64)m;  // ~0: more ties than the exchange record holds
+        }
+        for (int i = tid; i < m && i < P.vp_cap; i += kThreads) {
+            const u64 e = cand[i];
+            out[1 + i]  = (e & 0xffffffff00000000ull) | (u64)((u32)(e & 0xffffffffu) + (u32)P.vocab_offset);
+        }
+        __syncthreads();
+        return;
+    }
+    topk_finish(P, S, O, cand, n, k, u, top_p, true, false);
+}
+
+// ---- top-k in two passes -------------------------------------------------------------------------------
+// Pass 1 (HBM) keeps, per thread, the running maximum of eight disjoint column subsets ("slots", 2048 per
+// row).  The K-th largest slot maximum is a lower bound of the K-th largest column, usually a tight one:
+// the largest columns of a row almost always sit in different slots.  Pass 2 (L2) collects the columns at
+// or above that bound, which are then sorted and drawn from.  Special columns are counted separately
+// (their final value is not the raw one), and the collected set is checked to hold at least k columns.
+constexpr int kSlotsPerThread = 8;
+constexpr int kSlots          = kSlotsPerThread * kThreads;
+
+template<int DT>
+__device__ __forceinline__ void hot_slotmax_body(const uint4* vp, int jn, u32* slots)
+{
+    const int tid = threadIdx.x;
+    if (DT == FTB200_F32) {
+        float a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            a[i] = -INFINITY;
+        }
+        for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
+            uint4 q[kHotUnroll];
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                const int j = jb + u * kThreads + tid;
+                if (j < jn) {
+                    q[u] = ld_nc_v4(vp + j);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                if (jb + u * kThreads + tid < jn) {
+                    const int h = (u & 1) * 4;
+                    a[h + 0]    = fmaxf(a[h + 0], __uint_as_float(q[u].x));
+                    a[h + 1]    = fmaxf(a[h + 1], __uint_as_float(q[u].y));
+                    a[h + 2]    = fmaxf(a[h + 2], __uint_as_float(q[u].z));
+                    a[h + 3]    = fmaxf(a[h + 3], __uint_as_float(q[u].w));
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            slots[i * kThreads + tid] = fkey(a[i]);
+        }
+    }
+    else {
+        const u32 ninf = DT == FTB200_F16 ? 0xfc00fc00u : 0xff80ff80u;
+        u32       a0 = ninf, a1 = ninf, a2 = ninf, a3 = ninf;
+        for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
+            uint4 q[kHotUnroll];
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                const int j = jb + u * kThreads + tid;
+                if (j < jn) {
+                    q[u] = ld_nc_v4(vp + j);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                if (jb + u * kThreads + tid < jn) {
+                    a0 = max2<DT>(a0, q[u].x);
+                    a1 = max2<DT>(a1, q[u].y);
+                    a2 = max2<DT>(a2, q[u].z);
+                    a3 = max2<DT>(a3, q[u].w);
+                }
+            }
+        }
+        slots[0 * kThreads + tid] = key16(a0 & 0xffffu) << 16;
+        slots[1 * kThreads + tid] = key16(a0 >> 16) << 16;
+        slots[2 * kThreads + tid] = key16(a1 & 0xffffu) << 16;
+        slots[3 * kThreads + tid] = key16(a1 >> 16) << 16;
+        slots[4 * kThreads + tid] = key16(a2 & 0xffffu) << 16;
+        slots[5 * kThreads + tid] = key16(a2 >> 16) << 16;
+        slots[6 * kThreads + tid] = key16(a3 & 0xffffu) << 16;
+        slots[7 * kThreads + tid] = key16(a3 >> 16) << 16;
+    }
+}
+
+template<int DT>
+__device__ __noinline__ void hot_slotmax(const uint4* vp, int jn, u32* slots)
+{
+    hot_slotmax_body<DT>(vp, jn, slots);
+}
+
+// Returns false when the row has to take the general one-pass path (too many specials, a candidate set
+// that does not fit, a bound that the special columns invalidate).
+template<int DT>
+__device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O, int k, float u,
+                                       float top_p)
+{
+    __shared__ u32 s_n, s_ovf;
+    constexpr int  EPV = DT == FTB200_F32 ? 4 : 8;
+    {
+        // nothing but the arguments is live across the streaming call
+        const int nfull0 = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / EPV : 0);
+        if (nfull0 * EPV < 8 * k || nfull0 < kThreads) {
+            return false;  // short rows: the one-pass path is as good
+        }
+        trace_mark(O.trace, 0);
+        hot_slotmax<DT>(vec_base<DT>(C), nfull0, (u32*)S.hitq);
+        __syncthreads();
+        trace_mark(O.trace, 1);
+    }
+    const Xf  X     = make_xf(P, S, C);
+    const int tid   = threadIdx.x;
+    u32*      slots = (u32*)S.hitq;  // [kSlots], free again before the filtered pass needs its queue
+    u32*      hist  = S.hist;
+
+    // K-th largest slot key, 12 + 12 bits at a time
+    auto kth_slot_key = [&](int K) {
+        for (int i = tid; i < kNB; i += kThreads) {
+            hist[i] = 0;
+        }
+        __syncthreads();
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            atomicAdd(&hist[slots[i * kThreads + tid] >> 20], 1u);
+        }
+        __syncthreads();
+        const int b1 = find_from_top([&](int b) { return (double)hist[b]; }, (double)K, nullptr);
+        if (b1 < 0) {
+            return 0u;
+        }
+        u32 above = 0;
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            above += (slots[i * kThreads + tid] >> 20) > (u32)b1 ? 1u : 0u;
+        }
+        above = block_sum_u32(above);
+        for (int i = tid; i < kNB; i += kThreads) {
+            hist[i] = 0;
+        }
+        __syncthreads();
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            const u32 key = slots[i * kThreads + tid];
+            if ((key >> 20) == (u32)b1) {
+                atomicAdd(&hist[(key >> 8) & 0xfffu], 1u);
+            }
+        }
+        __syncthreads();
+        const int b2 = find_from_top([&](int b) { return (double)hist[b]; }, (double)(K - (int)above), nullptr);
+        return ((u32)b1 << 20) | ((u32)(b2 < 0 ? 0 : b2) << 8);
+    };
+    auto value_of_key = [&](u32 key) {
+        if (DT == FTB200_F32) {
+            return temp_value<DT>(X, __float_as_uint(fkey_inv(key)), 0);
+        }
+        return temp_value<DT>(X, key16_inv(key >> 16), 0);
+    };
+    // specials whose value before the penalty reaches the bound: they may occupy slots without being
+    // selectable at that value
+    auto specials_at = [&](float thr_y) {
+        u32 c = 0;
+        for (int i = tid; i < P.hash_slots; i += kThreads) {
+            c += (X.hash[i] != kHashEmpty && S.spre[i] >= thr_y) ? 1u : 0u;
+        }
+        return (int)block_sum_u32(c);
+    };
+    u32 key = kth_slot_key(k);
+    if (key == 0u) {
+        return false;
+    }
+    const int s1 = specials_at(value_of_key(key));
+    if (s1 > 0) {
+        if (k + s1 > 1600) {
+            return false;
+        }
+        key = kth_slot_key(k + s1);
+        if (key == 0u) {
+            return false;
+        }
+    }
+    const float thr_y = value_of_key(key);
+    trace_mark(O.trace, 2);
+    if (!(thr_y > C.neg_max)) {
+        return false;
+    }
+
+    // pass 2: collect
+    if (tid == 0) {
+        s_n   = 0;
+        s_ovf = 0;
+    }
+    __syncthreads();
+    u64* cand = S.cand;
+    auto push = [&](int v, float y) {
+        if (y > C.neg_max) {
+            const u32 pos = atomicAdd(&s_n, 1u);
+            if (pos < (u32)kCap) {
+                cand[pos] = ((u64)(~fkey(y)) << 32) | (u32)v;
+            }
+            else {
+                s_ovf = 1;
+            }
+        }
+    };
+    stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return thr_y; }, push);
+    trace_mark(O.trace, 3);
+    visit_specials<DT>(P, S, C, thr_y, push);
+    __syncthreads();
+    const int n = (int)s_n;
+    if (s_ovf || n < k) {
+        __syncthreads();
+        return false;
+    }
+    trace_mark(O.trace, 4);
+    topk_tail(P, S, O, cand, n, k, u, top_p);
+    trace_mark(O.trace, 5);
+    return true;
+}
+
 // ---- top-k, k > 1, no log-probs: one pass, running threshold, candidates in shared memory ----------
 template<int DT>
 __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O,
@@ -1208,40 +1490,7 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
         __syncthreads();
         n = (int)s_n;
     }
-    group_sort_u64(cand, n, tid, kThreads, CtaSync());
-    __syncthreads();
-    if (P.vp_out != nullptr) {
-        // Vocabulary-parallel local pass: hand over every column whose value reaches this shard's k-th
-        // value, whole tie class included.  The global k-th value cannot be smaller than a shard's, so
-        // the union over the shards holds every column the global selection and its tie order can touch.
-        __shared__ int s_m;
-        const int      k_eff = k < n ? k : n;
-        if (tid == 0) {
-            s_m = k_eff;
-        }
-        __syncthreads();
-        if (k_eff > 0) {
-            const u32 kv = (u32)(cand[k_eff - 1] >> 32);
-            for (int i = k_eff + tid; i < n; i += kThreads) {
-                if ((u32)(cand[i] >> 32) == kv) {
-                    atomicMax(&s_m, i + 1);
-                }
-            }
-        }
-        __syncthreads();
-        const int m   = s_m;
-        u64*      out = P.vp_out + (size_t)O.r * (P.vp_cap + 1);
-        if (tid == 0) {
-            out[0] = m > P.vp_cap ? ~0ull : (u64)m;  // ~0: more ties than the exchange record holds
-        }
-        for (int i = tid; i < m && i < P.vp_cap; i += kThreads) {
-            const u64 e = cand[i];
-            out[1 + i]  = (e & 0xffffffff00000000ull) | (u64)((u32)(e & 0xffffffffu) + (u32)P.vocab_offset);
-        }
-        __syncthreads();
-        return;
-    }
-    topk_finish(P, S, O, cand, n, k, u, top_p, true, false);
+    topk_tail(P, S, O, cand, n, k, u, top_p);
 }
 
 // ---- rows that need soft-max probabilities: top-p, and top-k when log-probs are requested -----------
@@ -1282,8 +1531,7 @@ __device__ __noinline__ bool build_patches(const KParams& P, const Smem& S, cons
         if (v >= limit) {
             continue;
         }
-        const u32 bits = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
-        const float y  = special_value<DT>(X, temp_value<DT>(X, bits, v), w & 3u);
+        const float y  = S.sfin[i];
         const int   t  = (v & 1023) >> 2;
         const u32   at = atomicAdd(&pcnt[t], 1u);
         if (at < (u32)kPatchSlots) {
@@ -1323,8 +1571,10 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
     constexpr int UN  = 8;
     const int     tid = threadIdx.x, wid = tid >> 5;
     float         a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    // head of this thread's patch list, held in registers one entry ahead of its use
     int           pi = 0;
     u32           nk = pn > 0 ? pkey[tid] : 0xffffffffu;
+    float         nv = pn > 0 ? pval[tid] : 0.0f;
     const char*   base = rowp + (size_t)tid * 4 * ES;
     auto value = [&](u32 bits) {
         if (DT == FTB200_F16) {
@@ -1341,19 +1591,17 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
         return x;
     };
     for (int m0 = 0; m0 < nfull; m0 += UN) {
-        u32 raw[UN][4];
+        uint4 raw[UN];  // 16-bit types use .x / .y only
 #pragma unroll
         for (int uu = 0; uu < UN; ++uu) {
             if (m0 + uu < nfull) {
                 const char* q = base + (size_t)(m0 + uu) * 1024 * ES;
                 if (DT == FTB200_F32) {
-                    const uint4 r = ld_nc_v4(q);
-                    raw[uu][0] = r.x, raw[uu][1] = r.y, raw[uu][2] = r.z, raw[uu][3] = r.w;
+                    raw[uu] = ld_nc_v4(q);
                 }
                 else {
                     const uint2 r = ld_nc_v2(q);
-                    raw[uu][0] = r.x & 0xffffu, raw[uu][1] = r.x >> 16;
-                    raw[uu][2] = r.y & 0xffffu, raw[uu][3] = r.y >> 16;
+                    raw[uu].x = r.x, raw[uu].y = r.y;
                 }
             }
         }
@@ -1361,11 +1609,17 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
         for (int uu = 0; uu < UN; ++uu) {
             const int m = m0 + uu;
             if (m < nfull) {
-                float y0 = value(raw[uu][0]), y1 = value(raw[uu][1]);
-                float y2 = value(raw[uu][2]), y3 = value(raw[uu][3]);
+                float y0, y1, y2, y3;
+                if (DT == FTB200_F32) {
+                    y0 = value(raw[uu].x), y1 = value(raw[uu].y), y2 = value(raw[uu].z), y3 = value(raw[uu].w);
+                }
+                else {
+                    y0 = value(raw[uu].x & 0xffffu), y1 = value(raw[uu].x >> 16);
+                    y2 = value(raw[uu].y & 0xffffu), y3 = value(raw[uu].y >> 16);
+                }
                 if ((int)(nk >> 2) == m) {
                     do {
-                        const float yy = pval[pi * kThreads + tid];
+                        const float yy = nv;
                         const u32   e  = nk & 3u;
                         y0             = e == 0 ? yy : y0;
                         y1             = e == 1 ? yy : y1;
@@ -1373,6 +1627,7 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
                         y3             = e == 3 ? yy : y3;
                         ++pi;
                         nk = pi < pn ? pkey[pi * kThreads + tid] : 0xffffffffu;
+                        nv = pi < pn ? pval[pi * kThreads + tid] : 0.0f;
                     } while ((int)(nk >> 2) == m);
                 }
                 // a column at or below -MAX adds exactly zero, as in the reference's loop
@@ -1538,13 +1793,55 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
 // and only the value class that holds the crossing is collected, to find its J-th column (the
 // reference's stable sort leaves equal probabilities in column order).
 // Returns 1 when the row is finished, 0 when the caller has to take the general path.
+// Dense form of the class count (16-bit logits): every column of the unflagged, fully valid vectors whose
+// ordered key lies within `limit` patterns of the row's largest one is counted, straight from the bit
+// pattern.  Used when a large part of the row lies above the cut, where queueing hits would queue everything.
+template<int DT>
+__device__ __noinline__ void hot_count_dense(const uint4* vp, int jn, const u32* flags, u32 kmax16, u32 limit, u32* hist)
+{
+    constexpr int U   = 4;
+    const int     tid = threadIdx.x;
+    auto count2 = [&](u32 w) {
+        const u32 m  = ((w >> 15) & 0x00010001u) * 0x7fffu;  // per half: 0x7fff when negative
+        const u32 k2 = w ^ (m | 0x80008000u);                // ordered keys of both halves
+        const u32 i0 = kmax16 - (k2 & 0xffffu), i1 = kmax16 - (k2 >> 16);
+        if (i0 < limit) {
+            atomicAdd(&hist[i0], 1u);
+        }
+        if (i1 < limit) {
+            atomicAdd(&hist[i1], 1u);
+        }
+    };
+    for (int jb = 0; jb < jn; jb += kThreads * U) {
+        uint4 q[U];
+        bool  ok[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = jb + u * kThreads + tid;
+            ok[u]       = j < jn && !((flags[j >> 5] >> (j & 31)) & 1u);
+            if (ok[u]) {
+                q[u] = ld_nc_v4(vp + j);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (ok[u]) {
+                count2(q[u].x);
+                count2(q[u].y);
+                count2(q[u].z);
+                count2(q[u].w);
+            }
+        }
+    }
+}
+
 constexpr int kMaxRuns  = 4096;  // runs held in shared memory
 constexpr int kMaxSpecs = 1024;  // special / edge columns above the cut
 
 template<int DT>
 __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O,
                                              float maxv, float denom, float rand_num, float cut0, u32 kmax16,
-                                             bool want_lp)
+                                             bool want_lp, bool dense)
 {
     __shared__ u32   s_ns, s_fail, s_wsum[kWarps], s_ncls;
     __shared__ int   s_c1, s_sel, s_imin, s_imax;
@@ -1573,24 +1870,66 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         s_fail = 0;
     }
     __syncthreads();
-    // pass 3 (L2, filtered): exact count of every bit pattern at or above the cut
+    // The cut in the pattern domain: the smallest ordered key whose value reaches cut0.  Everything at or
+    // above that pattern is counted, so the collected classes are complete down to the value y_c.
+    u32 k_cut = 0;
+    if (!complete) {
+        u32 lo = 0, hi = kmax16;  // value(key) is monotone in the key
+        while (lo < hi) {
+            const u32 mid = (lo + hi) >> 1;
+            if (temp_value<DT>(X, key16_inv(mid), 0) >= cut0) {
+                hi = mid;
+            }
+            else {
+                lo = mid + 1;
+            }
+        }
+        k_cut = lo;
+    }
+    if (kmax16 - k_cut >= (u32)kNB) {
+        return 0;  // the class window does not reach down to the cut
+    }
+    const u32   limit = kmax16 - k_cut + 1u;
+    const float y_c   = complete ? -INFINITY : temp_value<DT>(X, key16_inv(k_cut), 0);
+    // pass 3 (L2): exact count of every bit pattern at or above the cut
     {
-        u32* hist = S.hist;
+        constexpr int EPV = DT == FTB200_F32 ? 4 : 8;
+        u32*          hist = S.hist;
         auto count = [&](int v, float y, u32 raw) {
             if (y > C.neg_max) {
                 const u32 idx = kmax16 - key16(raw);
-                if (idx < (u32)kNB) {
+                if (idx < limit) {
                     atomicAdd(&hist[idx], 1u);
-                }
-                else {
-                    s_fail = 1;
                 }
             }
         };
-        stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return cut0; }, count);
+        if (dense && DT != FTB200_F32) {
+            const int nfull = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / EPV : 0);
+            hot_count_dense<DT>(vec_base<DT>(C), nfull, S.flags, kmax16, limit, hist);
+            // flagged vectors and the vectors that reach past the vocabulary: column by column
+            const uint4* vp = vec_base<DT>(C);
+            for (int j = tid; j < C.nvec; j += kThreads) {
+                const bool sp = (S.flags[j >> 5] >> (j & 31)) & 1u;
+                if (!sp && j < nfull) {
+                    continue;
+                }
+                const uint4 r = ld_nc_v4(vp + j);
+                for (int e = 0; e < EPV; ++e) {
+                    const int v = C.head + j * EPV + e;
+                    if (v < P.vocab && !(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
+                        const u32 raw = raw_bits<DT>(r, e);
+                        count(v, temp_value<DT>(X, raw, v), raw);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        else {
+            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_c; }, count);
+        }
         trace_mark(O.trace, 20);
         // (the filtered stream is done with its hit queue: the list of specials may live there)
-        visit_specials<DT>(P, S, C, cut0, [&](int v, float y) {
+        visit_specials<DT>(P, S, C, y_c, [&](int v, float y) {
             if (y > C.neg_max) {
                 const u32 pos = atomicAdd(&s_ns, 1u);
                 if (pos < (u32)kMaxSpecs) {
@@ -2007,10 +2346,8 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         bool     clash = false;
         for (int i = tid; i < P.hash_slots; i += kThreads) {
             const u32 w = X.hash[i];
-            if (w != kHashEmpty && (int)(w >> 2) < P.vocab) {
-                const int v    = (int)(w >> 2);
-                u32       bits = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
-                clash |= temp_value<DT>(X, bits, v) >= tall;
+            if (w != kHashEmpty) {
+                clash |= S.spre[i] >= tall;
             }
         }
         if (clash) {
@@ -2054,12 +2391,23 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     __syncthreads();
     trace_mark(O.trace, 3);
     if (wid == 0) {
+        const long long c0 = clock64();
         float s = butterfly_block_sum(S.val2, nvt);
+        const long long c1 = clock64();
         if (lane == 0) {
             s_S = s;
+            if (O.trace != nullptr) {
+                O.trace[4 + 24] = (u64)(c1 - c0);
+            }
         }
     }
-    __syncthreads();
+    {
+        const long long c2 = clock64();
+        __syncthreads();
+        if (tid == 0 && O.trace != nullptr) {
+            O.trace[4 + 26] = (u64)(clock64() - c2);
+        }
+    }
     trace_mark(O.trace, 17);
     const float denom = s_S + 1e-6f;
 
@@ -2140,10 +2488,17 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         float       cut_a = b_cut == 0 ? -INFINITY :
                                          maxv - (float)(kNB - b_cut) / (float)kLinScale - 1e-3f * fabsf(maxv) - 1e-3f;
         cut_a             = fmaxf(cut_a, cut_b);
-        if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_a, kraw, want_lp)) {
+        // columns above the provisional cut, from the 1-in-16 sample: a dense row skips the hit queue
+        u32 above = 0;
+        for (int i = tid; i < kNB; i += kThreads) {
+            above += i >= b_cut ? S.hist[i] : 0u;
+        }
+        above            = block_sum_u32(above) * 16u;
+        const bool dense = cut_a <= cut_b || above * 16u > (u32)P.vocab;
+        if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_a, kraw, want_lp, dense)) {
             return;
         }
-        if (cut_b < cut_a && row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_b, kraw, want_lp)) {
+        if (cut_b < cut_a && row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_b, kraw, want_lp, true)) {
             return;
         }
         __syncthreads();
@@ -2452,11 +2807,17 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
     else if (P.topp_states != nullptr && !(P.topp_skip != nullptr && P.topp_skip[r])) {
         mode = 2;
     }
-    RowOut O;
-    O.r      = r;
-    O.end_id = P.end_ids[r];
-    O.id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
-    O.trace  = trace;
+    // The per-row records live in shared memory: the row functions take them by reference, and a
+    // reference to a stack object would turn every field access into a local-memory load.
+    __shared__ RowOut s_O;
+    __shared__ RowCtx s_C;
+    RowOut&           O = s_O;
+    if (tid == 0) {
+        O.r      = r;
+        O.end_id = P.end_ids[r];
+        O.id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
+        O.trace  = trace;
+    }
 
     const bool fin     = P.finished != nullptr ? P.finished[r] != 0 : false;
     const bool want_lp = P.cum_log_probs != nullptr || P.out_log_probs != nullptr;
@@ -2465,11 +2826,13 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
     if (P.vp_out != nullptr) {
         // vocabulary-parallel local pass: candidates only; the merge draws
         if (mode == 1 && !fin) {
-            RowCtx C;
+            RowCtx& C = s_C;
             build_row<DT>(P, S, C, r);
             int k = (int)P.topk_ks[r];
             k     = k < 1 ? 1 : (k > kMaxTopK ? kMaxTopK : k);
-            row_topk<DT>(P, S, C, O, gscratch, k, 0.0f, 1.0f);
+            if (!(P.bias == nullptr && C.inv_t > 0.0f && row_topk2<DT>(P, S, C, O, k, 0.0f, 1.0f))) {
+                row_topk<DT>(P, S, C, O, gscratch, k, 0.0f, 1.0f);
+            }
         }
         else if (tid == 0) {
             P.vp_out[(size_t)r * (P.vp_cap + 1)] = 0;
@@ -2513,7 +2876,7 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
             }
         }
         else {
-            RowCtx C;
+            RowCtx& C = s_C;
             build_row<DT>(P, S, C, r);
             if (mode == 1) {
                 int k = (int)P.topk_ks[r];
@@ -2525,7 +2888,7 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
                 else if (k == 1) {
                     row_argmax<DT>(P, S, C, O);
                 }
-                else {
+                else if (!(P.bias == nullptr && C.inv_t > 0.0f && row_topk2<DT>(P, S, C, O, k, u, top_p))) {
                     row_topk<DT>(P, S, C, O, gscratch, k, u, top_p);
                 }
             }
@@ -2554,16 +2917,19 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int                                s_row;
-    Smem                                          S;
-    S.cand  = (u64*)smem_raw;
-    S.hist  = (u32*)(S.cand + kCap);
-    S.val2  = (float*)(S.hist + kNB);
-    S.flags = (u32*)(S.val2 + 1024);
-    S.hash  = S.flags + P.flag_words;
-    S.spec  = S.hash + P.hash_slots;
-    S.nspec = S.spec + P.hash_slots / 2;
-    S.nhit  = S.nspec + 1;
-    S.hitq  = (unsigned short*)(S.nhit + 3);
+    __shared__ Smem                               s_S;
+    Smem&                                         S = s_S;
+    if (threadIdx.x == 0) {
+        S.cand  = (u64*)smem_raw;
+        S.hist  = (u32*)(S.cand + kCap);
+        S.val2  = (float*)(S.hist + kNB);
+        S.flags = (u32*)(S.val2 + 1024);
+        S.hash  = S.flags + P.flag_words;
+        S.spre  = (float*)(S.hash + P.hash_slots);
+        S.sfin  = S.spre + P.hash_slots;
+        S.nhit  = (u32*)(S.sfin + P.hash_slots);
+        S.hitq  = (unsigned short*)(S.nhit + 4);
+    }
     u64* gscratch = P.scratch + (size_t)blockIdx.x * P.scratch_stride;
     for (;;) {
         __syncthreads();
@@ -2581,10 +2947,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
         u64*      rec = P.trace != nullptr ? P.trace + (size_t)t * kTraceWords : nullptr;
         if (rec != nullptr && threadIdx.x == 0) {
             rec[0] = (u64)r, rec[1] = (u64)blockIdx.x, rec[2] = global_timer_ns();
+            rec[30] = (u64)clock64();
         }
         process_row<DT>(P, S, r, gscratch, rec);
         if (rec != nullptr && threadIdx.x == 0) {
             rec[3] = global_timer_ns();
+            rec[31] = (u64)clock64();
         }
     }
 }
@@ -2605,7 +2973,7 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
     S.cand  = (u64*)smem_raw;
     S.hist  = (u32*)(S.cand + kCap);
     S.val2  = (float*)(S.hist + kNB);
-    S.flags = nullptr, S.hash = nullptr, S.spec = nullptr, S.nspec = nullptr, S.hitq = nullptr, S.nhit = nullptr;
+    S.flags = nullptr, S.hash = nullptr, S.spre = nullptr, S.sfin = nullptr, S.hitq = nullptr, S.nhit = nullptr;
     const int tid = threadIdx.x;
     for (int r = blockIdx.x; r < P.local_batch; r += gridDim.x) {
         __syncthreads();
