@@ -51,6 +51,13 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p)
     return r;
 }
 
+// Add to a counter that is known to live in shared memory.  Through a plain pointer the compiler has to
+// emit a generic-address atomic; this states the address space.
+__device__ __forceinline__ void smem_add(u32* p, u32 v)
+{
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"((u32)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ uint2 ld_nc_v2(const void* p)
 {
     uint2 r;

@@ -276,6 +276,35 @@ __device__ __forceinline__ u32 ge2_mask(u32 pair, u32 thr2)
 }
 
 template<int DT>
+__device__ __forceinline__ u32 le2_mask(u32 pair, u32 thr2)
+{
+    if (DT == FTB200_F16) {
+        return __hle2_mask(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&thr2));
+    }
+    return __hle2_mask(*reinterpret_cast<const __nv_bfloat162*>(&pair),
+                       *reinterpret_cast<const __nv_bfloat162*>(&thr2));
+}
+
+// Smallest raw 16-bit value r such that every column with final value <= thr_y has raw value <= r.
+template<int DT>
+__device__ __forceinline__ u32 raw_ceiling_pair(const KParams& P, const RowCtx& C, float thr_y)
+{
+    float t = thr_y;
+    if (P.apply_temp && t > -FLT_MAX && t < FLT_MAX) {
+        t = t / C.inv_t;
+        t = t + fabsf(t) * (1.0f / 256.0f);
+    }
+    u32 r;
+    if (DT == FTB200_F16) {
+        r = t >= 65504.0f ? 0x7c00u : (u32)__half_as_ushort(__float2half_ru(t));
+    }
+    else {
+        r = t >= 3.38e38f ? 0x7f80u : (u32)__bfloat16_as_ushort(__float2bfloat16_ru(t));
+    }
+    return r | (r << 16);
+}
+
+template<int DT>
 __device__ __forceinline__ u32 max2(u32 a, u32 b)
 {
     if (DT == FTB200_F16) {
@@ -334,38 +363,56 @@ __device__ __noinline__ void stream_all(const KParams& P, const Smem& S, const R
 // whole loop lives in registers.
 constexpr int kHotUnroll = 8;   // 16-byte loads in flight per thread in the register-only loops
 
-template<int DT>
-__device__ __noinline__ void hot_filter(const uint4* vp, int jb, int j1, float thr_y, u32 thr2, float inv, bool temp,
-                                        unsigned short* hitq, u32* qn)
+constexpr int kHitCap   = kThreads * 16;  // entries of the hit queue (16-bit offsets)
+constexpr int kHotBatch = kThreads * kHotUnroll;
+
+// Queues the offsets (relative to jb) of the vectors of [jb, je) that may hold a passing column.  The
+// counter keeps counting past the capacity so that the caller can see an overflow.
+template<int DT, bool BAND = false>
+__device__ __noinline__ void hot_filter(const uint4* vp, int jb, int je, float thr_y, u32 thr2, float inv, bool temp,
+                                        unsigned short* hitq, u32* qn, u32 hi2 = 0)
 {
     const int tid = threadIdx.x;
-    uint4     q[kHotUnroll];
+    for (int j0 = jb; j0 < je; j0 += kHotBatch) {
+        uint4 q[kHotUnroll];
 #pragma unroll
-    for (int u = 0; u < kHotUnroll; ++u) {
-        int j = jb + u * kThreads + tid;
-        if (j < j1) {
-            q[u] = ld_nc_v4(vp + j);
+        for (int u = 0; u < kHotUnroll; ++u) {
+            int j = j0 + u * kThreads + tid;
+            if (j < je) {
+                q[u] = ld_nc_v4(vp + j);
+            }
         }
-    }
 #pragma unroll
-    for (int u = 0; u < kHotUnroll; ++u) {
-        if (jb + u * kThreads + tid < j1) {
-            bool pass;
-            if (DT == FTB200_F32) {
-                float a = __uint_as_float(q[u].x), b = __uint_as_float(q[u].y);
-                float c = __uint_as_float(q[u].z), d = __uint_as_float(q[u].w);
-                if (temp) {
-                    a *= inv, b *= inv, c *= inv, d *= inv;  // the same multiply the exact path uses
+        for (int u = 0; u < kHotUnroll; ++u) {
+            if (j0 + u * kThreads + tid < je) {
+                bool pass;
+                if (DT == FTB200_F32) {
+                    float a = __uint_as_float(q[u].x), b = __uint_as_float(q[u].y);
+                    float c = __uint_as_float(q[u].z), d = __uint_as_float(q[u].w);
+                    if (temp) {
+                        a *= inv, b *= inv, c *= inv, d *= inv;  // the same multiply the exact path uses
+                    }
+                    pass = fmaxf(fmaxf(a, b), fmaxf(c, d)) >= thr_y;
                 }
-                pass = fmaxf(fmaxf(a, b), fmaxf(c, d)) >= thr_y;
-            }
-            else {
-                pass = ((ge2_mask<DT>(q[u].x, thr2) | ge2_mask<DT>(q[u].y, thr2))
-                        | (ge2_mask<DT>(q[u].z, thr2) | ge2_mask<DT>(q[u].w, thr2)))
-                       != 0;
-            }
-            if (pass) {
-                hitq[atomicAdd(qn, 1u)] = (unsigned short)(u * kThreads + tid);
+                else if (BAND) {
+                    // columns inside [thr2, hi2]: both compares have to hold for the same half
+                    pass = (((ge2_mask<DT>(q[u].x, thr2) & le2_mask<DT>(q[u].x, hi2))
+                             | (ge2_mask<DT>(q[u].y, thr2) & le2_mask<DT>(q[u].y, hi2)))
+                            | ((ge2_mask<DT>(q[u].z, thr2) & le2_mask<DT>(q[u].z, hi2))
+                               | (ge2_mask<DT>(q[u].w, thr2) & le2_mask<DT>(q[u].w, hi2))))
+                           != 0;
+                }
+                else {
+                    pass = ((ge2_mask<DT>(q[u].x, thr2) | ge2_mask<DT>(q[u].y, thr2))
+                            | (ge2_mask<DT>(q[u].z, thr2) | ge2_mask<DT>(q[u].w, thr2)))
+                           != 0;
+                }
+                if (pass) {
+                    const u32 pos = atomicAdd(qn, 1u);
+                    if (pos < (u32)kHitCap) {
+                        hitq[pos] = (unsigned short)(j0 - jb + u * kThreads + tid);
+                    }
+                }
             }
         }
     }
@@ -377,9 +424,15 @@ __device__ __noinline__ void hot_filter(const uint4* vp, int jb, int j1, float t
 // Per batch: hot_filter() queues the vectors that may hold a passing column; after a barrier the queued
 // vectors are fetched again (they are still in L1/L2) and handled one per thread, so the rare exact work
 // runs dense instead of divergent.  thr() is read once per batch; a caller may raise it between batches.
+// `span` is the number of vectors filtered per round: the default is one load batch, so that a caller can
+// move its threshold often; a caller with a fixed threshold passes kWholeRow and the row is filtered in one
+// go (a round whose hits do not fit the queue is repeated in single batches).
+constexpr int kWholeRow = 65536;
+
 template<int DT, class Thr, class Hit>
 __device__ __noinline__ void
-stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1, Thr&& thr, Hit&& hit)
+stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1, Thr&& thr, Hit&& hit, int span = kHotBatch,
+                float thr_hi = INFINITY)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int   EPV   = DT == FTB200_F32 ? 4 : 8;
@@ -394,20 +447,40 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
     unsigned short* hitq  = S.hitq;
     u32*            nhit  = S.nhit;
     int             par   = 0;
+    if (!fast) {
+        span = kHotBatch;
+    }
     if (tid == 0) {
         nhit[0] = 0;
         nhit[1] = 0;
     }
     __syncthreads();
-    for (int jb = j0; jb < j1; jb += kThreads * kHotUnroll, par ^= 1) {
+    for (int jb = j0; jb < j1;) {
+        const int   je    = j1 - jb < span ? j1 : jb + span;
         const float thr_y = thr();
         if (fast) {
             const u32 thr2 = DT == FTB200_F32 ? 0u : raw_threshold_pair<DT>(P, C, thr_y);
-            hot_filter<DT>(vp, jb, j1, thr_y, thr2, inv, temp, hitq, nhit + par);
+            if (DT != FTB200_F32 && thr_hi < INFINITY) {
+                // a band of values: the hits of the packed filter are the columns between the two bounds
+                hot_filter<DT, true>(vp, jb, je, thr_y, thr2, inv, temp, hitq, nhit + par, raw_ceiling_pair<DT>(P, C, thr_hi));
+            }
+            else {
+                hot_filter<DT>(vp, jb, je, thr_y, thr2, inv, temp, hitq, nhit + par);
+            }
         }
         __syncthreads();
         // embedding bias or a non-positive temperature: every vector takes the exact path
-        const int n = fast ? (int)nhit[par] : (j1 - jb < kThreads * kHotUnroll ? j1 - jb : kThreads * kHotUnroll);
+        const int n = fast ? (int)nhit[par] : je - jb;
+        if (fast && n > kHitCap) {
+            // more hits than the queue holds: this round again, one load batch at a time
+            __syncthreads();
+            if (tid == 0) {
+                nhit[par] = 0;
+            }
+            span = kHotBatch;
+            __syncthreads();
+            continue;
+        }
         if (tid == 0) {
             nhit[par ^ 1] = 0;
         }
@@ -437,6 +510,8 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
             }
         }
         __syncthreads();
+        jb = je;
+        par ^= 1;
     }
 }
 
@@ -1252,7 +1327,7 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
         }
         __syncthreads();
         for (int i = 0; i < kSlotsPerThread; ++i) {
-            atomicAdd(&hist[slots[i * kThreads + tid] >> 20], 1u);
+            smem_add(&hist[slots[i * kThreads + tid] >> 20], 1u);
         }
         __syncthreads();
         const int b1 = find_from_top([&](int b) { return (double)hist[b]; }, (double)K, nullptr);
@@ -1271,7 +1346,7 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
         for (int i = 0; i < kSlotsPerThread; ++i) {
             const u32 key = slots[i * kThreads + tid];
             if ((key >> 20) == (u32)b1) {
-                atomicAdd(&hist[(key >> 8) & 0xfffu], 1u);
+                smem_add(&hist[(key >> 8) & 0xfffu], 1u);
             }
         }
         __syncthreads();
@@ -1331,7 +1406,7 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
             }
         }
     };
-    stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return thr_y; }, push);
+    stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return thr_y; }, push, kWholeRow);
     trace_mark(O.trace, 3);
     visit_specials<DT>(P, S, C, thr_y, push);
     __syncthreads();
@@ -1354,7 +1429,7 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
     __shared__ u32 s_n, s_ovf;
     constexpr int  EPV = DT == FTB200_F32 ? 4 : 8;
     const int      tid = threadIdx.x;
-    constexpr int  VB  = kThreads * kHotUnroll;
+    constexpr int  VB  = kHotBatch;
 
     auto count_w = [&](int b) { return (double)S.hist[b]; };
     auto thr_of  = [&](int b) { return b < 0 ? 0u : ((u32)b << 20); };
@@ -1374,7 +1449,7 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
     u32  thr  = 0;  // order-preserving key of the current cut; columns below it cannot be in the top k
     auto histo = [&](int v, float y) {
         if (y > C.neg_max) {
-            atomicAdd(&S.hist[fkey(y) >> 20], 1u);
+            smem_add(&S.hist[fkey(y) >> 20], 1u);
         }
     };
     auto push = [&](int v, float y) {
@@ -1395,7 +1470,7 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
         if (y > C.neg_max) {
             u32 key = fkey(y);
             if (key >= thr) {
-                atomicAdd(&S.hist[key >> 20], 1u);
+                smem_add(&S.hist[key >> 20], 1u);
                 u32 pos = atomicAdd(&s_n, 1u);
                 if (pos < (u32)kCap) {
                     cand[pos] = ((u64)(~key) << 32) | (u32)v;
@@ -1494,11 +1569,26 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
 }
 
 // ---- rows that need soft-max probabilities: top-p, and top-k when log-probs are requested -----------
+// The provisional histogram of a soft-max row counts every column within kTopSpan logit units of the row
+// maximum (buckets above kTopBucket) and one column in sixteen of the rest: the few largest columns carry
+// most of the probability mass, and a sample that hits or misses one of them would misplace the cut.
+constexpr int   kTopBucket = kNB - 1 - 4 * kLinScale;
+constexpr float kTopSpan   = 4.0f;
+
 __device__ __forceinline__ int lin_bucket(float y, float maxv)
 {
     int q = (int)((maxv - y) * (float)kLinScale);
     q     = q < 0 ? 0 : (q > kNB - 1 ? kNB - 1 : q);
     return kNB - 1 - q;
+}
+
+// One column into the provisional histogram: always when it lies in the exact region, else when sampled.
+__device__ __forceinline__ void note_column(u32* hist, float y, float maxv, bool sampled)
+{
+    const int b = lin_bucket(y, maxv);
+    if (b > kTopBucket || sampled) {
+        smem_add(&hist[b], 1u);
+    }
 }
 
 // ---- ordered soft-max pass, lean form ----------------------------------------------------------------
@@ -1571,6 +1661,7 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
     constexpr int UN  = 8;
     const int     tid = threadIdx.x, wid = tid >> 5;
     float         a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    const float   ytop = maxv - kTopSpan - 0.02f;  // anything that can land above kTopBucket is at least this
     // head of this thread's patch list, held in registers one entry ahead of its use
     int           pi = 0;
     u32           nk = pn > 0 ? pkey[tid] : 0xffffffffu;
@@ -1636,10 +1727,28 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
                 a2 += round_to_T<DT>(__expf(y2 - maxv));
                 a3 += round_to_T<DT>(__expf(y3 - maxv));
                 if (((m + 2 * wid) & 15) == 0) {  // warp-uniform 1-in-16 sample for the provisional cut
-                    atomicAdd(&hist[lin_bucket(y0, maxv)], y0 > -FLT_MAX ? 1u : 0u);
-                    atomicAdd(&hist[lin_bucket(y1, maxv)], y1 > -FLT_MAX ? 1u : 0u);
-                    atomicAdd(&hist[lin_bucket(y2, maxv)], y2 > -FLT_MAX ? 1u : 0u);
-                    atomicAdd(&hist[lin_bucket(y3, maxv)], y3 > -FLT_MAX ? 1u : 0u);
+                    const int b0 = lin_bucket(y0, maxv), b1 = lin_bucket(y1, maxv);
+                    const int b2 = lin_bucket(y2, maxv), b3 = lin_bucket(y3, maxv);
+                    smem_add(&hist[b0], (y0 > -FLT_MAX && b0 <= kTopBucket) ? 1u : 0u);
+                    smem_add(&hist[b1], (y1 > -FLT_MAX && b1 <= kTopBucket) ? 1u : 0u);
+                    smem_add(&hist[b2], (y2 > -FLT_MAX && b2 <= kTopBucket) ? 1u : 0u);
+                    smem_add(&hist[b3], (y3 > -FLT_MAX && b3 <= kTopBucket) ? 1u : 0u);
+                }
+                if (fmaxf(fmaxf(y0, y1), fmaxf(y2, y3)) >= ytop) {  // rare: a column of the exact region
+                    const int b0 = lin_bucket(y0, maxv), b1 = lin_bucket(y1, maxv);
+                    const int b2 = lin_bucket(y2, maxv), b3 = lin_bucket(y3, maxv);
+                    if (b0 > kTopBucket) {
+                        smem_add(&hist[b0], 1u);
+                    }
+                    if (b1 > kTopBucket) {
+                        smem_add(&hist[b1], 1u);
+                    }
+                    if (b2 > kTopBucket) {
+                        smem_add(&hist[b2], 1u);
+                    }
+                    if (b3 > kTopBucket) {
+                        smem_add(&hist[b3], 1u);
+                    }
                 }
             }
         }
@@ -1734,9 +1843,7 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                             if (y > neg_max) {
                                 float ex = round_to_T<DT>(__expf(y - maxv));
                                 acc[e] += ex;
-                                if (sampled) {
-                                    atomicAdd(&hist[lin_bucket(y, maxv)], 1u);
-                                }
+                                note_column(hist, y, maxv, sampled);
                             }
                         }
                     }
@@ -1746,9 +1853,7 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                             if (y > neg_max) {
                                 float ex = round_to_T<DT>(__expf(y - maxv));
                                 acc[e] += ex;
-                                if (sampled) {
-                                    atomicAdd(&hist[lin_bucket(y, maxv)], 1u);
-                                }
+                                note_column(hist, y, maxv, sampled);
                             }
                         }
                     }
@@ -1771,9 +1876,7 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                         if (y > neg_max) {
                             float ex = round_to_T<DT>(__expf(y - maxv));
                             acc[q] += ex;
-                            if (((vt + v0 / nvt) & 15) == 0) {
-                                atomicAdd(&hist[lin_bucket(y, maxv)], 1u);
-                            }
+                            note_column(hist, y, maxv, ((vt + v0 / nvt) & 15) == 0);
                         }
                     }
                 }
@@ -1797,19 +1900,20 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
 // ordered key lies within `limit` patterns of the row's largest one is counted, straight from the bit
 // pattern.  Used when a large part of the row lies above the cut, where queueing hits would queue everything.
 template<int DT>
-__device__ __noinline__ void hot_count_dense(const uint4* vp, int jn, const u32* flags, u32 kmax16, u32 limit, u32* hist)
+__device__ __noinline__ void hot_count_dense(const uint4* vp, int jn, const u32* flags, u32 kmax16, u32 limit, u32* hist,
+                                             unsigned short* hitq, u32* qn)
 {
-    constexpr int U   = 4;
+    constexpr int U   = 8;
     const int     tid = threadIdx.x;
     auto count2 = [&](u32 w) {
         const u32 m  = ((w >> 15) & 0x00010001u) * 0x7fffu;  // per half: 0x7fff when negative
         const u32 k2 = w ^ (m | 0x80008000u);                // ordered keys of both halves
         const u32 i0 = kmax16 - (k2 & 0xffffu), i1 = kmax16 - (k2 >> 16);
         if (i0 < limit) {
-            atomicAdd(&hist[i0], 1u);
+            smem_add(&hist[i0], 1u);
         }
         if (i1 < limit) {
-            atomicAdd(&hist[i1], 1u);
+            smem_add(&hist[i1], 1u);
         }
     };
     for (int jb = 0; jb < jn; jb += kThreads * U) {
@@ -1818,9 +1922,19 @@ __device__ __noinline__ void hot_count_dense(const uint4* vp, int jn, const u32*
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int j = jb + u * kThreads + tid;
-            ok[u]       = j < jn && !((flags[j >> 5] >> (j & 31)) & 1u);
-            if (ok[u]) {
-                q[u] = ld_nc_v4(vp + j);
+            ok[u]       = false;
+            if (j < jn) {
+                if ((flags[j >> 5] >> (j & 31)) & 1u) {
+                    // a vector with a special column: queued, handled column by column afterwards
+                    const u32 pos = atomicAdd(qn, 1u);
+                    if (pos < (u32)kHitCap) {
+                        hitq[pos] = (unsigned short)j;
+                    }
+                }
+                else {
+                    ok[u] = true;
+                    q[u]  = ld_nc_v4(vp + j);
+                }
             }
         }
 #pragma unroll
@@ -1899,21 +2013,34 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
             if (y > C.neg_max) {
                 const u32 idx = kmax16 - key16(raw);
                 if (idx < limit) {
-                    atomicAdd(&hist[idx], 1u);
+                    smem_add(&hist[idx], 1u);
                 }
             }
         };
         if (dense && DT != FTB200_F32) {
             const int nfull = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / EPV : 0);
-            hot_count_dense<DT>(vec_base<DT>(C), nfull, S.flags, kmax16, limit, hist);
-            // flagged vectors and the vectors that reach past the vocabulary: column by column
-            const uint4* vp = vec_base<DT>(C);
-            for (int j = tid; j < C.nvec; j += kThreads) {
-                const bool sp = (S.flags[j >> 5] >> (j & 31)) & 1u;
-                if (!sp && j < nfull) {
-                    continue;
+            if (tid == 0) {
+                S.nhit[0] = 0;
+            }
+            __syncthreads();
+            hot_count_dense<DT>(vec_base<DT>(C), nfull, S.flags, kmax16, limit, hist, S.hitq, S.nhit);
+            // the vectors that reach past the vocabulary join the queue
+            for (int j = nfull + tid; j < C.nvec; j += kThreads) {
+                const u32 pos = atomicAdd(S.nhit, 1u);
+                if (pos < (u32)kHitCap) {
+                    S.hitq[pos] = (unsigned short)j;
                 }
-                const uint4 r = ld_nc_v4(vp + j);
+            }
+            __syncthreads();
+            const int nq = (int)S.nhit[0];
+            if (nq > kHitCap || C.nvec > 65535) {
+                return 0;
+            }
+            const uint4* vp = vec_base<DT>(C);
+            for (int i = tid; i < nq; i += kThreads) {
+                const int   j  = (int)S.hitq[i];
+                const bool  sp = (S.flags[j >> 5] >> (j & 31)) & 1u;
+                const uint4 r  = ld_nc_v4(vp + j);
                 for (int e = 0; e < EPV; ++e) {
                     const int v = C.head + j * EPV + e;
                     if (v < P.vocab && !(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
@@ -1925,7 +2052,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
             __syncthreads();
         }
         else {
-            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_c; }, count);
+            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_c; }, count, kWholeRow);
         }
         trace_mark(O.trace, 20);
         // (the filtered stream is done with its hit queue: the list of specials may live there)
@@ -2076,6 +2203,9 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     }
     __syncthreads();
     trace_mark(O.trace, 6);
+    if (O.trace != nullptr && tid == 0) {
+        O.trace[4 + 24] = (u64)N | ((u64)(dense ? 1 : 0) << 32) | ((u64)M << 40);
+    }
     const int nch = (int)((N + 255u) / 256u);
     if (nch > 1024 || N == 0) {
         return 0;
@@ -2263,6 +2393,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     if (s_imax >= 0) {
         const u32   k_hi  = kmax16 - (u32)s_imin, k_lo = kmax16 - (u32)s_imax;
         const float y_lo  = temp_value<DT>(X, key16_inv(k_lo), 0);
+        const float y_hi  = temp_value<DT>(X, key16_inv(k_hi), 0);
         auto        member = [&](int v, float y, u32 raw) {
             const u32 k = key16(raw);
             if (k >= k_lo && k <= k_hi) {
@@ -2272,23 +2403,56 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
                 }
             }
         };
-        stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_lo; }, member);
+        stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_lo; }, member, kWholeRow, y_hi);
     }
     __syncthreads();
     const int ncls = (int)s_ncls;
     trace_mark(O.trace, 8);
-    if (ncls > 1024 || J >= ncls) {
+    if (ncls > 2 * kMaxRuns || J >= ncls) {
         return 0;  // an unusually large class of equal values: general path
     }
-    // J-th smallest column of the class
-    for (int a = tid; a < ncls; a += kThreads) {
-        const u32 ca = cls[a];
-        u32       rk = 0;
-        for (int b = 0; b < ncls; ++b) {
-            rk += cls[b] < ca ? 1u : 0u;
+    // J-th smallest column of the class: members are counted per block of columns (reversed, so that the
+    // walk from the top runs over ascending columns), the block holding rank J is found, and only the few
+    // members of that block are ranked against each other.
+    {
+        __shared__ u32 s_blk[512];
+        __shared__ u32 s_nblk;
+        int            shift = 0;
+        while (((P.vocab_padded - 1) >> shift) >= kNB) {
+            ++shift;
         }
-        if ((int)rk == J) {
-            s_sel = (int)ca;
+        for (int i = tid; i < kNB; i += kThreads) {
+            S.hist[i] = 0;
+        }
+        if (tid == 0) {
+            s_nblk = 0;
+        }
+        __syncthreads();
+        for (int a = tid; a < ncls; a += kThreads) {
+            smem_add(&S.hist[kNB - 1 - (int)(cls[a] >> shift)], 1u);
+        }
+        __syncthreads();
+        const int bsel = find_from_top([&](int b) { return (double)S.hist[b]; }, (double)(J + 1), nullptr);
+        u32       before = 0;
+        for (int a = tid; a < ncls; a += kThreads) {
+            const int b = kNB - 1 - (int)(cls[a] >> shift);
+            before += b > bsel ? 1u : 0u;
+            if (b == bsel) {
+                s_blk[atomicAdd(&s_nblk, 1u)] = cls[a];
+            }
+        }
+        before = block_sum_u32(before);
+        const int m  = (int)s_nblk;
+        const int jj = J - (int)before;
+        for (int a = tid; a < m; a += kThreads) {
+            const u32 ca = s_blk[a];
+            int       rk = 0;
+            for (int b = 0; b < m; ++b) {
+                rk += s_blk[b] < ca ? 1 : 0;
+            }
+            if (rk == jj) {
+                s_sel = (int)ca;
+            }
         }
     }
     __syncthreads();
@@ -2391,23 +2555,12 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     __syncthreads();
     trace_mark(O.trace, 3);
     if (wid == 0) {
-        const long long c0 = clock64();
         float s = butterfly_block_sum(S.val2, nvt);
-        const long long c1 = clock64();
         if (lane == 0) {
             s_S = s;
-            if (O.trace != nullptr) {
-                O.trace[4 + 24] = (u64)(c1 - c0);
-            }
         }
     }
-    {
-        const long long c2 = clock64();
-        __syncthreads();
-        if (tid == 0 && O.trace != nullptr) {
-            O.trace[4 + 26] = (u64)(clock64() - c2);
-        }
-    }
+    __syncthreads();
     trace_mark(O.trace, 17);
     const float denom = s_S + 1e-6f;
 
@@ -2425,7 +2578,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
                     atomicMin(&s_argmax, v);
                 }
             };
-            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return maxv; }, first_max);
+            stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return maxv; }, first_max, kWholeRow);
             visit_specials<DT>(P, S, C, maxv, first_max);
             __syncthreads();
             const int argmax = s_argmax;
@@ -2453,17 +2606,38 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     int b_cut;
     {
         int b_est;
+        auto weight = [&](int b) { return b > kTopBucket ? 1.0f : 16.0f; };
         if (is_topp) {
-            const float scale = 16.0f / denom;
-            auto        w     = [&](int b) {
-                const int q = kNB - 1 - b;
-                return (double)S.hist[b] * (double)(__expf(-((float)q + 0.5f) / (float)kLinScale) * scale);
-            };
-            b_est = find_from_top(w, (double)(rand_num * 1.25f + 0.02f), nullptr);
+            const float scale = 1.0f / denom;
+            auto        prob  = [&](int b) { return __expf(-((float)(kNB - 1 - b) + 0.5f) / (float)kLinScale) * scale; };
+            // spread of the estimate: only the sampled buckets contribute, 240 n p^2 each
+            float var = 0.0f;
+            for (int b = tid; b <= kTopBucket; b += kThreads) {
+                const float pb = prob(b);
+                var += 240.0f * (float)S.hist[b] * pb * pb;
+            }
+            {
+                __shared__ float s_var[kWarps];
+                for (int m = 16; m > 0; m >>= 1) {
+                    var += __shfl_xor_sync(0xffffffffu, var, m);
+                }
+                if (lane == 0) {
+                    s_var[wid] = var;
+                }
+                __syncthreads();
+                var = 0.0f;
+                for (int i = 0; i < kWarps; ++i) {
+                    var += s_var[i];
+                }
+                __syncthreads();
+            }
+            const float margin = 3.0f * sqrtf(var) + 0.01f;
+            auto        w      = [&](int b) { return (double)S.hist[b] * (double)(prob(b) * weight(b)); };
+            b_est = find_from_top(w, (double)(rand_num + margin), nullptr);
             trace_mark(O.trace, 19);
         }
         else {
-            auto w = [&](int b) { return 16.0 * (double)S.hist[b]; };
+            auto w = [&](int b) { return (double)weight(b) * (double)S.hist[b]; };
             b_est  = find_from_top(w, 1.25 * (double)k + 64.0, nullptr);
         }
         if (tid == 0) {
@@ -2491,10 +2665,10 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         // columns above the provisional cut, from the 1-in-16 sample: a dense row skips the hit queue
         u32 above = 0;
         for (int i = tid; i < kNB; i += kThreads) {
-            above += i >= b_cut ? S.hist[i] : 0u;
+            above += i >= b_cut ? S.hist[i] * (i > kTopBucket ? 1u : 16u) : 0u;
         }
-        above            = block_sum_u32(above) * 16u;
-        const bool dense = cut_a <= cut_b || above * 16u > (u32)P.vocab;
+        above            = block_sum_u32(above);
+        const bool dense = cut_a <= cut_b || above * 40u > (u32)P.vocab;
         if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_a, kraw, want_lp, dense)) {
             return;
         }
@@ -2521,7 +2695,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
                 if (y > C.neg_max) {
                     const int b = lin_bucket(y, maxv);
                     if (b >= b_cut) {
-                        atomicAdd(&S.hist[b], 1u);
+                        smem_add(&S.hist[b], 1u);
                     }
                 }
             };
