@@ -76,5 +76,25 @@ def build(verbose=False, force=False):
     return LIB
 
 
+def build_shim_driver():
+    """Compile the C++ decode layers (shim/) with their test driver (tests/cpp/shim_driver.cc) against the
+    library; the binary lands next to libftb200.so (same folder, found through its rpath)."""
+    root = os.path.dirname(HERE)
+    out = os.path.join(OUT, "shim_driver")
+    srcs = [os.path.join(root, "tests", "cpp", "shim_driver.cc"), os.path.join(HERE, "shim", "DynamicDecodeLayer.cc")]
+    deps = srcs + [os.path.join(HERE, "shim", "DynamicDecodeLayer.h"), os.path.join(HERE, "shim", "ft_compat.h"), LIB]
+    if os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
+        return out
+    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O2", "-x", "cu"] + srcs + [
+        "-I" + INC, "-I" + os.path.join(HERE, "shim"), "-L" + OUT, "-lftb200", "-Xlinker", "-rpath", "-Xlinker",
+        "$ORIGIN", "-o", out]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("building the shim driver failed")
+    return out
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build_shim_driver())

@@ -58,6 +58,20 @@ __device__ __forceinline__ void smem_add(u32* p, u32 v)
     asm volatile("red.shared.add.u32 [%0], %1;" ::"r"((u32)__cvta_generic_to_shared(p)), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void smem_or(u32* p, u32 v)
+{
+    asm volatile("red.shared.or.b32 [%0], %1;" ::"r"((u32)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ u32 smem_cas(u32* p, u32 expect, u32 want)
+{
+    u32 old;
+    asm volatile("atom.shared.cas.b32 %0, [%1], %2, %3;"
+                 : "=r"(old)
+                 : "r"((u32)__cvta_generic_to_shared(p)), "r"(expect), "r"(want)
+                 : "memory");
+    return old;
+}
+
 __device__ __forceinline__ uint2 ld_nc_v2(const void* p)
 {
     uint2 r;

@@ -75,22 +75,22 @@ static __device__ void hash_insert(const KParams& P, const Smem& S, const RowCtx
     u32 h    = hash_slot(id, P.hash_shift);
     u32 want = ((u32)id << 2) | flag;
     for (int probe = 0; probe < P.hash_slots; ++probe) {
-        u32 old = atomicCAS(&S.hash[h], kHashEmpty, want);
+        u32 old = smem_cas(&S.hash[h], kHashEmpty, want);
         if (old == kHashEmpty) {
             break;
         }
         if ((old >> 2) == (u32)id) {
-            atomicOr(&S.hash[h], flag);
+            smem_or(&S.hash[h], flag);
             break;
         }
         h = (h + 1) & (P.hash_slots - 1);
     }
-    const int epv = P.dtype == FTB200_F32 ? 4 : 8;
+    const int sh  = P.dtype == FTB200_F32 ? 2 : 3;  // log2 of the columns per 16-byte vector
     int       rel = id - C.head;
-    if (rel >= 0 && rel < C.nvec * epv) {
-        int j   = rel / epv;
+    if (rel >= 0 && rel < (C.nvec << sh)) {
+        int j   = rel >> sh;
         u32 bit = 1u << (j & 31);
-        atomicOr(&S.flags[j >> 5], bit);
+        smem_or(&S.flags[j >> 5], bit);
     }
 }
 
@@ -712,6 +712,59 @@ __device__ __noinline__ int find_from_top(W w, double target, double* total_out)
     return r;
 }
 
+// Integer form of find_from_top over plain counts: the largest bucket b whose suffix sum reaches `target`
+// (-1 when the total stays below), and the count strictly above it.
+static __device__ __noinline__ int find_count_from_top(const u32* hist, u32 target, u32* above_out)
+{
+    __shared__ u32 s_part[kWarps];
+    __shared__ int s_found;
+    __shared__ u32 s_above;
+    constexpr int  PER = kNB / kThreads;
+    const int      tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (tid == 0) {
+        s_found = -1;
+        s_above = 0;
+    }
+    u32 c[PER], local = 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        c[i] = hist[kNB - 1 - (tid * PER + i)];
+        local += c[i];
+    }
+    u32 incl = local;
+    for (int off = 1; off < 32; off <<= 1) {
+        const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) {
+            incl += t;
+        }
+    }
+    if (lane == 31) {
+        s_part[wid] = incl;
+    }
+    __syncthreads();
+    u32 base = 0;
+    for (int i = 0; i < wid; ++i) {
+        base += s_part[i];
+    }
+    const u32 excl = base + incl - local;
+    if (excl < target && excl + local >= target) {
+        u32 run = excl;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            if (run < target && run + c[i] >= target) {
+                s_found = kNB - 1 - (tid * PER + i);
+                s_above = run;
+            }
+            run += c[i];
+        }
+    }
+    __syncthreads();
+    const int r = s_found;
+    *above_out  = s_above;
+    __syncthreads();
+    return r;
+}
+
 static __device__ float draw_uniform(curandState_t* states, int row)
 {
     curandState_t st = states[row];
@@ -841,6 +894,65 @@ __device__ __noinline__ void build_row(const KParams& P, const Smem& S, RowCtx& 
         C.neg_max = DT == FTB200_F16 ? -65504.0f : -FLT_MAX;
     }
 
+    const size_t col = (size_t)P.ite * P.local_batch + r;
+    // The global loads of this set-up are issued level by level, all independent ones together, so that a
+    // thread waits for memory two or three times instead of once per token.
+    // level 1: word-list offsets of this thread's bad word, first batch of history ids
+    const int  L        = P.bad_words != nullptr ? P.bad_words_len : 0;
+    const int* wbase    = L > 0 ? (P.bad_words_shared ? P.bad_words : P.bad_words + (size_t)r * 2 * L) : nullptr;
+    const bool has_word = tid < L;  // lists longer than the CTA take the loop at the end
+    int        item_end = -1, item_start = 0;
+    if (has_word) {
+        item_end   = wbase[L + tid];
+        item_start = tid > 0 ? wbase[L + tid - 1] : 0;
+    }
+    constexpr int HB        = 4;
+    const int     input_len = P.apply_rep ? (P.input_lengths != nullptr ? P.input_lengths[r] : P.max_input_len) : 0;
+    const int     nhist     = P.apply_rep ? P.step : 0;
+    int           ids[HB];
+    bool          okh[HB];
+#pragma unroll
+    for (int q = 0; q < HB; ++q) {
+        const int t = q * kThreads + tid;
+        okh[q]      = t < nhist && !(t >= input_len && t < P.max_input_len);
+        ids[q]      = okh[q] ? P.output_ids[(size_t)t * P.batch_size + col] : 0;
+    }
+    // level 2: the tokens of the word and the generated tokens it has to match (ban_bad_words.cu:35-85):
+    // a word bans its last token when the preceding tokens match the tail of the generated sequence;
+    // token 0 can never be banned.
+    int  ban_tok = 0;
+    bool ban     = false;
+    if (has_word && item_end >= 0) {
+        const int item_size = item_end - item_start;
+        ban                 = item_size == 1;
+        ban_tok             = wbase[item_end - 1];
+        if (item_size > 1 && P.step >= item_size - 1) {
+            ban = true;
+            if (item_size <= 4) {
+                int want[3], have[3];
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    const bool in = j < item_size - 1;
+                    want[j]       = in ? wbase[item_start + j] : 0;
+                    have[j]       = in ? P.output_ids[(size_t)(P.step - (item_size - 1) + j) * P.batch_size + col] : 0;
+                }
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    ban = ban && want[j] == have[j];
+                }
+            }
+            else {
+                for (int j = item_size - 2; j >= 0; --j) {
+                    const int prev = P.output_ids[(size_t)(P.step - (item_size - 1) + j) * P.batch_size + col];
+                    if (prev != wbase[item_start + j]) {
+                        ban = false;
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    // (the table is cleared while those loads are in flight)
     for (int i = tid; i < P.hash_slots; i += kThreads) {
         S.hash[i] = kHashEmpty;
     }
@@ -848,47 +960,46 @@ __device__ __noinline__ void build_row(const KParams& P, const Smem& S, RowCtx& 
         S.flags[i] = 0;
     }
     __syncthreads();
-
-    const size_t col = (size_t)P.ite * P.local_batch + r;
     // token history -> repetition / presence penalty (sampling_penalty_kernels.cu:385-410)
-    if (P.apply_rep) {
-        const int input_len = P.input_lengths != nullptr ? P.input_lengths[r] : P.max_input_len;
-        for (int t = tid; t < P.step; t += kThreads) {
-            if (t >= input_len && t < P.max_input_len) {
-                continue;
-            }
-            hash_insert(P, S, C, P.output_ids[(size_t)t * P.batch_size + col], kFlagHist);
+#pragma unroll
+    for (int q = 0; q < HB; ++q) {
+        if (okh[q]) {
+            hash_insert(P, S, C, ids[q], kFlagHist);
         }
     }
-    // bad words (ban_bad_words.cu:35-85): a word bans its last token when the preceding tokens match
-    // the tail of the generated sequence; token 0 can never be banned.
-    if (P.bad_words != nullptr) {
-        const int  L    = P.bad_words_len;
-        const int* base = P.bad_words_shared ? P.bad_words : P.bad_words + (size_t)r * 2 * L;
-        const int* offs = base + L;
-        for (int i = tid; i < L; i += kThreads) {
-            const int item_end = offs[i];
-            if (item_end < 0) {
-                continue;
-            }
-            const int item_start = i > 0 ? offs[i - 1] : 0;
-            const int item_size  = item_end - item_start;
-            bool      ban        = item_size == 1;
-            if (item_size > 1 && P.step >= item_size - 1) {
-                ban = true;
-                for (int j = item_size - 2; j >= 0; --j) {
-                    const int prev = P.output_ids[(size_t)(P.step - (item_size - 1) + j) * P.batch_size + col];
-                    if (prev != base[item_start + j]) {
-                        ban = false;
-                        break;
-                    }
+    for (int t = HB * kThreads + tid; t < nhist; t += kThreads) {
+        if (t >= input_len && t < P.max_input_len) {
+            continue;
+        }
+        hash_insert(P, S, C, P.output_ids[(size_t)t * P.batch_size + col], kFlagHist);
+    }
+    if (ban && 0 < ban_tok && (P.vp_out != nullptr || ban_tok < P.vocab_padded)) {
+        hash_insert(P, S, C, ban_tok, kFlagDead);
+    }
+    // word lists with more entries than the CTA has threads
+    for (int i = tid + kThreads; i < L; i += kThreads) {
+        const int* offs = wbase + L;
+        const int  e1   = offs[i];
+        if (e1 < 0) {
+            continue;
+        }
+        const int s1   = offs[i - 1];
+        const int size = e1 - s1;
+        bool      b    = size == 1;
+        if (size > 1 && P.step >= size - 1) {
+            b = true;
+            for (int j = size - 2; j >= 0; --j) {
+                const int prev = P.output_ids[(size_t)(P.step - (size - 1) + j) * P.batch_size + col];
+                if (prev != wbase[s1 + j]) {
+                    b = false;
+                    break;
                 }
             }
-            if (ban) {
-                const int tok = base[item_end - 1];
-                if (0 < tok && (P.vp_out != nullptr || tok < P.vocab_padded)) {
-                    hash_insert(P, S, C, tok, kFlagDead);
-                }
+        }
+        if (b) {
+            const int tok = wbase[e1 - 1];
+            if (0 < tok && (P.vp_out != nullptr || tok < P.vocab_padded)) {
+                hash_insert(P, S, C, tok, kFlagDead);
             }
         }
     }
@@ -1320,67 +1431,63 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
     u32*      slots = (u32*)S.hitq;  // [kSlots], free again before the filtered pass needs its queue
     u32*      hist  = S.hist;
 
-    // K-th largest slot key, 12 + 12 bits at a time
-    auto kth_slot_key = [&](int K) {
-        for (int i = tid; i < kNB; i += kThreads) {
-            hist[i] = 0;
-        }
-        __syncthreads();
-        for (int i = 0; i < kSlotsPerThread; ++i) {
-            smem_add(&hist[slots[i * kThreads + tid] >> 20], 1u);
-        }
-        __syncthreads();
-        const int b1 = find_from_top([&](int b) { return (double)hist[b]; }, (double)K, nullptr);
-        if (b1 < 0) {
-            return 0u;
-        }
-        u32 above = 0;
-        for (int i = 0; i < kSlotsPerThread; ++i) {
-            above += (slots[i * kThreads + tid] >> 20) > (u32)b1 ? 1u : 0u;
-        }
-        above = block_sum_u32(above);
-        for (int i = tid; i < kNB; i += kThreads) {
-            hist[i] = 0;
-        }
-        __syncthreads();
-        for (int i = 0; i < kSlotsPerThread; ++i) {
-            const u32 key = slots[i * kThreads + tid];
-            if ((key >> 20) == (u32)b1) {
-                smem_add(&hist[(key >> 8) & 0xfffu], 1u);
-            }
-        }
-        __syncthreads();
-        const int b2 = find_from_top([&](int b) { return (double)hist[b]; }, (double)(K - (int)above), nullptr);
-        return ((u32)b1 << 20) | ((u32)(b2 < 0 ? 0 : b2) << 8);
-    };
     auto value_of_key = [&](u32 key) {
         if (DT == FTB200_F32) {
             return temp_value<DT>(X, __float_as_uint(fkey_inv(key)), 0);
         }
         return temp_value<DT>(X, key16_inv(key >> 16), 0);
     };
-    // specials whose value before the penalty reaches the bound: they may occupy slots without being
-    // selectable at that value
-    auto specials_at = [&](float thr_y) {
-        u32 c = 0;
-        for (int i = tid; i < P.hash_slots; i += kThreads) {
-            c += (X.hash[i] != kHashEmpty && S.spre[i] >= thr_y) ? 1u : 0u;
-        }
-        return (int)block_sum_u32(c);
-    };
-    u32 key = kth_slot_key(k);
-    if (key == 0u) {
+    // K-th largest slot key, 12 + 12 bits at a time.  The special columns may occupy slots without being
+    // selectable at their raw value: those whose value before the penalty reaches the (coarse) bound are
+    // added to K before the final selection.
+    for (int i = tid; i < kNB; i += kThreads) {
+        hist[i] = 0;
+    }
+    __syncthreads();
+    for (int i = 0; i < kSlotsPerThread; ++i) {
+        smem_add(&hist[slots[i * kThreads + tid] >> 20], 1u);
+    }
+    __syncthreads();
+    u32 above = 0;
+    int b1    = find_count_from_top(hist, (u32)k, &above);
+    if (b1 < 0) {
         return false;
     }
-    const int s1 = specials_at(value_of_key(key));
-    if (s1 > 0) {
-        if (k + s1 > 1600) {
-            return false;
+    int K = k;
+    {
+        const float coarse = value_of_key((u32)b1 << 20);  // lower edge of the bucket: a bound below the K-th key
+        u32         c      = 0;
+        for (int i = tid; i < P.hash_slots; i += kThreads) {
+            c += (X.hash[i] != kHashEmpty && S.spre[i] >= coarse) ? 1u : 0u;
         }
-        key = kth_slot_key(k + s1);
-        if (key == 0u) {
-            return false;
+        const int s1 = (int)block_sum_u32(c);
+        if (s1 > 0) {
+            K = k + s1;
+            if (K > 1600) {
+                return false;
+            }
+            b1 = find_count_from_top(hist, (u32)K, &above);
+            if (b1 < 0) {
+                return false;
+            }
         }
+    }
+    for (int i = tid; i < kNB; i += kThreads) {
+        hist[i] = 0;
+    }
+    __syncthreads();
+    for (int i = 0; i < kSlotsPerThread; ++i) {
+        const u32 key = slots[i * kThreads + tid];
+        if ((key >> 20) == (u32)b1) {
+            smem_add(&hist[(key >> 8) & 0xfffu], 1u);
+        }
+    }
+    __syncthreads();
+    u32       above2 = 0;
+    const int b2     = find_count_from_top(hist, (u32)K - above, &above2);
+    const u32 key    = ((u32)b1 << 20) | ((u32)(b2 < 0 ? 0 : b2) << 8);
+    if (key == 0u) {
+        return false;
     }
     const float thr_y = value_of_key(key);
     trace_mark(O.trace, 2);

@@ -1,0 +1,104 @@
+// C++ classes with FasterTransformer's names and interface for the decode step, implemented on the
+// libftb200 C ABI (include/ftb200.h).  They replace, one for one:
+//   DynamicDecodeLayer<T>     layers/DynamicDecodeLayer.h:58-75
+//   TopKSamplingLayer<T>      layers/sampling_layers/TopKSamplingLayer.h:55-71
+//   TopPSamplingLayer<T>      layers/sampling_layers/TopPSamplingLayer.h:64-81
+//   OnlineBeamSearchLayer<T>  layers/beam_search_layers/OnlineBeamSearchLayer.h:44-62
+// Same constructor arguments, same setup()/forward() signatures, same TensorMap keys, dtypes and
+// placement, same exception types (std::runtime_error with the "[FT][ERROR]" prefix, std::domain_error
+// for k outside [1, 1024]).  T is float, half or __nv_bfloat16.
+//
+// Inside a FasterTransformer checkout compile with -DFTB200_WITH_FT_HEADERS: the project's own Tensor,
+// TensorMap and IAllocator are used.  Elsewhere the stand-ins of ft_compat.h are.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#ifdef FTB200_WITH_FT_HEADERS
+#include "src/fastertransformer/utils/Tensor.h"
+#include "src/fastertransformer/utils/allocator.h"
+namespace fastertransformer {
+class cublasMMWrapper;
+}
+#else
+#include "ft_compat.h"
+#endif
+
+namespace fastertransformer {
+
+namespace ftb200_detail {
+class DecodeCore;  // dtype-erased state and logic shared by the four class templates
+}
+
+template<typename T>
+class DynamicDecodeLayer {
+public:
+    DynamicDecodeLayer(size_t vocab_size, size_t vocab_size_padded, int end_id, cudaStream_t stream,
+                       cublasMMWrapper* cublas_wrapper, IAllocator* allocator, bool is_free_buffer_after_forward,
+                       cudaDeviceProp* cuda_device_prop);
+    ~DynamicDecodeLayer();
+    DynamicDecodeLayer(DynamicDecodeLayer const& other);
+
+    void setup(const size_t batch_size, const size_t beam_width, TensorMap* runtime_args);
+    void forward(TensorMap* output_tensors, TensorMap* input_tensors);
+    void forward(std::unordered_map<std::string, Tensor>* output_tensors,
+                 const std::unordered_map<std::string, Tensor>* input_tensors);
+
+private:
+    std::unique_ptr<ftb200_detail::DecodeCore> core_;
+};
+
+// The two sampling layers used on their own (without the dispatcher): each owns its curand states and
+// samples the rows its runtime arguments select; the other half of the argument block stays empty.
+template<typename T>
+class TopKSamplingLayer {
+public:
+    TopKSamplingLayer(size_t max_batch_size, size_t vocab_size, size_t vocab_size_padded, int end_id, size_t top_k,
+                      unsigned long long random_seed, float temperature, float len_penalty, float repetition_penalty,
+                      cudaStream_t stream, cublasMMWrapper* cublas_wrapper, IAllocator* allocator,
+                      bool is_free_buffer_after_forward);
+    ~TopKSamplingLayer();
+    void setup(const size_t batch_size, const size_t beam_width, TensorMap* runtime_args);
+    void forward(TensorMap* output_tensors, TensorMap* input_tensors);
+
+private:
+    std::unique_ptr<ftb200_detail::DecodeCore> core_;
+};
+
+template<typename T>
+class TopPSamplingLayer {
+public:
+    TopPSamplingLayer(size_t max_batch_size, size_t vocab_size, size_t vocab_size_padded, int end_id, float top_p,
+                      unsigned long long random_seed, float temperature, float len_penalty, float repetition_penalty,
+                      cudaStream_t stream, cublasMMWrapper* cublas_wrapper, IAllocator* allocator,
+                      bool is_free_buffer_after_forward, cudaDeviceProp* cuda_device_prop);
+    ~TopPSamplingLayer();
+    void setup(const size_t batch_size, const size_t beam_width, TensorMap* runtime_args);
+    void forward(TensorMap* output_tensors, TensorMap* input_tensors);
+
+private:
+    std::unique_ptr<ftb200_detail::DecodeCore> core_;
+};
+
+template<typename T>
+class OnlineBeamSearchLayer {
+public:
+    OnlineBeamSearchLayer(size_t max_batch_size, size_t head_num, size_t size_per_head, size_t beam_width,
+                          size_t vocab_size, size_t vocab_size_padded, int end_id, float diversity_rate,
+                          float temperature, float len_penalty, float repetition_penalty, cudaStream_t stream,
+                          cublasMMWrapper* cublas_wrapper, IAllocator* allocator, bool is_free_buffer_after_forward);
+    ~OnlineBeamSearchLayer();
+    void setup(const size_t batch_size, TensorMap* runtime_args);
+    void forward(TensorMap* output_tensors, TensorMap* input_tensors);
+
+private:
+    std::unique_ptr<ftb200_detail::DecodeCore> core_;
+};
+
+}  // namespace fastertransformer
