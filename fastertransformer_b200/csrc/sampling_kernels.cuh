@@ -1010,8 +1010,15 @@ __device__ __noinline__ void build_row(const KParams& P, const Smem& S, RowCtx& 
         }
     }
     __syncthreads();
-    // Values of the special columns, fetched once per row with all loads of a thread in flight together:
-    // every later visit of the specials reads shared memory only.
+}
+
+// Values of the special columns (before and after penalty / ban), fetched with all loads of a thread in
+// flight together; every later visit of the specials reads shared memory only.  Called after the row's
+// first streaming pass, when the row sits in L2 and the scattered 2-byte reads no longer go to DRAM.
+template<int DT>
+__device__ __noinline__ void fetch_specials(const KParams& P, const Smem& S, const RowCtx& C)
+{
+    const int tid = threadIdx.x;
     {
         const Xf      X  = make_xf(P, S, C);
         constexpr int SB = 8;
@@ -1271,6 +1278,7 @@ __device__ __noinline__ void row_argmax(const KParams& P, const Smem& S, const R
     const int jseed = C.nvec < kThreads ? C.nvec : kThreads;
     stream_filtered<DT>(P, S, C, 0, jseed, running, consider);
     stream_filtered<DT>(P, S, C, jseed, C.nvec, running, consider);
+    fetch_specials<DT>(P, S, C);
     visit_specials<DT>(P, S, C, running(), consider);
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -1423,7 +1431,7 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
         }
         trace_mark(O.trace, 0);
         hot_slotmax<DT>(vec_base<DT>(C), nfull0, (u32*)S.hitq);
-        __syncthreads();
+        fetch_specials<DT>(P, S, C);
         trace_mark(O.trace, 1);
     }
     const Xf  X     = make_xf(P, S, C);
@@ -1538,6 +1546,7 @@ __device__ __noinline__ void row_topk(const KParams& P, const Smem& S, const Row
     const int      tid = threadIdx.x;
     constexpr int  VB  = kHotBatch;
 
+    fetch_specials<DT>(P, S, C);  // (a second fetch after the two-pass path gave up costs little: the row is in L2)
     auto count_w = [&](int b) { return (double)S.hist[b]; };
     auto thr_of  = [&](int b) { return b < 0 ? 0u : ((u32)b << 20); };
 
@@ -2604,6 +2613,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     trace_mark(O.trace, 0);
     u32   kraw = 0;
     float tall = stream_max<DT>(P, S, C, true, &kraw);
+    fetch_specials<DT>(P, S, C);
     trace_mark(O.trace, 1);
     {
         // largest value and largest 16-bit pattern (as an ordered key) in one reduction
