@@ -1028,11 +1028,13 @@ __device__ __noinline__ void fetch_specials(const KParams& P, const Smem& S, con
             for (int q = 0; q < SB; ++q) {
                 const int i = i0 + q * kThreads;
                 w[q]        = i < P.hash_slots ? S.hash[i] : kHashEmpty;
-                bits[q]     = 0;
-                if (w[q] != kHashEmpty && (int)(w[q] >> 2) < P.vocab) {
-                    const int v = (int)(w[q] >> 2);
-                    bits[q] = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
-                }
+            }
+#pragma unroll
+            for (int q = 0; q < SB; ++q) {
+                // unconditional loads (column 0 stands in for an empty slot): all eight are in flight together
+                const bool use = w[q] != kHashEmpty && (int)(w[q] >> 2) < P.vocab;
+                const int  v   = use ? (int)(w[q] >> 2) : 0;
+                bits[q] = DT == FTB200_F32 ? __ldg((const u32*)C.rowp + v) : (u32)__ldg((const unsigned short*)C.rowp + v);
             }
 #pragma unroll
             for (int q = 0; q < SB; ++q) {
