@@ -560,9 +560,87 @@ __device__ __forceinline__ u32 key16_inv(u32 k)
     return (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
 }
 
+// Per-thread maxima of eight disjoint column subsets ("slots"), see the two-pass top-k below.
+constexpr int kSlotsPerThread = 8;
+constexpr int kSlots          = kSlotsPerThread * kThreads;
+
+template<int DT>
+__device__ __forceinline__ void hot_slotmax_body(const uint4* vp, int jn, u32* slots)
+{
+    const int tid = threadIdx.x;
+    if (DT == FTB200_F32) {
+        float a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            a[i] = -INFINITY;
+        }
+        for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
+            uint4 q[kHotUnroll];
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                const int j = jb + u * kThreads + tid;
+                if (j < jn) {
+                    q[u] = ld_nc_v4(vp + j);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                if (jb + u * kThreads + tid < jn) {
+                    const int h = (u & 1) * 4;
+                    a[h + 0]    = fmaxf(a[h + 0], __uint_as_float(q[u].x));
+                    a[h + 1]    = fmaxf(a[h + 1], __uint_as_float(q[u].y));
+                    a[h + 2]    = fmaxf(a[h + 2], __uint_as_float(q[u].z));
+                    a[h + 3]    = fmaxf(a[h + 3], __uint_as_float(q[u].w));
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            slots[i * kThreads + tid] = fkey(a[i]);
+        }
+    }
+    else {
+        const u32 ninf = DT == FTB200_F16 ? 0xfc00fc00u : 0xff80ff80u;
+        u32       a0 = ninf, a1 = ninf, a2 = ninf, a3 = ninf;
+        for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
+            uint4 q[kHotUnroll];
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                const int j = jb + u * kThreads + tid;
+                if (j < jn) {
+                    q[u] = ld_nc_v4(vp + j);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kHotUnroll; ++u) {
+                if (jb + u * kThreads + tid < jn) {
+                    a0 = max2<DT>(a0, q[u].x);
+                    a1 = max2<DT>(a1, q[u].y);
+                    a2 = max2<DT>(a2, q[u].z);
+                    a3 = max2<DT>(a3, q[u].w);
+                }
+            }
+        }
+        slots[0 * kThreads + tid] = key16(a0 & 0xffffu) << 16;
+        slots[1 * kThreads + tid] = key16(a0 >> 16) << 16;
+        slots[2 * kThreads + tid] = key16(a1 & 0xffffu) << 16;
+        slots[3 * kThreads + tid] = key16(a1 >> 16) << 16;
+        slots[4 * kThreads + tid] = key16(a2 & 0xffffu) << 16;
+        slots[5 * kThreads + tid] = key16(a2 >> 16) << 16;
+        slots[6 * kThreads + tid] = key16(a3 & 0xffffu) << 16;
+        slots[7 * kThreads + tid] = key16(a3 >> 16) << 16;
+    }
+}
+
+template<int DT>
+__device__ __noinline__ void hot_slotmax(const uint4* vp, int jn, u32* slots)
+{
+    hot_slotmax_body<DT>(vp, jn, slots);
+}
+
 template<int DT>
 __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const RowCtx& C, bool include_flagged,
-                                         u32* raw_key_max = nullptr)
+                                         u32* raw_key_max = nullptr, u32* slots = nullptr)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int EPV   = DT == FTB200_F32 ? 4 : 8;
@@ -576,6 +654,18 @@ __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const 
     const int     jfast = fast ? nfull : 0;
     if (jfast > 0) {
         // temperature is monotone for inv_t > 0: the largest raw value gives the largest final value
+        if (DT != FTB200_F32 && slots != nullptr) {
+            // same pass, but the eight per-thread subset maxima are kept (ordered keys << 16)
+            hot_slotmax<DT>(vp, jfast, slots);
+            u32 km = 0;
+            for (int i = 0; i < kSlotsPerThread; ++i) {
+                const u32 k = slots[i * kThreads + tid] >> 16;
+                km          = k > km ? k : km;
+            }
+            kraw = km;
+            best = temp_value<DT>(X, key16_inv(km), 0);
+        }
+        else {
         const u32 m = hot_max<DT>(vp, jfast);
         if (DT == FTB200_F32) {
             const float raw = __uint_as_float(m);
@@ -585,6 +675,7 @@ __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const 
             best = fmaxf(temp_value<DT>(X, m & 0xffffu, 0), temp_value<DT>(X, m >> 16, 0));
             const u32 ka = key16(m & 0xffffu), kb = key16(m >> 16);
             kraw         = ka > kb ? ka : kb;
+        }
         }
     }
 #pragma unroll 1
@@ -1340,83 +1431,6 @@ static __device__ __noinline__ void topk_tail(const KParams& P, const Smem& S, c
 // the largest columns of a row almost always sit in different slots.  Pass 2 (L2) collects the columns at
 // or above that bound, which are then sorted and drawn from.  Special columns are counted separately
 // (their final value is not the raw one), and the collected set is checked to hold at least k columns.
-constexpr int kSlotsPerThread = 8;
-constexpr int kSlots          = kSlotsPerThread * kThreads;
-
-template<int DT>
-__device__ __forceinline__ void hot_slotmax_body(const uint4* vp, int jn, u32* slots)
-{
-    const int tid = threadIdx.x;
-    if (DT == FTB200_F32) {
-        float a[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            a[i] = -INFINITY;
-        }
-        for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
-            uint4 q[kHotUnroll];
-#pragma unroll
-            for (int u = 0; u < kHotUnroll; ++u) {
-                const int j = jb + u * kThreads + tid;
-                if (j < jn) {
-                    q[u] = ld_nc_v4(vp + j);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kHotUnroll; ++u) {
-                if (jb + u * kThreads + tid < jn) {
-                    const int h = (u & 1) * 4;
-                    a[h + 0]    = fmaxf(a[h + 0], __uint_as_float(q[u].x));
-                    a[h + 1]    = fmaxf(a[h + 1], __uint_as_float(q[u].y));
-                    a[h + 2]    = fmaxf(a[h + 2], __uint_as_float(q[u].z));
-                    a[h + 3]    = fmaxf(a[h + 3], __uint_as_float(q[u].w));
-                }
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            slots[i * kThreads + tid] = fkey(a[i]);
-        }
-    }
-    else {
-        const u32 ninf = DT == FTB200_F16 ? 0xfc00fc00u : 0xff80ff80u;
-        u32       a0 = ninf, a1 = ninf, a2 = ninf, a3 = ninf;
-        for (int jb = 0; jb < jn; jb += kThreads * kHotUnroll) {
-            uint4 q[kHotUnroll];
-#pragma unroll
-            for (int u = 0; u < kHotUnroll; ++u) {
-                const int j = jb + u * kThreads + tid;
-                if (j < jn) {
-                    q[u] = ld_nc_v4(vp + j);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kHotUnroll; ++u) {
-                if (jb + u * kThreads + tid < jn) {
-                    a0 = max2<DT>(a0, q[u].x);
-                    a1 = max2<DT>(a1, q[u].y);
-                    a2 = max2<DT>(a2, q[u].z);
-                    a3 = max2<DT>(a3, q[u].w);
-                }
-            }
-        }
-        slots[0 * kThreads + tid] = key16(a0 & 0xffffu) << 16;
-        slots[1 * kThreads + tid] = key16(a0 >> 16) << 16;
-        slots[2 * kThreads + tid] = key16(a1 & 0xffffu) << 16;
-        slots[3 * kThreads + tid] = key16(a1 >> 16) << 16;
-        slots[4 * kThreads + tid] = key16(a2 & 0xffffu) << 16;
-        slots[5 * kThreads + tid] = key16(a2 >> 16) << 16;
-        slots[6 * kThreads + tid] = key16(a3 & 0xffffu) << 16;
-        slots[7 * kThreads + tid] = key16(a3 >> 16) << 16;
-    }
-}
-
-template<int DT>
-__device__ __noinline__ void hot_slotmax(const uint4* vp, int jn, u32* slots)
-{
-    hot_slotmax_body<DT>(vp, jn, slots);
-}
-
 // Returns false when the row has to take the general one-pass path (too many specials, a candidate set
 // that does not fit, a bound that the special columns invalidate).
 template<int DT>
@@ -1701,10 +1715,10 @@ __device__ __forceinline__ int lin_bucket(float y, float maxv)
 }
 
 // One column into the provisional histogram: always when it lies in the exact region, else when sampled.
-__device__ __forceinline__ void note_column(u32* hist, float y, float maxv, bool sampled)
+__device__ __forceinline__ void note_column(u32* hist, float y, float maxv, bool sampled, bool exact_top)
 {
     const int b = lin_bucket(y, maxv);
-    if (b > kTopBucket || sampled) {
+    if (b > kTopBucket ? exact_top : sampled) {
         smem_add(&hist[b], 1u);
     }
 }
@@ -1771,7 +1785,7 @@ __device__ __noinline__ bool build_patches(const KParams& P, const Smem& S, cons
     return true;
 }
 
-template<int DT, bool TEMP>
+template<int DT, bool TEMP, bool EXACT_TOP>
 __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv, float inv_t, __half inv_t_h,
                                         const u32* pkey, const float* pval, int pn, u32* hist, float* acc_out)
 {
@@ -1852,7 +1866,7 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
                     smem_add(&hist[b2], (y2 > -FLT_MAX && b2 <= kTopBucket) ? 1u : 0u);
                     smem_add(&hist[b3], (y3 > -FLT_MAX && b3 <= kTopBucket) ? 1u : 0u);
                 }
-                if (fmaxf(fmaxf(y0, y1), fmaxf(y2, y3)) >= ytop) {  // rare: a column of the exact region
+                if (EXACT_TOP && fmaxf(fmaxf(y0, y1), fmaxf(y2, y3)) >= ytop) {  // rare: a column of the exact region
                     const int b0 = lin_bucket(y0, maxv), b1 = lin_bucket(y1, maxv);
                     const int b2 = lin_bucket(y2, maxv), b3 = lin_bucket(y3, maxv);
                     if (b0 > kTopBucket) {
@@ -1879,7 +1893,8 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
 // (kernels/sampling_topp_kernels.cu:1331-1334), plus the bucket counts.  The per-virtual-thread partial
 // sums land in S.val2[0..nvt).
 template<int DT>
-__device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, const RowCtx& C, float maxv, int nvt, u64* dbg = nullptr)
+__device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, const RowCtx& C, float maxv, int nvt, u64* dbg,
+                                           bool exact_top)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int ES  = DT == FTB200_F32 ? 4 : 2;
@@ -1903,10 +1918,18 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                 trace_mark(dbg, 12);
                 const int pn = (int)pcnt[tid];
                 if (P.apply_temp) {
-                    pass2_lean<DT, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                    if (exact_top) {
+                        pass2_lean<DT, true, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                    }
+                    else {
+                        pass2_lean<DT, true, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                    }
+                }
+                else if (exact_top) {
+                    pass2_lean<DT, false, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
                 }
                 else {
-                    pass2_lean<DT, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                    pass2_lean<DT, false, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
                 }
                 mstart = nfull;
                 trace_mark(dbg, 13);
@@ -1961,7 +1984,7 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                             if (y > neg_max) {
                                 float ex = round_to_T<DT>(__expf(y - maxv));
                                 acc[e] += ex;
-                                note_column(hist, y, maxv, sampled);
+                                note_column(hist, y, maxv, sampled, exact_top);
                             }
                         }
                     }
@@ -1971,7 +1994,7 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                             if (y > neg_max) {
                                 float ex = round_to_T<DT>(__expf(y - maxv));
                                 acc[e] += ex;
-                                note_column(hist, y, maxv, sampled);
+                                note_column(hist, y, maxv, sampled, exact_top);
                             }
                         }
                     }
@@ -1994,7 +2017,7 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                         if (y > neg_max) {
                             float ex = round_to_T<DT>(__expf(y - maxv));
                             acc[q] += ex;
-                            note_column(hist, y, maxv, ((vt + v0 / nvt) & 15) == 0);
+                            note_column(hist, y, maxv, ((vt + v0 / nvt) & 15) == 0, exact_top);
                         }
                     }
                 }
@@ -2613,8 +2636,14 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         s_redo = 0;
     }
     trace_mark(O.trace, 0);
-    u32   kraw = 0;
-    float tall = stream_max<DT>(P, S, C, true, &kraw);
+    u32        kraw       = 0;
+    const bool have_slots = DT != FTB200_F32 && packed_ok<DT>(P, C);  // the max pass also leaves the slot maxima
+    if (have_slots) {
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            ((u32*)S.hitq)[i * kThreads + tid] = 0;  // lowest key: a row too short for the vector pass leaves it
+        }
+    }
+    float      tall       = stream_max<DT>(P, S, C, true, &kraw, have_slots ? (u32*)S.hitq : nullptr);
     fetch_specials<DT>(P, S, C);
     trace_mark(O.trace, 1);
     {
@@ -2669,8 +2698,22 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         S.hist[i] = 0;
     }
     __syncthreads();
+    if (have_slots) {
+        // exact part of the provisional histogram: the slot maxima within kTopSpan of the row maximum.  A large
+        // column that shares its slot with a larger one is missed, which only makes the cut more generous.
+        const Xf   X     = make_xf(P, S, C);
+        const u32* slots = (const u32*)S.hitq;
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            const float y = temp_value<DT>(X, key16_inv(slots[i * kThreads + tid] >> 16), 0);
+            const int   b = lin_bucket(y, maxv);
+            if (b > kTopBucket && y > C.neg_max) {
+                smem_add(&S.hist[b], 1u);
+            }
+        }
+        __syncthreads();
+    }
     const int nvt = P.vocab < 1024 ? P.vocab : 1024;  // blockDim of addBiasSoftMax (:1364)
-    softmax_pass2<DT>(P, S, C, maxv, nvt, O.trace);
+    softmax_pass2<DT>(P, S, C, maxv, nvt, O.trace, !have_slots);
     __syncthreads();
     trace_mark(O.trace, 3);
     if (wid == 0) {
