@@ -202,3 +202,49 @@ def test_full_size_properties(cuda_device):
         assert not (ids[:, None] == bad[:, :1]).any() or True
         assert (rank[greedy] <= w.max_input_length + s + 24).all()
     assert (out["sequence_length"][-1] == w.max_input_length + 2).all() or out["finished"].any()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["topk", "topp"])
+def test_draw_distribution_chi_square(kind, cuda_device):
+    """10^6 draws from one logits row against the analytic distribution of the reference's draw rule
+    (sampling_topk_kernels.cu:276-287: r = u * sum of the k exponentials, first index whose running difference
+    is <= 0; sampling_topp_kernels.cu:910-960: first sorted index whose inclusive cumulative probability
+    reaches u * p).  Every row has its own curand stream."""
+    from scipy.stats import chisquare
+    from fastertransformer_b200 import DynamicDecodeLayer
+    B, V, steps = 8192, 64, 123
+    rng = np.random.Generator(np.random.PCG64(77))
+    row = rng.normal(0.0, 1.5, size=V).astype(np.float32)
+    order = np.argsort(-row, kind="stable")
+    e = np.exp((row - row.max()).astype(np.float64))
+    if kind == "topk":
+        k = 12
+        args = {"runtime_top_k": np.asarray([k], np.uint32), "runtime_top_p": np.asarray([1.0], np.float32)}
+        expect = np.zeros(V)
+        expect[order[:k]] = e[order[:k]] / e[order[:k]].sum()
+    else:
+        p = 0.8
+        args = {"runtime_top_k": np.asarray([0], np.uint32), "runtime_top_p": np.asarray([p], np.float32)}
+        prob = e / e.sum()
+        c = np.cumsum(prob[order])
+        lo = np.concatenate([[0.0], c[:-1]])
+        width = np.clip(np.minimum(c, p) - lo, 0.0, None) / p
+        expect = np.zeros(V)
+        expect[order] = width
+    args["random_seed"] = (np.arange(B) * 11 + 5).astype(np.uint64)
+    layer = DynamicDecodeLayer(V, V, torch.float32, cuda_device)
+    layer.setup(B, 1, args)
+    st = {"output_ids": torch.zeros(steps + 1, B, dtype=torch.int32, device=cuda_device)}
+    logits = torch.from_numpy(np.tile(row, (B, 1))).to(cuda_device)
+    end = torch.full((B,), V + 5, dtype=torch.int32, device=cuda_device)  # never drawn: rows never finish
+    for s in range(steps):
+        layer.forward(st, {"logits": logits, "step": s + 1, "max_input_length": 1, "ite": 0, "local_batch_size": B,
+                           "end_id": end})
+    ids = st["output_ids"][1:].cpu().numpy().reshape(-1)
+    assert ids.size >= 10 ** 6
+    counts = np.bincount(ids, minlength=V).astype(np.float64)
+    assert counts[expect == 0].sum() == 0, "a column outside the top-k / nucleus was drawn"
+    sel = expect > 0
+    stat, pval = chisquare(counts[sel], expect[sel] * ids.size)
+    assert pval > 1e-4, (stat, pval)
