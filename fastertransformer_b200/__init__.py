@@ -9,7 +9,8 @@ entry point without the built library raises ImportError: there is no CPU fallba
 _LAZY = {
     "lib": "._lib", "FtbError": "._lib", "SamplingParams": "._lib", "check": "._lib",
     "BeamParams": "._lib", "BeamHyps": "._lib",
-    "DynamicDecodeLayer": ".decode_layer",
+    "DynamicDecodeLayer": ".decode_layer", "DynamicDecodeOp": ".th_decode_op",
+    "VocabParallelSampler": ".vocab_parallel",
 }
 
 

@@ -1,0 +1,116 @@
+"""The cases of the reference's own test of its torch op (tests/unittests/th_op/test_th_decode_op.py: minimum
+length at sampling and at beam search, the id sequence under repetition / presence penalty), re-driven through
+fastertransformer_b200.th_decode_op.DynamicDecodeOp with the same positional argument lists."""
+import itertools
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+VOCAB, END_ID = 1024, 0
+
+
+def _vec(batch, value, dtype, cpu):
+    if value is None:
+        return None
+    return value * torch.ones(batch, dtype=dtype, device="cpu" if cpu else "cuda")
+
+
+def run_decode(batch_size=4, beam_width=1, max_input_length=4, gen_length=3, top_k=None, top_p=None, temperature=None,
+               repetition_penalty=None, presence_penalty=None, min_length=None, len_penalty=None,
+               beam_search_diversity_rate=None, random_seed=None, logit_fn=None, use_random_input_tokens=True):
+    from fastertransformer_b200.th_decode_op import DynamicDecodeOp
+    op = DynamicDecodeOp(VOCAB, VOCAB, 1, 1, torch.float)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ite, lbs, L = 0, batch_size, max_input_length + gen_length
+    eos = _vec(batch_size, END_ID, torch.int, False)
+    a = dict(top_ks=_vec(batch_size, top_k, torch.int, True), top_ps=_vec(batch_size, top_p, torch.float, True),
+             temps=_vec(batch_size, temperature, torch.float, True),
+             reps=_vec(batch_size, repetition_penalty, torch.float, True),
+             pres=_vec(batch_size, presence_penalty, torch.float, True), mins=_vec(batch_size, min_length, torch.int, True),
+             lens=_vec(batch_size, len_penalty, torch.float, True),
+             divs=_vec(batch_size, beam_search_diversity_rate, torch.float, True),
+             seeds=_vec(batch_size, random_seed, torch.int64, True))
+    if beam_width > 1:
+        parent_ids = torch.zeros(L, batch_size * beam_width, dtype=torch.int32, device=dev)
+        cache = torch.zeros(2, batch_size, beam_width, L, dtype=torch.int32, device=dev)
+        cum = torch.zeros(batch_size * beam_width, device=dev)
+    else:
+        parent_ids = cache = cum = None
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    if use_random_input_tokens:
+        tokens = torch.randint(1, VOCAB, (batch_size, max_input_length), dtype=torch.int, device=dev, generator=g)
+    else:
+        tokens = torch.ones(batch_size, max_input_length, dtype=torch.int, device=dev)
+    in_len = torch.randint(1, max_input_length + 1, (batch_size,), dtype=torch.int, device=dev, generator=g)
+    in_len[0] = max_input_length
+    steps = torch.arange(0, max_input_length, device=dev).unsqueeze(0).tile(batch_size, 1)
+    tokens[in_len.unsqueeze(1) <= steps] = END_ID
+    tokens = tokens.repeat(1, beam_width).view(batch_size * beam_width, -1)
+    in_len = in_len.view(-1, 1).repeat(1, beam_width).view(-1)
+    op.setup(batch_size, beam_width, a["top_ks"], a["top_ps"], a["temps"], a["reps"], a["pres"], a["mins"], a["lens"],
+             a["divs"], a["seeds"], None, None, None)
+    finished = torch.zeros_like(in_len).bool()
+    seq_len = (max_input_length - 1) * torch.ones_like(in_len)
+    out_ids = torch.zeros(L, batch_size * beam_width, dtype=torch.int32, device=dev)
+    out_ids[:max_input_length] = tokens.T
+    src = tgt = None
+    for step in range(max_input_length, L):
+        if cache is not None:
+            s = (step - max_input_length) % 2
+            src, tgt = cache[s], cache[1 - s]
+        logits = (torch.randn(batch_size, beam_width, VOCAB, device=dev, generator=g) if logit_fn is None
+                  else logit_fn(batch_size, beam_width, dev, g))
+        stop = op.forward(logits, step, max_input_length, ite, lbs, eos, a["top_ks"], a["top_ps"], a["temps"], a["reps"],
+                          a["pres"], a["mins"], a["lens"], a["divs"], None, None, None, None, in_len, None, None, None, src,
+                          out_ids.view(-1, batch_size, beam_width), finished, seq_len, cum, None, parent_ids, tgt)
+        if bool(stop):
+            break
+    return dict(output_token_ids=out_ids.T, output_sequence_lengths=seq_len + 1)
+
+
+def _eos_most_probable(batch, beam, dev, g):
+    logits = torch.randn(batch, beam, VOCAB, device=dev, generator=g)
+    logits[..., END_ID] = logits.max(dim=-1)[0] + 1
+    return logits
+
+
+@pytest.mark.parametrize("tc,method", list(itertools.product(
+    [dict(batch_size=4, max_input_length=4, min_length=2, gen_length=4),
+     dict(batch_size=4, max_input_length=4, min_length=32, gen_length=64),
+     dict(batch_size=2048, max_input_length=6, min_length=4, gen_length=8)],   # batch exceeds 1024
+    [dict(top_k=1, top_p=0.0), dict(top_k=0, top_p=0.8)])))
+def test_min_length_correctness_at_sampling(tc, method):
+    out = run_decode(beam_width=1, logit_fn=_eos_most_probable, **tc, **method)
+    assert bool((out["output_sequence_lengths"] >= tc["max_input_length"] + tc["min_length"]).all())
+
+
+@pytest.mark.parametrize("tc", [dict(batch_size=4, beam_width=2, max_input_length=4, min_length=2, gen_length=4),
+                                dict(batch_size=1024, beam_width=2, max_input_length=4, min_length=4, gen_length=8),
+                                dict(batch_size=4, beam_width=60, max_input_length=4, min_length=4, gen_length=8)])
+def test_min_length_correctness_at_beamsearch(tc):
+    out = run_decode(logit_fn=_eos_most_probable, **tc)
+    assert bool((out["output_sequence_lengths"] >= tc["max_input_length"] + tc["min_length"]).all())
+
+
+def _descending_three(batch, beam, dev, g):
+    # token v-1 is the most probable unless penalised: the expected ids are v-1, v-2, v-3, v-1, v-1, ...
+    logits = torch.zeros(batch, beam, VOCAB, device=dev)
+    logits[..., VOCAB - 1], logits[..., VOCAB - 2], logits[..., VOCAB - 3] = 2.0, 1.8, 1.6
+    return logits
+
+
+@pytest.mark.parametrize("tc,method", list(itertools.product(
+    [dict(batch_size=4, max_input_length=4, repetition_penalty=2), dict(batch_size=2048, max_input_length=4, repetition_penalty=2),
+     dict(batch_size=4, max_input_length=4, presence_penalty=0.5), dict(batch_size=4, max_input_length=4, presence_penalty=1.0),
+     dict(batch_size=2048, max_input_length=4, presence_penalty=0.5)],
+    [dict(top_k=1, top_p=0.0), dict(beam_width=2)])))
+def test_repetition_penalty_correctness(tc, method):
+    gen = 5
+    beam = method.get("beam_width", 1)
+    expect = (VOCAB - 1) * torch.ones(tc["batch_size"] * beam, gen, dtype=torch.int32)
+    expect[:, 1], expect[:, 2] = VOCAB - 2, VOCAB - 3
+    out = run_decode(gen_length=gen, use_random_input_tokens=False, logit_fn=_descending_three, **tc, **method)
+    got = out["output_token_ids"][:, tc["max_input_length"]:]
+    assert bool((expect.to(got.device) == got).all())
