@@ -1314,9 +1314,24 @@ static __device__ __noinline__ void topk_finish(const KParams& P, const Smem& S,
     else {
         const u32 bs1 = P.max_top_k <= 16 ? 128 : 256;
         const u32 bs2 = P.max_top_k <= 32 ? 128 : 256;
-        for (int i = tid; i < lo; i += kThreads) {
-            u32 c = (u32)(sorted[i] & 0xffffffffu);
-            atomicAdd(&s_lane_base[(c / bs1) & 7u], 1u);
+        {
+            // per-thread counts packed 8 x 8 bits (a thread sees at most kCap / kThreads entries), one atomic
+            // per lane value and warp
+            const int sh1   = bs1 == 128 ? 7 : 8;
+            u64       packd = 0;
+            for (int i = tid; i < lo; i += kThreads) {
+                const u32 c = (u32)(sorted[i] & 0xffffffffu);
+                packd += 1ull << (8 * ((c >> sh1) & 7u));
+            }
+            for (int l = 0; l < 8; ++l) {
+                u32 cnt = (u32)(packd >> (8 * l)) & 0xffu;
+                for (int m = 16; m > 0; m >>= 1) {
+                    cnt += __shfl_xor_sync(0xffffffffu, cnt, m);
+                }
+                if ((tid & 31) == 0 && cnt != 0) {
+                    atomicAdd(&s_lane_base[l], cnt);
+                }
+            }
         }
         __syncthreads();
         col = resolve_topk_class(sorted + lo, hi - lo, pick - lo, k, (int)bs1, (int)bs2, s_lane_base);
@@ -1383,14 +1398,115 @@ __device__ __noinline__ void row_argmax(const KParams& P, const Smem& S, const R
     __syncthreads();
 }
 
+// Candidates (~key(value) << 32 | column) into value-descending order.  Up to half the candidate area a
+// counting sort on the leading key bits does it in two sweeps (the other half receives the result); buckets
+// that hold more than one distinct key - possible when the keys span more than 4096 values - are finished by
+// a small sort each.  Larger sets take the bitonic network in place.  Returns where the sorted entries are.
+static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, int n)
+{
+    __shared__ u32 s_w[kWarps];
+    __shared__ u32 s_bits[kNB / 32];
+    const int      tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (n > kCap / 2 || cand != S.cand || n < 64) {
+        group_sort_u64(cand, n, tid, kThreads, CtaSync());
+        __syncthreads();
+        return cand;
+    }
+    u64* dst = cand + kCap / 2;
+    u32  kmin = 0xffffffffu, kmax = 0;
+    for (int i = tid; i < n; i += kThreads) {
+        const u32 k = (u32)(cand[i] >> 32);
+        kmin        = k < kmin ? k : kmin;
+        kmax        = k > kmax ? k : kmax;
+    }
+    kmin = ~(u32)block_max_u64((u64)(~kmin));
+    kmax = (u32)block_max_u64((u64)kmax);
+    int shift = 0;
+    while (((kmax - kmin) >> shift) >= (u32)kNB) {
+        ++shift;
+    }
+    u32* hist = S.hist;
+    for (int i = tid; i < kNB; i += kThreads) {
+        hist[i] = 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += kThreads) {
+        smem_add(&hist[((u32)(cand[i] >> 32) - kmin) >> shift], 1u);
+    }
+    __syncthreads();
+    {
+        // exclusive scan, ascending buckets: hist becomes the scatter cursor
+        constexpr int PER = kNB / kThreads;
+        u32           c[PER], mine = 0;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            c[i] = hist[tid * PER + i];
+            mine += c[i];
+        }
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        if (lane == 31) {
+            s_w[wid] = incl;
+        }
+        __syncthreads();
+        u32 base = 0;
+        for (int i = 0; i < wid; ++i) {
+            base += s_w[i];
+        }
+        u32 at = base + incl - mine;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            hist[tid * PER + i] = at;
+            at += c[i];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += kThreads) {
+        const u64 e = cand[i];
+        dst[atomicAdd(&hist[((u32)(e >> 32) - kmin) >> shift], 1u)] = e;
+    }
+    __syncthreads();
+    if (shift > 0) {
+        // a bucket with two different keys next to each other has to be ordered
+        for (int i = tid; i < kNB / 32; i += kThreads) {
+            s_bits[i] = 0;
+        }
+        __syncthreads();
+        for (int i = tid + 1; i < n; i += kThreads) {
+            const u32 ka = (u32)(dst[i - 1] >> 32), kb = (u32)(dst[i] >> 32);
+            const u32 ba = (ka - kmin) >> shift, bb = (kb - kmin) >> shift;
+            if (ba == bb && ka != kb) {
+                atomicOr(&s_bits[bb >> 5], 1u << (bb & 31));
+            }
+        }
+        __syncthreads();
+        for (int j = wid; j < kNB / 32; j += kWarps) {
+            u32 word = s_bits[j];  // the same for every lane of the warp
+            while (word != 0) {
+                const u32 b  = (u32)j * 32u + (u32)(__ffs(word) - 1);
+                const u32 hi = hist[b];  // cursor after the scatter = end of the bucket
+                const u32 lo = b == 0 ? 0u : hist[b - 1];
+                group_sort_u64(dst + lo, (int)(hi - lo), lane, 32, WarpSync());
+                word &= word - 1;
+            }
+        }
+        __syncthreads();
+    }
+    return dst;
+}
+
 // Common end of the top-k rows: sort the candidates (value descending), then either hand them to the
 // vocabulary-parallel exchange or draw.
 static __device__ __noinline__ void topk_tail(const KParams& P, const Smem& S, const RowOut& O, u64* cand, int n, int k, float u,
                                               float top_p)
 {
     const int tid = threadIdx.x;
-    group_sort_u64(cand, n, tid, kThreads, CtaSync());
-    __syncthreads();
+    cand          = sort_candidates(S, cand, n);
     if (P.vp_out != nullptr) {
         // Vocabulary-parallel local pass: hand over every column whose value reaches this shard's k-th
         // value, whole tie class included.  The global k-th value cannot be smaller than a shard's, so
@@ -1528,7 +1644,16 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
     u64* cand = S.cand;
     auto push = [&](int v, float y) {
         if (y > C.neg_max) {
-            const u32 pos = atomicAdd(&s_n, 1u);
+            // one atomic per warp: the lanes that arrive here together take consecutive positions
+            const u32 act  = __activemask();
+            const int lead = __ffs(act) - 1;
+            const int lane = threadIdx.x & 31;
+            u32       base = 0;
+            if (lane == lead) {
+                base = atomicAdd(&s_n, (u32)__popc(act));
+            }
+            base          = __shfl_sync(act, base, lead);
+            const u32 pos = base + (u32)__popc(act & ((1u << lane) - 1u));
             if (pos < (u32)kCap) {
                 cand[pos] = ((u64)(~fkey(y)) << 32) | (u32)v;
             }
