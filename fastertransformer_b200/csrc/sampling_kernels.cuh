@@ -864,31 +864,6 @@ static __device__ float draw_uniform(curandState_t* states, int row)
     return u;
 }
 
-// The reference's blockReduceSum over blockDim = nvt threads (reduce_kernel_utils.cuh:73-103), applied to
-// the per-thread partial sums held in `partial[0..nvt)`.  Executed by warp 0.
-static __device__ float butterfly_block_sum(const float* partial, int nvt)
-{
-    const int lane   = threadIdx.x & 31;
-    const int nwarps = (nvt + 31) / 32;
-    float     mine   = 0.0f;
-    for (int w = 0; w < nwarps; ++w) {
-        int   i = w * 32 + lane;
-        float v = i < nvt ? partial[i] : 0.0f;
-        for (int m = 16; m > 0; m >>= 1) {
-            v = v + __shfl_xor_sync(0xffffffffu, v, m);
-        }
-        if (lane == w) {
-            mine = v;
-        }
-    }
-    // second stage: threads with threadIdx < blockDim/32.f read shared[lane], others 0
-    float v = ((float)lane < (float)nvt / 32.f) ? mine : 0.0f;
-    for (int m = 16; m > 0; m >>= 1) {
-        v = v + __shfl_xor_sync(0xffffffffu, v, m);
-    }
-    return v;
-}
-
 template<int DT>
 __device__ __forceinline__ float round_to_T(float x)
 {
@@ -2698,16 +2673,15 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
             smem_add(&S.hist[kNB - 1 - (int)(cls[a] >> shift)], 1u);
         }
         __syncthreads();
-        const int bsel = find_from_top([&](int b) { return (double)S.hist[b]; }, (double)(J + 1), nullptr);
         u32       before = 0;
+        const int bsel   = find_count_from_top(S.hist, (u32)(J + 1), &before);
         for (int a = tid; a < ncls; a += kThreads) {
             const int b = kNB - 1 - (int)(cls[a] >> shift);
-            before += b > bsel ? 1u : 0u;
             if (b == bsel) {
                 s_blk[atomicAdd(&s_nblk, 1u)] = cls[a];
             }
         }
-        before = block_sum_u32(before);
+        __syncthreads();
         const int m  = (int)s_nblk;
         const int jj = J - (int)before;
         for (int a = tid; a < m; a += kThreads) {
@@ -2841,10 +2815,32 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     softmax_pass2<DT>(P, S, C, maxv, nvt, O.trace, !have_slots);
     __syncthreads();
     trace_mark(O.trace, 3);
-    if (wid == 0) {
-        float s = butterfly_block_sum(S.val2, nvt);
-        if (lane == 0) {
-            s_S = s;
+    {
+        // the reference's blockReduceSum (reduce_kernel_utils.cuh:73-103) over nvt partial sums: every
+        // 32-value butterfly is independent, so the warps of the CTA share them; warp 0 then runs the second
+        // stage over the per-warp results (threads with threadIdx < blockDim / 32.f read their warp's result,
+        // the others 0)
+        __shared__ float s_vw[32];
+        const int        nvw = (nvt + 31) / 32;
+        for (int w = wid; w < nvw; w += kWarps) {
+            const int i = w * 32 + lane;
+            float     v = i < nvt ? S.val2[i] : 0.0f;
+            for (int m = 16; m > 0; m >>= 1) {
+                v = v + __shfl_xor_sync(0xffffffffu, v, m);
+            }
+            if (lane == 0) {
+                s_vw[w] = v;
+            }
+        }
+        __syncthreads();
+        if (wid == 0) {
+            float v = ((float)lane < (float)nvt / 32.f) ? s_vw[lane] : 0.0f;
+            for (int m = 16; m > 0; m >>= 1) {
+                v = v + __shfl_xor_sync(0xffffffffu, v, m);
+            }
+            if (lane == 0) {
+                s_S = v;
+            }
         }
     }
     __syncthreads();
