@@ -58,6 +58,17 @@ __device__ __forceinline__ void smem_add(u32* p, u32 v)
     asm volatile("red.shared.add.u32 [%0], %1;" ::"r"((u32)__cvta_generic_to_shared(p)), "r"(v) : "memory");
 }
 
+// The same on a 32-bit shared-memory address.
+__device__ __forceinline__ void reds_add(u32 addr, u32 v)
+{
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ u32 lds_u32(u32 addr)
+{
+    u32 v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void smem_or(u32* p, u32 v)
 {
     asm volatile("red.shared.or.b32 [%0], %1;" ::"r"((u32)__cvta_generic_to_shared(p)), "r"(v) : "memory");

@@ -1887,8 +1887,10 @@ __device__ __noinline__ bool build_patches(const KParams& P, const Smem& S, cons
 
 template<int DT, bool TEMP, bool EXACT_TOP>
 __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv, float inv_t, __half inv_t_h,
-                                        const u32* pkey, const float* pval, int pn, u32* hist, float* acc_out)
+                                        u32 pkey, u32 pval, int pn, u32 hist, float* acc_out)
 {
+    // pkey, pval, hist: 32-bit shared-memory addresses (one register each, ld.shared / red.shared without a
+    // generic-to-shared conversion per access)
     constexpr int ES  = DT == FTB200_F32 ? 4 : 2;
     constexpr int UN  = 8;
     const int     tid = threadIdx.x, wid = tid >> 5;
@@ -1896,8 +1898,8 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
     const float   ytop = maxv - kTopSpan - 0.02f;  // anything that can land above kTopBucket is at least this
     // head of this thread's patch list, held in registers one entry ahead of its use
     int           pi = 0;
-    u32           nk = pn > 0 ? pkey[tid] : 0xffffffffu;
-    float         nv = pn > 0 ? pval[tid] : 0.0f;
+    u32           nk = pn > 0 ? lds_u32(pkey + 4u * tid) : 0xffffffffu;
+    float         nv = pn > 0 ? __uint_as_float(lds_u32(pval + 4u * tid)) : 0.0f;
     const char*   base = rowp + (size_t)tid * 4 * ES;
     auto value = [&](u32 bits) {
         if (DT == FTB200_F16) {
@@ -1949,8 +1951,8 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
                         y2             = e == 2 ? yy : y2;
                         y3             = e == 3 ? yy : y3;
                         ++pi;
-                        nk = pi < pn ? pkey[pi * kThreads + tid] : 0xffffffffu;
-                        nv = pi < pn ? pval[pi * kThreads + tid] : 0.0f;
+                        nk = pi < pn ? lds_u32(pkey + 4u * (u32)(pi * kThreads + tid)) : 0xffffffffu;
+                        nv = pi < pn ? __uint_as_float(lds_u32(pval + 4u * (u32)(pi * kThreads + tid))) : 0.0f;
                     } while ((int)(nk >> 2) == m);
                 }
                 // a column at or below -MAX adds exactly zero, as in the reference's loop
@@ -1961,25 +1963,25 @@ __device__ __noinline__ void pass2_lean(const char* rowp, int nfull, float maxv,
                 if (((m + 2 * wid) & 15) == 0) {  // warp-uniform 1-in-16 sample for the provisional cut
                     const int b0 = lin_bucket(y0, maxv), b1 = lin_bucket(y1, maxv);
                     const int b2 = lin_bucket(y2, maxv), b3 = lin_bucket(y3, maxv);
-                    smem_add(&hist[b0], (y0 > -FLT_MAX && b0 <= kTopBucket) ? 1u : 0u);
-                    smem_add(&hist[b1], (y1 > -FLT_MAX && b1 <= kTopBucket) ? 1u : 0u);
-                    smem_add(&hist[b2], (y2 > -FLT_MAX && b2 <= kTopBucket) ? 1u : 0u);
-                    smem_add(&hist[b3], (y3 > -FLT_MAX && b3 <= kTopBucket) ? 1u : 0u);
+                    reds_add(hist + 4u * (u32)b0, (y0 > -FLT_MAX && b0 <= kTopBucket) ? 1u : 0u);
+                    reds_add(hist + 4u * (u32)b1, (y1 > -FLT_MAX && b1 <= kTopBucket) ? 1u : 0u);
+                    reds_add(hist + 4u * (u32)b2, (y2 > -FLT_MAX && b2 <= kTopBucket) ? 1u : 0u);
+                    reds_add(hist + 4u * (u32)b3, (y3 > -FLT_MAX && b3 <= kTopBucket) ? 1u : 0u);
                 }
                 if (EXACT_TOP && fmaxf(fmaxf(y0, y1), fmaxf(y2, y3)) >= ytop) {  // rare: a column of the exact region
                     const int b0 = lin_bucket(y0, maxv), b1 = lin_bucket(y1, maxv);
                     const int b2 = lin_bucket(y2, maxv), b3 = lin_bucket(y3, maxv);
                     if (b0 > kTopBucket) {
-                        smem_add(&hist[b0], 1u);
+                        reds_add(hist + 4u * (u32)b0, 1u);
                     }
                     if (b1 > kTopBucket) {
-                        smem_add(&hist[b1], 1u);
+                        reds_add(hist + 4u * (u32)b1, 1u);
                     }
                     if (b2 > kTopBucket) {
-                        smem_add(&hist[b2], 1u);
+                        reds_add(hist + 4u * (u32)b2, 1u);
                     }
                     if (b3 > kTopBucket) {
-                        smem_add(&hist[b3], 1u);
+                        reds_add(hist + 4u * (u32)b3, 1u);
                     }
                 }
             }
@@ -2019,17 +2021,21 @@ __device__ __noinline__ void softmax_pass2(const KParams& P, const Smem& S, cons
                 const int pn = (int)pcnt[tid];
                 if (P.apply_temp) {
                     if (exact_top) {
-                        pass2_lean<DT, true, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                        pass2_lean<DT, true, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, (u32)__cvta_generic_to_shared(pkey), (u32)__cvta_generic_to_shared(pval), pn,
+                                                    (u32)__cvta_generic_to_shared(hist), acc);
                     }
                     else {
-                        pass2_lean<DT, true, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                        pass2_lean<DT, true, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, (u32)__cvta_generic_to_shared(pkey), (u32)__cvta_generic_to_shared(pval), pn,
+                                                    (u32)__cvta_generic_to_shared(hist), acc);
                     }
                 }
                 else if (exact_top) {
-                    pass2_lean<DT, false, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                    pass2_lean<DT, false, true>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, (u32)__cvta_generic_to_shared(pkey), (u32)__cvta_generic_to_shared(pval), pn,
+                                                    (u32)__cvta_generic_to_shared(hist), acc);
                 }
                 else {
-                    pass2_lean<DT, false, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, pkey, pval, pn, hist, acc);
+                    pass2_lean<DT, false, false>(rowp, nfull, maxv, C.inv_t, C.inv_t_h, (u32)__cvta_generic_to_shared(pkey), (u32)__cvta_generic_to_shared(pval), pn,
+                                                    (u32)__cvta_generic_to_shared(hist), acc);
                 }
                 mstart = nfull;
                 trace_mark(dbg, 13);
