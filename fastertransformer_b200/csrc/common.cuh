@@ -90,13 +90,20 @@ __device__ __forceinline__ uint2 ld_nc_v2(const void* p)
     return r;
 }
 
+// Tells the compiler that a pointer loaded from a structure points into shared memory, so that it emits
+// ld.shared / st.shared instead of generic accesses (every pointer of the kernel's shared-memory map qualifies).
+#define FTB_ASSUME_SHARED(p) __builtin_assume(__isShared(p))
+
 // ---- in-place ascending sort of u64 keys by a cooperating thread group ---------------------------
 // Bitonic network in its "all ascending" form (first sub-step of every merge compares mirrored
 // positions), which tolerates any n: positions >= n behave as +infinity and are never touched.
 // `sync` is __syncthreads for a whole CTA or __syncwarp for one warp.
-template<class Sync>
+template<class Sync, bool SMEM = false>
 __device__ __forceinline__ void group_sort_u64(u64* a, int n, int tid, int nthr, Sync sync)
 {
+    if (SMEM) {
+        FTB_ASSUME_SHARED(a);
+    }
     if (n < 2) {
         return;
     }

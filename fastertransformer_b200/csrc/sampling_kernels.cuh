@@ -72,15 +72,19 @@ static __device__ void hash_insert(const KParams& P, const Smem& S, const RowCtx
     if (id < 0 || id >= P.vocab_padded) {
         return;
     }
+    u32* const hash  = S.hash;
+    u32* const flags = S.flags;
+    FTB_ASSUME_SHARED(hash);
+    FTB_ASSUME_SHARED(flags);
     u32 h    = hash_slot(id, P.hash_shift);
     u32 want = ((u32)id << 2) | flag;
     for (int probe = 0; probe < P.hash_slots; ++probe) {
-        u32 old = smem_cas(&S.hash[h], kHashEmpty, want);
+        u32 old = smem_cas(&hash[h], kHashEmpty, want);
         if (old == kHashEmpty) {
             break;
         }
         if ((old >> 2) == (u32)id) {
-            smem_or(&S.hash[h], flag);
+            smem_or(&hash[h], flag);
             break;
         }
         h = (h + 1) & (P.hash_slots - 1);
@@ -90,13 +94,14 @@ static __device__ void hash_insert(const KParams& P, const Smem& S, const RowCtx
     if (rel >= 0 && rel < (C.nvec << sh)) {
         int j   = rel >> sh;
         u32 bit = 1u << (j & 31);
-        smem_or(&S.flags[j >> 5], bit);
+        smem_or(&flags[j >> 5], bit);
     }
 }
 
 struct Xf;
 __device__ __forceinline__ u32 hash_lookup_raw(const u32* hash, int shift, int mask, int id)
 {
+    FTB_ASSUME_SHARED(hash);
     u32 h = hash_slot(id, shift);
     for (int probe = 0; probe <= mask; ++probe) {
         u32 v = hash[h];
@@ -372,6 +377,8 @@ template<int DT, bool BAND = false>
 __device__ __noinline__ void hot_filter(const uint4* vp, int jb, int je, float thr_y, u32 thr2, float inv, bool temp,
                                         unsigned short* hitq, u32* qn, u32 hi2 = 0)
 {
+    FTB_ASSUME_SHARED(hitq);
+    FTB_ASSUME_SHARED(qn);
     const int tid = threadIdx.x;
     for (int j0 = jb; j0 < je; j0 += kHotBatch) {
         uint4 q[kHotUnroll];
@@ -446,6 +453,9 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
     const u32*      flags = S.flags;
     unsigned short* hitq  = S.hitq;
     u32*            nhit  = S.nhit;
+    FTB_ASSUME_SHARED(flags);
+    FTB_ASSUME_SHARED(hitq);
+    FTB_ASSUME_SHARED(nhit);
     int             par   = 0;
     if (!fast) {
         span = kHotBatch;
@@ -567,6 +577,7 @@ constexpr int kSlots          = kSlotsPerThread * kThreads;
 template<int DT>
 __device__ __forceinline__ void hot_slotmax_body(const uint4* vp, int jn, u32* slots)
 {
+    FTB_ASSUME_SHARED(slots);
     const int tid = threadIdx.x;
     if (DT == FTB200_F32) {
         float a[8];
@@ -713,6 +724,9 @@ __device__ __noinline__ void visit_specials(const KParams& P, const Smem& S, con
     const int     tid = threadIdx.x;
     const char*   rowp = C.rowp;
     const int     nslots = P.hash_slots;
+    const float*  sfin   = S.sfin;
+    FTB_ASSUME_SHARED(sfin);
+    FTB_ASSUME_SHARED(X.hash);
 #pragma unroll 1
     for (int i = tid; i < nslots; i += kThreads) {
         const u32 w = X.hash[i];
@@ -720,7 +734,7 @@ __device__ __noinline__ void visit_specials(const KParams& P, const Smem& S, con
             continue;
         }
         const int   v = (int)(w >> 2);
-        const float y = S.sfin[i];
+        const float y = sfin[i];
         if (y >= thr_y) {
             f(v, y);
         }
@@ -812,6 +826,7 @@ static __device__ __noinline__ int find_count_from_top(const u32* hist, u32 targ
     __shared__ u32 s_above;
     constexpr int  PER = kNB / kThreads;
     const int      tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    FTB_ASSUME_SHARED(hist);
     if (tid == 0) {
         s_found = -1;
         s_above = 0;
@@ -1088,12 +1103,18 @@ __device__ __noinline__ void fetch_specials(const KParams& P, const Smem& S, con
     {
         const Xf      X  = make_xf(P, S, C);
         constexpr int SB = 8;
+        u32* const    hash = S.hash;
+        float* const  spre = S.spre;
+        float* const  sfin = S.sfin;
+        FTB_ASSUME_SHARED(hash);
+        FTB_ASSUME_SHARED(spre);
+        FTB_ASSUME_SHARED(sfin);
         for (int i0 = tid; i0 < P.hash_slots; i0 += kThreads * SB) {
             u32 w[SB], bits[SB];
 #pragma unroll
             for (int q = 0; q < SB; ++q) {
                 const int i = i0 + q * kThreads;
-                w[q]        = i < P.hash_slots ? S.hash[i] : kHashEmpty;
+                w[q]        = i < P.hash_slots ? hash[i] : kHashEmpty;
             }
 #pragma unroll
             for (int q = 0; q < SB; ++q) {
@@ -1111,8 +1132,8 @@ __device__ __noinline__ void fetch_specials(const KParams& P, const Smem& S, con
                         pre = temp_value<DT>(X, bits[q], (int)(w[q] >> 2));
                         fin = special_value<DT>(X, pre, w[q] & 3u);
                     }
-                    S.spre[i] = pre;
-                    S.sfin[i] = fin;
+                    spre[i] = pre;
+                    sfin[i] = fin;
                 }
             }
         }
@@ -1388,6 +1409,8 @@ static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, in
         return cand;
     }
     u64* dst = cand + kCap / 2;
+    FTB_ASSUME_SHARED(cand);
+    FTB_ASSUME_SHARED(dst);
     u32  kmin = 0xffffffffu, kmax = 0;
     for (int i = tid; i < n; i += kThreads) {
         const u32 k = (u32)(cand[i] >> 32);
@@ -1401,6 +1424,7 @@ static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, in
         ++shift;
     }
     u32* hist = S.hist;
+    FTB_ASSUME_SHARED(hist);
     for (int i = tid; i < kNB; i += kThreads) {
         hist[i] = 0;
     }
@@ -1466,7 +1490,7 @@ static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, in
                 const u32 b  = (u32)j * 32u + (u32)(__ffs(word) - 1);
                 const u32 hi = hist[b];  // cursor after the scatter = end of the bucket
                 const u32 lo = b == 0 ? 0u : hist[b - 1];
-                group_sort_u64(dst + lo, (int)(hi - lo), lane, 32, WarpSync());
+                group_sort_u64<WarpSync, true>(dst + lo, (int)(hi - lo), lane, 32, WarpSync());
                 word &= word - 1;
             }
         }
@@ -1545,6 +1569,8 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
     const int tid   = threadIdx.x;
     u32*      slots = (u32*)S.hitq;  // [kSlots], free again before the filtered pass needs its queue
     u32*      hist  = S.hist;
+    FTB_ASSUME_SHARED(slots);
+    FTB_ASSUME_SHARED(hist);
 
     auto value_of_key = [&](u32 key) {
         if (DT == FTB200_F32) {
@@ -1617,6 +1643,7 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
     }
     __syncthreads();
     u64* cand = S.cand;
+    FTB_ASSUME_SHARED(cand);
     auto push = [&](int v, float y) {
         if (y > C.neg_max) {
             // one atomic per warp: the lanes that arrive here together take consecutive positions
@@ -1838,6 +1865,12 @@ __device__ __noinline__ bool build_patches(const KParams& P, const Smem& S, cons
     __shared__ int s_over;
     const Xf       X   = make_xf(P, S, C);
     const int      tid = threadIdx.x;
+    const float*   sfin = S.sfin;
+    FTB_ASSUME_SHARED(sfin);
+    FTB_ASSUME_SHARED(pkey);
+    FTB_ASSUME_SHARED(pval);
+    FTB_ASSUME_SHARED(pcnt);
+    FTB_ASSUME_SHARED(X.hash);
     pcnt[tid]          = 0;
     if (tid == 0) {
         s_over = 0;
@@ -1853,7 +1886,7 @@ __device__ __noinline__ bool build_patches(const KParams& P, const Smem& S, cons
         if (v >= limit) {
             continue;
         }
-        const float y  = S.sfin[i];
+        const float y  = sfin[i];
         const int   t  = (v & 1023) >> 2;
         const u32   at = atomicAdd(&pcnt[t], 1u);
         if (at < (u32)kPatchSlots) {
@@ -2150,6 +2183,10 @@ template<int DT>
 __device__ __noinline__ void hot_count_dense(const uint4* vp, int jn, const u32* flags, u32 kmax16, u32 limit, u32* hist,
                                              unsigned short* hitq, u32* qn)
 {
+    FTB_ASSUME_SHARED(flags);
+    FTB_ASSUME_SHARED(hist);
+    FTB_ASSUME_SHARED(hitq);
+    FTB_ASSUME_SHARED(qn);
     constexpr int U   = 8;
     const int     tid = threadIdx.x;
     auto count2 = [&](u32 w) {
@@ -2211,11 +2248,16 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     const int        tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const bool       complete = !(cut0 > -INFINITY);
     u64*             spec     = (u64*)S.hitq;            // [kMaxSpecs] (~key(prob) << 32) | column
-    float*           run_pr   = (float*)S.cand;          // [kMaxRuns] runs, probability descending
+    u32*             run_pr   = (u32*)S.cand;            // [kMaxRuns] runs, probability (float bits) descending;
+                                                         // one element type for everything that shares this area
     u32*             run_st   = (u32*)S.cand + kMaxRuns; // [kMaxRuns] length, then first position of each run
     u32*             cls      = (u32*)S.cand;            // columns of the crossing class (after the replay)
     u32*             rank     = S.hist;                  // per pattern: count, then number of non-empty patterns before it
     float*           agg      = S.val2;                  // [1024] per-chunk aggregates
+    FTB_ASSUME_SHARED(spec);
+    FTB_ASSUME_SHARED(run_st);
+    FTB_ASSUME_SHARED(rank);
+    FTB_ASSUME_SHARED(agg);
 
     auto prob_of = [&](float y) {
         const float ex = round_to_T<DT>(__expf(y - maxv));
@@ -2321,7 +2363,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         return 0;
     }
     const int ns = (int)s_ns;
-    group_sort_u64(spec, ns, tid, kThreads, CtaSync());
+    group_sort_u64<CtaSync, true>(spec, ns, tid, kThreads, CtaSync());
     __syncthreads();
     trace_mark(O.trace, 22);
 
@@ -2374,7 +2416,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
                         hi = mid;
                     }
                 }
-                run_pr[at + lo] = pr;
+                run_pr[at + lo] = __float_as_uint(pr);
                 run_st[at + lo] = cnt[i];
                 ++at;
             }
@@ -2394,14 +2436,14 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
             }
         }
         const int nb     = lo < kNB ? (int)rank[lo] : nA;  // non-empty patterns with a probability >= this one
-        run_pr[j + nb]   = fkey_inv(~kp);
+        run_pr[j + nb]   = __float_as_uint(fkey_inv(~kp));
         run_st[j + nb]   = 1u;
     }
     __syncthreads();
     const int M = nA + ns;
     // the exponential has to be monotone over the patterns for the order of the runs to be the sorted order
     for (int i = tid; i + 1 < M; i += kThreads) {
-        if (run_pr[i] < run_pr[i + 1]) {
+        if (__uint_as_float(run_pr[i]) < __uint_as_float(run_pr[i + 1])) {
             s_fail = 1;
         }
     }
@@ -2482,7 +2524,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
                 if (i + 1 < M && run_st[i + 1] <= p) {
                     ++i;
                 }
-                x[e] = run_pr[i];
+                x[e] = __uint_as_float(run_pr[i]);
             }
             else {
                 x[e] = 0.0f;
@@ -2592,7 +2634,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     }
     // the class of the crossing: every column whose probability equals that of position sel
     const int   i_at  = run_of((u32)sel);
-    const float p_sel = run_pr[i_at];
+    const float p_sel = __uint_as_float(run_pr[i_at]);
     const u32   k_sel = fkey(p_sel);
     if (tid == 0) {
         s_ncls = 0;
@@ -2605,7 +2647,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         int lo = 0, hi = i_at;  // first run with probability == p_sel (runs are descending)
         while (lo < hi) {
             const int mid = (lo + hi) >> 1;
-            if (fkey(run_pr[mid]) > k_sel) {
+            if (fkey(__uint_as_float(run_pr[mid])) > k_sel) {
                 lo = mid + 1;
             }
             else {
