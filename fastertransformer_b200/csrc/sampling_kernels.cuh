@@ -1409,8 +1409,6 @@ static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, in
         return cand;
     }
     u64* dst = cand + kCap / 2;
-    FTB_ASSUME_SHARED(cand);
-    FTB_ASSUME_SHARED(dst);
     u32  kmin = 0xffffffffu, kmax = 0;
     for (int i = tid; i < n; i += kThreads) {
         const u32 k = (u32)(cand[i] >> 32);
@@ -1424,7 +1422,6 @@ static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, in
         ++shift;
     }
     u32* hist = S.hist;
-    FTB_ASSUME_SHARED(hist);
     for (int i = tid; i < kNB; i += kThreads) {
         hist[i] = 0;
     }
@@ -1490,7 +1487,7 @@ static __device__ __noinline__ u64* sort_candidates(const Smem& S, u64* cand, in
                 const u32 b  = (u32)j * 32u + (u32)(__ffs(word) - 1);
                 const u32 hi = hist[b];  // cursor after the scatter = end of the bucket
                 const u32 lo = b == 0 ? 0u : hist[b - 1];
-                group_sort_u64<WarpSync, true>(dst + lo, (int)(hi - lo), lane, 32, WarpSync());
+                group_sort_u64(dst + lo, (int)(hi - lo), lane, 32, WarpSync());
                 word &= word - 1;
             }
         }
