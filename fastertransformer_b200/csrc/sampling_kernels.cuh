@@ -2667,12 +2667,20 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         }
     }
     __syncthreads();  // the runs have been read for the last time: the class list takes their place
-    for (int j = tid; j < ns; j += kThreads) {
-        if ((u32)(spec[j] >> 32) == ~k_sel) {
-            const u32 pos = atomicAdd(&s_ncls, 1u);
-            cls[pos]      = (u32)(spec[j] & 0xffffffffu);
-        }
+    if (s_imax >= kNB - 1) {
+        return 0;  // the class of equal probabilities may go on below the pattern window
     }
+    // Special and edge columns of the class - all of them, also those below the cut: with probabilities
+    // rounded to the logits type a class of equal probabilities can span several bit patterns and reach
+    // below the counted range, and the rank of the crossing counts every column of the class.
+    visit_specials<DT>(P, S, C, -INFINITY, [&](int v, float y) {
+        if (y > C.neg_max && fkey(prob_of(y)) == k_sel) {
+            const u32 pos = atomicAdd(&s_ncls, 1u);
+            if (pos < (u32)(2 * kMaxRuns)) {
+                cls[pos] = (u32)v;
+            }
+        }
+    });
     __syncthreads();
     const int J = s_c1;
     trace_mark(O.trace, 27);
@@ -3269,6 +3277,30 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         if (sel == -2) {
             __syncthreads();
             continue;  // collect the whole row and repeat
+        }
+        if (sel >= 0 && sel < (int)n_g) {
+            // Equal probabilities stand in column order in the reference's stable sort.  The buckets above are
+            // ordered by logit: probabilities rounded to the logits type can be equal across a bucket boundary,
+            // so the whole run of entries equal to the selected one is put into column order before it is read.
+            __shared__ int s_eq_lo, s_eq_hi;
+            if (tid == 0) {
+                s_eq_lo = sel;
+                s_eq_hi = sel + 1;
+            }
+            __syncthreads();
+            const u32 ksel = (u32)(dest[sel] >> 32);
+            for (int i = tid; i < (int)n_g; i += kThreads) {
+                if ((u32)(dest[i] >> 32) == ksel) {
+                    atomicMin(&s_eq_lo, i);
+                    atomicMax(&s_eq_hi, i + 1);
+                }
+            }
+            __syncthreads();
+            const int eq_lo = s_eq_lo, eq_hi = s_eq_hi;
+            if (eq_hi - eq_lo > 1) {
+                group_sort_u64(dest + eq_lo, eq_hi - eq_lo, tid, kThreads, CtaSync());
+            }
+            __syncthreads();
         }
         if (tid == 0) {
             if (sel >= 0 && sel < (int)n_g) {

@@ -248,3 +248,43 @@ def test_draw_distribution_chi_square(kind, cuda_device):
     sel = expect > 0
     stat, pval = chisquare(counts[sel], expect[sel] * ids.size)
     assert pval > 1e-4, (stat, pval)
+
+
+def _random_workload(seed):
+    """A random decode configuration: logits type, shape, per-row k / p mix, temperature, penalty kind, bad words,
+    spread of the logits (flat rows make large top-p nuclei, peaked rows make small ones)."""
+    from fastertransformer_b200.workloads import SamplingWorkload, _bad_words
+    rng = np.random.default_rng(9000 + seed)
+    dtype = [torch.float32, torch.float16, torch.bfloat16][seed % 3]
+    vocab = int(rng.choice([1536, 4099, 8192, 20011, 32000, 50257]))
+    vpad = vocab if seed % 4 else (vocab + 7) // 8 * 8 + 8 * int(rng.integers(0, 3))
+    batch = int(rng.integers(3, 40))
+    mil, steps = int(rng.integers(2, 40)), int(rng.integers(2, 5))
+    ks = np.asarray([0, 1, 2, 17, 64, 300, 1024], np.uint32)
+    ps = np.asarray([0.0, 0.05, 0.3, 0.7, 0.95, 1.0], np.float32)
+    args = {"runtime_top_k": rng.choice(ks, size=batch), "runtime_top_p": rng.choice(ps, size=batch),
+            "random_seed": rng.integers(0, 2 ** 40, size=batch).astype(np.uint64)}
+    if seed % 2:
+        args["temperature"] = rng.choice(np.asarray([0.5, 0.8, 1.0, 1.7], np.float32), size=batch)
+    kind = seed % 5
+    if kind in (0, 1):
+        args["repetition_penalty"] = rng.choice(np.asarray([0.8, 1.0, 1.3, 2.0], np.float32), size=batch)
+    elif kind == 2:
+        args["presence_penalty"] = np.asarray([0.6], np.float32)
+    if seed % 3 == 1:
+        args["min_length"] = np.asarray([2], np.int32)
+    w = SamplingWorkload("rand%d" % seed, batch, vocab, vpad, dtype, float(rng.choice([0.4, 1.5, 3.0, 6.0])), steps, mil,
+                         int(rng.integers(0, vocab)), args, 4000 + seed,
+                         bad_words=_bad_words(rng, batch, vocab) if seed % 2 == 0 else None,
+                         prompt=rng.integers(0, vocab, size=(mil, batch)).astype(np.int32))
+    return w
+
+
+@pytest.mark.parametrize("seed", list(range(30)))
+def test_random_configurations_against_reference(seed, cuda_device):
+    w = _random_workload(seed)
+    log_probs = seed % 7 == 3
+    ref_layer, ref_dt = _ref_layer(w, cuda_device)
+    ref = run_cuda_like(ref_layer, w, cuda_device, want_log_probs=log_probs, cast=ref_dt, with_criteria=False)
+    mine = run_cuda_like(_layer(w, cuda_device), w, cuda_device, want_log_probs=log_probs)
+    _compare(mine, ref, w.name)
