@@ -3068,8 +3068,9 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
                 --bt;
                 extra += S.hist[bt];
             }
-            // -1: the counted range does not reach far enough
-            s_bthr = (b_cut > 0 && (b_star < 0 || extra < 64u)) ? -1 : bt;
+            // -1: the counted range does not reach far enough; the second attempt takes the whole row (a class
+            // of equal probabilities - zeros after rounding to half, say - can be larger than any partial set)
+            s_bthr = attempt == 1 ? 0 : ((b_cut > 0 && (b_star < 0 || extra < 64u)) ? -1 : bt);
         }
         __syncthreads();
         const int b_thr = s_bthr;

@@ -280,7 +280,7 @@ def _random_workload(seed):
     return w
 
 
-@pytest.mark.parametrize("seed", list(range(30)))
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("FTB200_RANDOM_CASES", "30")))))
 def test_random_configurations_against_reference(seed, cuda_device):
     w = _random_workload(seed)
     log_probs = seed % 7 == 3
