@@ -288,3 +288,28 @@ def test_random_configurations_against_reference(seed, cuda_device):
     ref = run_cuda_like(ref_layer, w, cuda_device, want_log_probs=log_probs, cast=ref_dt, with_criteria=False)
     mine = run_cuda_like(_layer(w, cuda_device), w, cuda_device, want_log_probs=log_probs)
     _compare(mine, ref, w.name)
+
+
+@pytest.mark.parametrize("seed", list(range(9)))
+def test_random_large_vocabularies_against_reference(seed, cuda_device):
+    """The same random mix at the vocabulary sizes of current models (aligned and odd), where the two-pass
+    top-k, the dense class count and the wide candidate sets come into play."""
+    from fastertransformer_b200.workloads import SamplingWorkload, _bad_words
+    rng = np.random.default_rng(777 + seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    vocab = [128256, 100003, 151936][seed // 3]
+    batch, mil, steps = 40, int(rng.integers(20, 200)), 3
+    args = {"runtime_top_k": rng.choice(np.asarray([0, 1, 5, 40, 512, 1024], np.uint32), size=batch),
+            "runtime_top_p": rng.choice(np.asarray([0.0, 0.2, 0.6, 0.9, 0.99], np.float32), size=batch),
+            "random_seed": rng.integers(0, 2 ** 40, size=batch).astype(np.uint64),
+            "repetition_penalty": np.asarray([1.15], np.float32)}
+    if seed % 2:
+        args["temperature"] = rng.choice(np.asarray([0.6, 1.0, 1.3], np.float32), size=batch)
+    w = SamplingWorkload("large%d" % seed, batch, vocab, vocab, dtype, float(rng.choice([1.0, 2.5, 5.0])), steps, mil,
+                         vocab - 3, args, 5000 + seed, bad_words=_bad_words(rng, batch, vocab),
+                         prompt=rng.integers(0, vocab, size=(mil, batch)).astype(np.int32))
+    log_probs = seed % 4 == 2
+    ref_layer, ref_dt = _ref_layer(w, cuda_device)
+    ref = run_cuda_like(ref_layer, w, cuda_device, want_log_probs=log_probs, cast=ref_dt, with_criteria=False)
+    mine = run_cuda_like(_layer(w, cuda_device), w, cuda_device, want_log_probs=log_probs)
+    _compare(mine, ref, w.name)
