@@ -331,7 +331,15 @@ __global__ void __launch_bounds__(kBeamThreads) beam_step_kernel(const __grid_co
             if (use_lp && len != 1) {
                 e = beam_round<DT>(e / beam_round<DT>(powf((float)len, P.length_penalty)));
             }
-            e          = beam_round<DT>(e + beam_round<DT>(beam_round<DT>(P.diversity) * beam_round<DT>((float)(i % K))));
+            if (DT == FTB200_F16) {
+                // `elem += diversity_rate * (T)i` in half: the compiler contracts the half multiply and add of the
+                // reference into one fused multiply-add, so the sum is rounded once (exact in double first)
+                const double d = (double)beam_round<DT>(P.diversity) * (double)beam_round<DT>((float)(i % K)) + (double)e;
+                e              = __half2float(__double2half(d));
+            }
+            else {
+                e = e + P.diversity * (float)(i % K);
+            }
             sortbuf[i] = x[i] < 0 ? ~0ull : order_key(e, (u32)i);
         }
         __syncthreads();

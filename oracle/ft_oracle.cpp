@@ -59,6 +59,25 @@ struct RowView {
     }
 };
 
+// Nearest half (ties to even) of a double, as a float: one rounding, for results the GPU forms with a fused
+// half multiply-add.
+static float round_half_from_double(double d)
+{
+    if (!(d == d) || d == 0.0 || std::isinf(d)) {
+        return (float)d;
+    }
+    int    ex;
+    double a = std::fabs(d);
+    std::frexp(a, &ex);                        // a = m * 2^ex, m in [0.5, 1)
+    int    e2      = ex - 1 < -14 ? -14 : ex - 1;  // exponent of the leading bit, clamped to the subnormal range
+    double spacing = std::ldexp(1.0, e2 - 10);
+    double r       = std::nearbyint(a / spacing) * spacing;
+    if (r > 65504.0) {
+        r = INFINITY;
+    }
+    return (float)(d < 0 ? -r : r);
+}
+
 // The logits type of the reference is float or half; bf16 inputs are handled as float on the up-cast.
 struct TypeOps {
     bool  is_half;
@@ -801,7 +820,14 @@ extern "C" int oracle_beam_search_step(const ftb200_beam_params* p)
                 if (p->length_penalty != 0.0f && len != 1) {
                     s = T.rnd(s / T.rnd(powf((float)len, p->length_penalty)));
                 }
-                e[i] = T.rnd(s + T.rnd(T.rnd(p->diversity_rate) * T.rnd((float)(i % K))));
+                // `elem += diversity_rate * (T)i` (online_softmax_beamsearch_kernels.cu:157): in half the multiply
+                // and the add are contracted into one fused multiply-add, so the sum is rounded once
+                if (T.is_half) {
+                    e[i] = round_half_from_double((double)T.rnd(p->diversity_rate) * (double)T.rnd((float)(i % K)) + (double)s);
+                }
+                else {
+                    e[i] = std::fmaf(p->diversity_rate, (float)(i % K), s);
+                }
                 if (x[i] >= 0) {
                     ord.push_back(i);
                 }

@@ -89,3 +89,36 @@ def test_beam_config4_shape(cuda_device):
     for a, b in zip(mine, ref):
         for key in ("output_ids", "parent_ids", "finished", "sequence_length", "tgt_cache_indirection"):
             assert (a[key] == b[key]).all(), key
+
+
+@pytest.mark.parametrize("seed", list(range(int(__import__("os").environ.get("FTB200_RANDOM_CASES", "24")))))
+def test_random_beam_configurations_against_reference(seed, cuda_device):
+    """Random batch / beam / vocabulary / penalty combinations through several steps."""
+    if not ft_reference.available():
+        pytest.skip("oracle/_ref/libft_decode_ref.so not built")
+    from fastertransformer_b200 import DynamicDecodeLayer
+    rng = np.random.default_rng(31000 + seed)
+    dtype = [torch.float32, torch.float16][seed % 2]
+    B, K = int(rng.integers(1, 9)), int(rng.choice([2, 3, 4, 5, 8, 12]))
+    V = int(rng.choice([257, 1031, 4096, 32000]))
+    mil, steps = int(rng.integers(2, 6)), int(rng.integers(2, 6))
+    L = mil + steps + 1
+    args = {}
+    if seed % 3 == 0:
+        args["len_penalty"] = np.asarray([float(rng.choice([0.5, 1.0, 2.0]))], np.float32)
+    if seed % 4 == 1:
+        args["beam_search_diversity_rate"] = np.asarray([0.3], np.float32)
+    if seed % 5 == 2:
+        args["temperature"] = np.asarray([0.7], np.float32)
+        args["repetition_penalty"] = np.asarray([1.4], np.float32)
+    if seed % 5 == 3:
+        args["presence_penalty"] = np.asarray([0.5], np.float32)
+        args["min_length"] = np.asarray([2], np.int32)
+    ref = run_beam(ft_reference.RefDynamicDecodeLayer(V, V, dtype, cuda_device), True, B, K, V, L, mil, steps, dtype,
+                   cuda_device, args, 500 + seed)
+    mine = run_beam(DynamicDecodeLayer(V, V, dtype, cuda_device), False, B, K, V, L, mil, steps, dtype, cuda_device,
+                    args, 500 + seed)
+    for s, (a, b) in enumerate(zip(mine, ref)):
+        for key in ("output_ids", "parent_ids", "finished", "sequence_length", "tgt_cache_indirection"):
+            assert np.array_equal(a[key], b[key]), (seed, s, key)
+        np.testing.assert_allclose(a["cum_log_probs"], b["cum_log_probs"], rtol=1e-3, atol=1e-3)
