@@ -2236,7 +2236,7 @@ constexpr int kMaxSpecs = 1024;  // special / edge columns above the cut
 template<int DT>
 __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O,
                                              float maxv, float denom, float rand_num, float cut0, u32 kmax16,
-                                             bool want_lp, bool dense)
+                                             bool want_lp, bool dense, u32 k_cut_given = 0xffffffffu)
 {
     __shared__ u32   s_ns, s_fail, s_wsum[kWarps], s_ncls;
     __shared__ int   s_c1, s_sel, s_imin, s_imax;
@@ -2273,7 +2273,12 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     // The cut in the pattern domain: the smallest ordered key whose value reaches cut0.  Everything at or
     // above that pattern is counted, so the collected classes are complete down to the value y_c.
     u32 k_cut = 0;
-    if (!complete) {
+    if (k_cut_given != 0xffffffffu) {
+        // the caller names the lowest pattern itself (the bottom of the class window): a search by value could
+        // land on a lower pattern that rounds to the same value
+        k_cut = k_cut_given;
+    }
+    else if (!complete) {
         u32 lo = 0, hi = kmax16;  // value(key) is monotone in the key
         while (lo < hi) {
             const u32 mid = (lo + hi) >> 1;
@@ -2287,10 +2292,10 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         k_cut = lo;
     }
     if (kmax16 - k_cut >= (u32)kNB) {
-        return 0;  // the class window does not reach down to the cut
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 1; } return 0; }
     }
     const u32   limit = kmax16 - k_cut + 1u;
-    const float y_c   = complete ? -INFINITY : temp_value<DT>(X, key16_inv(k_cut), 0);
+    const float y_c   = (complete && k_cut_given == 0xffffffffu) ? -INFINITY : temp_value<DT>(X, key16_inv(k_cut), 0);
     // pass 3 (L2): exact count of every bit pattern at or above the cut
     {
         constexpr int EPV = DT == FTB200_F32 ? 4 : 8;
@@ -2320,7 +2325,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
             __syncthreads();
             const int nq = (int)S.nhit[0];
             if (nq > kHitCap || C.nvec > 65535) {
-                return 0;
+                { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 2; } return 0; }
             }
             const uint4* vp = vec_base<DT>(C);
             for (int i = tid; i < nq; i += kThreads) {
@@ -2357,7 +2362,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     __syncthreads();
     trace_mark(O.trace, 5);
     if (s_fail) {
-        return 0;
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 3; } return 0; }
     }
     const int ns = (int)s_ns;
     group_sort_u64<CtaSync, true>(spec, ns, tid, kThreads, CtaSync());
@@ -2394,7 +2399,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         }
         nA = (int)tot;
         if (nA + ns > kMaxRuns) {
-            return 0;  // uniform: every thread sees the same totals
+            { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 4; } return 0; }
         }
         u32 at = base + incl - mine;
         for (int i = 0; i < PER; ++i) {
@@ -2446,7 +2451,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     }
     __syncthreads();
     if (s_fail) {
-        return 0;
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 5; } return 0; }
     }
     // exclusive scan of the run lengths -> first position of each run
     u32 N;
@@ -2494,7 +2499,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     }
     const int nch = (int)((N + 255u) / 256u);
     if (nch > 1024 || N == 0) {
-        return 0;
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 6; } return 0; }
     }
     // run that holds position p
     auto run_of = [&](u32 p) {
@@ -2571,7 +2576,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     }
     __syncthreads();
     if (s_c1 >= nch) {
-        return 0;  // the cut was too high (or the draw is never reached): general path
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 7; } return 0; }
     }
     if (wid == 0) {
         float R   = s_R;
@@ -2627,7 +2632,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     const int sel = s_sel;
     trace_mark(O.trace, 7);
     if (sel < 0 || (u32)sel >= N) {
-        return 0;
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 8; } return 0; }
     }
     // the class of the crossing: every column whose probability equals that of position sel
     const int   i_at  = run_of((u32)sel);
@@ -2668,7 +2673,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     }
     __syncthreads();  // the runs have been read for the last time: the class list takes their place
     if (s_imax >= kNB - 1) {
-        return 0;  // the class of equal probabilities may go on below the pattern window
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 9; } return 0; }
     }
     // Special and edge columns of the class - all of them, also those below the cut: with probabilities
     // rounded to the logits type a class of equal probabilities can span several bit patterns and reach
@@ -2703,7 +2708,7 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     const int ncls = (int)s_ncls;
     trace_mark(O.trace, 8);
     if (ncls > 2 * kMaxRuns || J >= ncls) {
-        return 0;  // an unusually large class of equal values: general path
+        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 10; } return 0; }
     }
     // J-th smallest column of the class: members are counted per block of columns (reversed, so that the
     // walk from the top runs over ascending columns), the block holding rank J is found, and only the few
@@ -3008,7 +3013,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_a, kraw, want_lp, dense)) {
             return;
         }
-        if (cut_b < cut_a && row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_b, kraw, want_lp, true)) {
+        if (cut_b < cut_a && row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_b, kraw, want_lp, true, k_bot)) {
             return;
         }
         __syncthreads();
