@@ -168,12 +168,16 @@ def run_ours(a, rank, world, local):
     torch.cuda.set_device(device)
     K, W = a.steps, a.warmup
     e2e_steps = min(K, 16)
-    w = make_workload("c3", batch=a.batch, steps=W + K + e2e_steps + 40, seed=1237 + rank)
+    wname = a.workload if a.workload in ("c1", "c2") else "c3"
+    w = make_workload(wname, batch=a.batch, steps=W + K + e2e_steps + 40, seed=(1237 if wname == "c3" else 1234 + int(wname[1])) + rank)
     B = w.batch
     layer = DynamicDecodeLayer(w.vocab, w.vocab_padded, w.dtype, device)
     layer.setup(B, 1, w.runtime_args)
     st = w.initial_state(device)
     inputs = w.static_inputs(device)
+    # enough rotating buffers that a step never finds its logits in the 126 MB L2
+    buf_bytes = B * w.vocab_padded * torch.empty(0, dtype=w.dtype).element_size()
+    N_BUFFERS = max(4, min(200, -(-300_000_000 // buf_bytes)))
     pool = make_pool(w, device, w.dtype, N_BUFFERS)
     torch.cuda.synchronize()
 
@@ -243,21 +247,26 @@ def run_ours(a, rank, world, local):
     achieved = alg_bytes / (kern_ms_mean * 1e-3) / 1e9
     es = pool[0].element_size()
     line = {
-        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256",
+        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256" if wname == "c3"
+        else "sampled tokens/sec and achieved HBM GB/s (config %s: batch %d, vocab %d)" % (wname[1], B, w.vocab),
         "value": world * B * K / (ms_total * 1e-3),
         "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_total / K,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 logits, fp32 arithmetic", "data": "synthetic",
-        "config": {"workload": "c3: mixed per-row top-k/top-p, batch %d x vocab %d bf16, repetition 1.1, "
-                               "8 bad words/row, length criterion" % (B, w.vocab),
+        "dtype": {"c1": "fp32", "c2": "fp16 logits and probabilities", "c3": "bf16 logits, fp32 arithmetic"}[wname],
+        "data": "synthetic",
+        "config": {"workload": {"c1": "c1: top-k 50, T 1.0, repetition 1.2, batch %d x vocab %d fp32",
+                                "c2": "c2: top-p 0.9, T 0.8, presence 0.5, min_length 16, batch %d x vocab %d fp16",
+                                "c3": "c3: mixed per-row top-k/top-p, batch %d x vocab %d bf16, repetition 1.1, "
+                                      "8 bad words/row, length criterion"}[wname] % (B, w.vocab),
                    "rows_per_gpu": B, "history_tokens": "%d..%d" % (first_step, first_step + K),
-                   "l2": "%d logits buffers of %.0f MB rotate (> 126 MB L2)" % (N_BUFFERS, B * w.vocab_padded * es / 1e6),
+                   "l2": "%d logits buffers of %.1f MB rotate (%.0f MB in all, L2 is 126 MB)" % (
+                       N_BUFFERS, B * w.vocab_padded * es / 1e6, N_BUFFERS * B * w.vocab_padded * es / 1e6),
                    "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": a.traffic, "peak_kind": peak_kind,
-                     "kernel": "decode_sampling_kernel<bf16>", "kernel_ms": kern_ms_mean,
+                     "frac": achieved / peak, "traffic": a.traffic if wname == "c3" and B == 1024 else None, "peak_kind": peak_kind,
+                     "kernel": "decode_sampling_kernel<%s>" % {"c1": "f32", "c2": "f16", "c3": "bf16"}[wname], "kernel_ms": kern_ms_mean,
                      "algorithmic_bytes_per_launch": alg_bytes},
         "e2e": {"value": world * B * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": B * w.vocab_padded * es, "d2h_bytes_per_step": B * 4 + 4,
@@ -406,13 +415,15 @@ def run_reference(a, rank, world, local):
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     K, W = a.steps, a.warmup
-    w = make_workload("c3", batch=a.batch, steps=W + K + 4)
+    wname = a.workload if a.workload in ("c1", "c2") else "c3"
+    w = make_workload(wname, batch=a.batch, steps=W + K + 4)
     B = w.batch
-    layer = ft_reference.RefDynamicDecodeLayer(w.vocab, w.vocab_padded, torch.float32, device)
+    ref_dt = torch.float32 if w.dtype == torch.bfloat16 else w.dtype  # the reference has float and half only
+    layer = ft_reference.RefDynamicDecodeLayer(w.vocab, w.vocab_padded, ref_dt, device)
     layer.setup(B, 1, w.runtime_args)
     st = w.initial_state(device)
     inputs = w.static_inputs(device)
-    pool = make_pool(w, device, torch.float32, 2)
+    pool = make_pool(w, device, ref_dt, 2)
     work = torch.empty_like(pool[0])
     sampler = ClockSampler(local, period=0.02)
     total_ms, n = 0.0, 0
@@ -434,11 +445,13 @@ def run_reference(a, rank, world, local):
     val = B * n / (total_ms * 1e-3)
     return {
         "impl": "reference",
-        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256",
+        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256" if wname == "c3"
+        else "sampled tokens/sec and achieved HBM GB/s (config %s: batch %d, vocab %d)" % (wname[1], B, w.vocab),
         "value": val, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": total_ms / n,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp32 (up-cast of the bf16 logits; the reference has no bf16 path)", "data": "synthetic",
-        "config": {"workload": "c3: mixed per-row top-k/top-p, batch %d x vocab %d, repetition 1.1, "
+        "dtype": "fp32 (up-cast of the bf16 logits; the reference has no bf16 path)" if wname == "c3"
+        else str(ref_dt).replace("torch.", ""), "data": "synthetic",
+        "config": {"workload": wname + " as above" if wname != "c3" else "c3: mixed per-row top-k/top-p, batch %d x vocab %d, repetition 1.1, "
                                "8 bad words/row, length criterion" % (B, w.vocab),
                    "what": "unmodified FasterTransformer DynamicDecodeLayer<float> compiled for sm_100a "
                            "(oracle/_ref), logits resident in HBM, CUDA events around each forward()"},
@@ -455,9 +468,10 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=1024)
-    ap.add_argument("--workload", default="c3", choices=["c3", "c4", "c5"],
-                    help="c3 (default, the headline) | c4 beam search | c5 vocabulary-parallel")
+    ap.add_argument("--batch", type=int, default=None, help="rows per GPU (default: the configuration's own)")
+    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="c3 (default, the headline) | c1 / c2 the small sampling configurations | c4 beam search | "
+                         "c5 vocabulary-parallel")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the fused kernel from an ncu capture (profiles/)")
