@@ -240,9 +240,8 @@ extern "C" int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int 
         set_error("ftb200_vocab_parallel_local: invalid argument");
         return FTB200_INVALID_ARG;
     }
-    if (p != nullptr && (p->topk_states == nullptr || p->topp_states != nullptr || p->cum_log_probs != nullptr
-                         || p->output_log_probs != nullptr)) {
-        set_error("ftb200_vocab_parallel_local: only top-k rows without log-probs are exchanged as candidates");
+    if (p != nullptr && (p->cum_log_probs != nullptr || p->output_log_probs != nullptr)) {
+        set_error("ftb200_vocab_parallel_local: log-probs are not available with a sharded vocabulary");
         return FTB200_UNSUPPORTED;
     }
     KParams K;

@@ -1523,7 +1523,7 @@ static __device__ __noinline__ void topk_tail(const KParams& P, const Smem& S, c
         }
         __syncthreads();
         const int m   = s_m;
-        u64*      out = P.vp_out + (size_t)O.r * (P.vp_cap + 1);
+        u64*      out = P.vp_out + (size_t)O.r * (P.vp_cap + 2);
         if (tid == 0) {
             out[0] = m > P.vp_cap ? ~0ull : (u64)m;  // ~0: more ties than the exchange record holds
         }
@@ -3335,6 +3335,53 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     }
 }
 
+// Vocabulary-parallel local pass of a top-p row: largest final value of the shard's columns and the sum of
+// exp(value - that maximum) over them, stored in the last word of the row's record as two floats.  The ranks
+// combine the pairs as the reference's online soft-max does (reduce_md_op,
+// kernels/online_softmax_beamsearch_kernels.cu:270-279), so the denominator is not summed in the single-GPU
+// order: a draw that falls within rounding of a boundary may pick the neighbouring column.
+template<int DT>
+__device__ __noinline__ void row_vp_stats(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O)
+{
+    const int tid = threadIdx.x;
+    float     m   = stream_max<DT>(P, S, C, false);  // ordinary columns (special ones are left out)
+    fetch_specials<DT>(P, S, C);
+    visit_specials<DT>(P, S, C, -INFINITY, [&](int v, float y) {
+        if (y > C.neg_max) {
+            m = fmaxf(m, y);
+        }
+    });
+    const u64 best = block_max_u64(m > C.neg_max ? ((u64)fkey(m) << 32) | 1u : 0ull);
+    float     maxv = -INFINITY, sum = 0.0f;
+    if (best != 0) {
+        maxv = fkey_inv((u32)(best >> 32));
+        auto add = [&](int v, float y) {
+            if (y > C.neg_max) {
+                sum += __expf(y - maxv);
+            }
+        };
+        stream_all<DT>(P, S, C, 0, C.nvec, add);
+        visit_specials<DT>(P, S, C, -INFINITY, add);
+    }
+    // block-wide sum of the per-thread partial sums
+    __shared__ float s_part[kWarps];
+    for (int k = 16; k > 0; k >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, k);
+    }
+    if ((tid & 31) == 0) {
+        s_part[tid >> 5] = sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < kWarps; ++i) {
+            t += s_part[i];
+        }
+        P.vp_out[(size_t)O.r * (P.vp_cap + 2) + P.vp_cap + 1] = ((u64)__float_as_uint(maxv) << 32) | __float_as_uint(t);
+    }
+    __syncthreads();
+}
+
 template<int DT>
 __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratch, u64* trace)
 {
@@ -3374,8 +3421,20 @@ __device__ void process_row(const KParams& P, const Smem& S, int r, u64* gscratc
                 row_topk<DT>(P, S, C, O, gscratch, k, 0.0f, 1.0f);
             }
         }
+        else if (mode == 2 && !fin) {
+            // top-p row: the shard's (maximum, sum of exponentials) and its largest columns; the merge builds
+            // the nucleus from the union
+            RowCtx& C = s_C;
+            build_row<DT>(P, S, C, r);
+            row_vp_stats<DT>(P, S, C, O);
+            int k = P.vp_cap > 128 ? P.vp_cap - 64 : P.vp_cap / 2;
+            k     = k < 1 ? 1 : (k > kMaxTopK ? kMaxTopK : k);
+            if (!(P.bias == nullptr && C.inv_t > 0.0f && row_topk2<DT>(P, S, C, O, k, 0.0f, 1.0f))) {
+                row_topk<DT>(P, S, C, O, gscratch, k, 0.0f, 1.0f);
+            }
+        }
         else if (tid == 0) {
-            P.vp_out[(size_t)r * (P.vp_cap + 1)] = 0;
+            P.vp_out[(size_t)r * (P.vp_cap + 2)] = 0;
         }
         __syncthreads();
         return;
@@ -3498,6 +3557,246 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
 }
 
 
+// Merge of one top-p row: union of the shards' candidates, soft-max statistics combined, probabilities of the
+// candidates, the reference's block-wide scan over them in sorted order (kernels/sampling_topp_kernels.cu:
+// 877-1004) until the draw is crossed.  A row whose nucleus needs more columns than the shards sent is
+// counted in `overflow` and gets id -1: the caller repeats it with a larger cap or on gathered logits.
+template<int DT>
+__device__ __noinline__ void vp_merge_topp_row(const KParams& P, const Smem& S, const u64* gathered, int nranks,
+                                               int* overflow, int r)
+{
+    __shared__ float s_u, s_M, s_den;
+    __shared__ u32   s_n, s_bad, s_all;
+    __shared__ int   s_sel, s_lo, s_hi;
+    const int        tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    int* const       id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
+    const int        end_id = P.end_ids[r];
+    const bool       fin    = P.finished != nullptr ? P.finished[r] != 0 : false;
+    const float      top_p  = P.topp_ps[r];
+    __syncthreads();
+    if (tid == 0) {
+        s_u   = draw_uniform(P.topp_states, r);  // every row of the top-p layer draws, finished or not
+        s_n   = 0;
+        s_bad = 0;
+        s_all = 1;
+        s_sel = -1;
+    }
+    __syncthreads();
+    const float u = s_u;
+    int         id = -1;
+    bool        update_state = false;
+    if (fin) {
+        // one-hot row on the end id (sampling_topp_kernels.cu:1309-1341)
+        const float p0 = DT == FTB200_F16 ? __half2float(__float2half_rn(1.0f / (1.0f + 1e-6f))) : 1.0f / (1.0f + 1e-6f);
+        id             = end_id;
+        if (tid == 0) {
+            *id_out = id;
+            if ((p0 >= top_p || u * top_p <= p0) && P.seq_len != nullptr && P.finished != nullptr) {
+                P.finished[r] = 1;
+            }
+        }
+    }
+    else {
+        // union of the candidates, statistics
+        float M = -INFINITY;
+        for (int q = 0; q < nranks; ++q) {
+            const u64* rec = gathered + ((size_t)q * P.local_batch + r) * (P.vp_cap + 2);
+            const u64  c   = rec[0];
+            if (c == ~0ull) {
+                if (tid == 0) {
+                    s_bad = 1;
+                }
+                continue;
+            }
+            const u32 base = s_n;
+            __syncthreads();
+            if (base + (u32)c > (u32)kCap) {
+                if (tid == 0) {
+                    s_bad = 1;
+                }
+            }
+            else {
+                for (u32 i = tid; i < (u32)c; i += kThreads) {
+                    S.cand[base + i] = rec[1 + i];
+                }
+                if (tid == 0) {
+                    s_n = base + (u32)c;
+                    const int k_local = P.vp_cap > 128 ? P.vp_cap - 64 : P.vp_cap / 2;
+                    if ((int)c >= (k_local < kMaxTopK ? k_local : kMaxTopK)) {
+                        s_all = 0;  // this shard may hold more columns than it sent
+                    }
+                }
+            }
+            M = fmaxf(M, __uint_as_float((u32)(rec[P.vp_cap + 1] >> 32)));
+            __syncthreads();
+        }
+        if (tid == 0) {
+            float den = 0.0f;
+            for (int q = 0; q < nranks; ++q) {
+                const u64 w = gathered[((size_t)q * P.local_batch + r) * (P.vp_cap + 2) + P.vp_cap + 1];
+                const float m = __uint_as_float((u32)(w >> 32)), d = __uint_as_float((u32)w);
+                if (m > -INFINITY) {
+                    den += d * __expf(m - M);
+                }
+            }
+            s_M   = M;
+            s_den = den + 1e-6f;
+        }
+        __syncthreads();
+        const int   n     = (int)s_n;
+        const float denom = s_den;
+        if (s_bad || n == 0 || !(M > -INFINITY)) {
+            if (tid == 0) {
+                atomicAdd(overflow, 1);
+                *id_out = -1;
+            }
+            __syncthreads();
+            return;
+        }
+        group_sort_u64(S.cand, n, tid, kThreads, CtaSync());  // value descending, column ascending
+        __syncthreads();
+        // probabilities in place of the values (monotone: the order stays, equal probabilities are handled below)
+        for (int i = tid; i < n; i += kThreads) {
+            const u64   e  = S.cand[i];
+            const float y  = fkey_inv(~(u32)(e >> 32));
+            const float ex = round_to_T<DT>(__expf(y - M));
+            const float pr = round_to_T<DT>(ex / denom);
+            S.cand[i]      = ((u64)(~fkey(pr)) << 32) | (e & 0xffffffffu);
+        }
+        __syncthreads();
+        const float p_max    = fkey_inv(~(u32)(S.cand[0] >> 32));
+        const float rand_num = u * top_p;
+        if (p_max >= top_p) {
+            if (tid == 0) {
+                s_sel = 0;  // arg-max shortcut of topp_beam_topk_kernel (sampling_topp_kernels.cu:801-860)
+            }
+        }
+        else if (wid == 0) {
+            float R   = 0.0f;
+            int   sel = -1;
+            for (int c = 0; c * 256 < n; ++c) {
+                const int bi = c * 256 + lane * 8;
+                float     x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    x[i] = bi + i < n ? fkey_inv(~(u32)(S.cand[bi + i] >> 32)) : 0.0f;
+                }
+                float up = x[0];
+#pragma unroll
+                for (int i = 1; i < 8; ++i) {
+                    up = up + x[i];
+                }
+                float inc = up;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    float t = __shfl_up_sync(0xffffffffu, inc, off);
+                    if (lane >= off) {
+                        inc = inc + t;
+                    }
+                }
+                const float agg = __shfl_sync(0xffffffffu, inc, 31);
+                const float ex  = __shfl_up_sync(0xffffffffu, inc, 1);
+                float       o   = lane == 0 ? R : R + ex;
+                u32         cnt = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    o = o + x[i];
+                    cnt += rand_num <= o ? 1u : 0u;
+                }
+                u32 c4 = cnt;
+                c4 += __shfl_xor_sync(0xffffffffu, c4, 1);
+                c4 += __shfl_xor_sync(0xffffffffu, c4, 2);
+                const u32 any = __ballot_sync(0xffffffffu, c4 > 0);
+                if (any) {
+                    const int g  = (__ffs(any) - 1) >> 2;
+                    const u32 pc = __shfl_sync(0xffffffffu, c4, g * 4);
+                    sel          = c * 256 + g * 32 + (32 - (int)pc);
+                    if (!s_all && c * 256 + g * 32 + 31 >= n) {
+                        sel = -2;  // the 32 probabilities of that warp are not all known
+                    }
+                    break;
+                }
+                R = R + agg;
+            }
+            if (sel >= n) {
+                sel = -2;
+            }
+            if (sel == -1 && !s_all) {
+                sel = -2;  // the draw lies beyond what the shards sent
+            }
+            if (lane == 0) {
+                s_sel = sel;
+            }
+        }
+        __syncthreads();
+        int sel = s_sel;
+        if (sel == -2) {
+            if (tid == 0) {
+                atomicAdd(overflow, 1);
+                *id_out = -1;
+            }
+            __syncthreads();
+            return;
+        }
+        if (sel >= 0) {
+            // equal probabilities stand in column order
+            if (tid == 0) {
+                s_lo = sel;
+                s_hi = sel + 1;
+            }
+            __syncthreads();
+            const u32 ksel = (u32)(S.cand[sel] >> 32);
+            for (int i = tid; i < n; i += kThreads) {
+                if ((u32)(S.cand[i] >> 32) == ksel) {
+                    atomicMin(&s_lo, i);
+                    atomicMax(&s_hi, i + 1);
+                }
+            }
+            __syncthreads();
+            const int lo = s_lo, hi = s_hi;
+            if (!s_all && hi == n) {
+                // the class of the crossing may continue in columns that were not sent
+                if (tid == 0) {
+                    atomicAdd(overflow, 1);
+                    *id_out = -1;
+                }
+                __syncthreads();
+                return;
+            }
+            if (hi - lo > 1) {
+                group_sort_u64(S.cand + lo, hi - lo, tid, kThreads, CtaSync());
+            }
+            __syncthreads();
+            id           = (int)(S.cand[sel] & 0xffffffffu);
+            update_state = true;
+        }
+        else {
+            // the cumulative sum never reached the draw: the best token, no length / finished update
+            id = (int)(S.cand[0] & 0xffffffffu);
+        }
+        if (tid == 0) {
+            *id_out = id;
+            if (update_state && P.seq_len != nullptr && P.finished != nullptr) {
+                P.seq_len[r]  = P.seq_len[r] + 1;
+                P.finished[r] = id == end_id ? 1 : 0;
+            }
+        }
+    }
+    __syncthreads();
+    // top-p decay / reset (sampling_topp_kernels.cu:1381-1408)
+    if (P.topp_decay != nullptr && tid == 0) {
+        float p = P.topp_ps[r];
+        if (id == P.topp_reset[r]) {
+            p = P.topp_initial[r];
+        }
+        else {
+            p = fmaxf(p * P.topp_decay[r], P.topp_min[r]);
+        }
+        P.topp_ps[r] = p;
+    }
+    __syncthreads();
+}
+
 // Vocabulary-parallel merge: one CTA per row.  `gathered` holds, rank after rank, the records the local
 // passes emitted ([rank][row][1 + cap]: count, then (~key(value) << 32 | global column) entries).  The
 // union is sorted and handed to the same draw and tie-order code as the single-GPU path, so every rank
@@ -3517,7 +3816,13 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
     const int tid = threadIdx.x;
     for (int r = blockIdx.x; r < P.local_batch; r += gridDim.x) {
         __syncthreads();
-        if (P.topk_skip != nullptr && P.topk_skip[r]) {
+        const bool by_topk = P.topk_states != nullptr && !(P.topk_skip != nullptr && P.topk_skip[r]);
+        const bool by_topp = !by_topk && P.topp_states != nullptr && !(P.topp_skip != nullptr && P.topp_skip[r]);
+        if (by_topp) {
+            vp_merge_topp_row<DT>(P, S, gathered, nranks, overflow, r);
+            continue;
+        }
+        if (!by_topk) {
             continue;
         }
         RowOut O;
@@ -3540,7 +3845,7 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
         __syncthreads();
         bool bad = false;
         for (int q = 0; q < nranks; ++q) {
-            const u64* rec = gathered + ((size_t)q * P.local_batch + r) * (P.vp_cap + 1);
+            const u64* rec = gathered + ((size_t)q * P.local_batch + r) * (P.vp_cap + 2);
             const u64  c   = rec[0];
             if (c == ~0ull) {
                 bad = true;

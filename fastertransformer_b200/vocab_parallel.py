@@ -1,9 +1,14 @@
-"""Vocabulary-parallel top-k sampling over a column-sharded lm_head (host side).
+"""Vocabulary-parallel sampling over a column-sharded lm_head (host side).
 
 Each rank holds logits[:, rank*V/n : (rank+1)*V/n].  Instead of FasterTransformer's all-gather of the full
 fp32 logits followed by redundant sampling on every rank (models/multi_gpu_gpt/ParallelGpt.cc:1394-1435),
 each rank selects candidates on its shard, ONE all-gather exchanges a few hundred bytes per row, and every
 rank merges and draws with identical curand states - same id on every rank, equal to the single-GPU result.
+
+Top-k rows are exact (the union of the shards' candidates holds every column the selection can touch).  Top-p
+rows exchange each shard's largest columns plus its (maximum, sum of exponentials); the ranks combine the pairs
+like an online soft-max, so the denominator is not summed in the single-GPU order and a draw within rounding of
+a boundary may pick the neighbouring column; a nucleus larger than the union is reported, not cut.
 
 `VocabParallelSampler` reuses DynamicDecodeLayer for the set-up (runtime arguments, curand states).  The
 exchange goes through torch.distributed (NCCL) when a process group is given; `forward_shards` runs all
@@ -18,9 +23,13 @@ from .decode_layer import CURAND_STATE_BYTES, DynamicDecodeLayer, _DT
 
 
 class VocabParallelSampler(DynamicDecodeLayer):
-    def __init__(self, vocab_size, shard_size, n_shards, dtype, device, cap_extra=64, group=None):
+    def __init__(self, vocab_size, shard_size, n_shards, dtype, device, cap_extra=64, group=None, topp_candidates=448):
+        """`topp_candidates`: columns every shard sends for a top-p row (its largest ones, plus its soft-max
+        statistics).  A row whose nucleus needs more than the union holds comes back with id -1 and is counted
+        by overflow_count(); the caller repeats such rows with a larger value or on gathered logits."""
         super().__init__(vocab_size, shard_size * n_shards, dtype, device)
         self.shard_size, self.n_shards, self.cap_extra, self.group = shard_size, n_shards, cap_extra, group
+        self.topp_candidates = int(topp_candidates)
         self._records = None
         self._gathered = None
         self._overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -28,8 +37,6 @@ class VocabParallelSampler(DynamicDecodeLayer):
     def _params(self, outputs, inputs, logits, vocab, vocab_padded):
         B = logits.shape[0]
         step, mil = int(inputs["step"]), int(inputs["max_input_length"])
-        if self.topp.active and not self.topp.skip_host.all():
-            raise RuntimeError("[FT][ERROR] vocabulary-parallel sampling handles top-k rows only")
         P = SamplingParams()
         P.dtype = _DT[logits.dtype]
         P.batch_size = P.local_batch_size = B
@@ -55,6 +62,11 @@ class VocabParallelSampler(DynamicDecodeLayer):
         P.topk_states = self.topk.curand.data_ptr()
         P.topk_ks, P.topk_ps = self.topk.top_ks.data_ptr(), self.topk.top_ps.data_ptr()
         P.topk_skip, P.max_top_k = self.topk.skip.data_ptr(), self.max_top_k
+        if self._has_topp():
+            P.topp_states = self.topp.curand.data_ptr()
+            P.topp_ps, P.topp_skip = self.topp.top_ps.data_ptr(), self.topp.skip.data_ptr()
+            P.topp_initial_ps, P.topp_decay = self.topp.initial.data_ptr(), self.topp.decay.data_ptr()
+            P.topp_min, P.topp_reset_ids = self.topp.min.data_ptr(), self.topp.reset.data_ptr()
         for key, width in (("sequence_length", 4), ("finished", 1)):
             t = outputs.get(key)
             setattr(P, key, None if t is None else t.data_ptr())
@@ -66,12 +78,17 @@ class VocabParallelSampler(DynamicDecodeLayer):
         P.stream = self._stream_ptr().value
         return P
 
+    def _has_topp(self):
+        return self.topp.active and not bool(self.topp.skip_host.all())
+
     @property
     def cap(self):
-        return self.max_top_k + self.cap_extra
+        k = max(self.max_top_k, self.topp_candidates) if self._has_topp() else self.max_top_k
+        return min(k, 1024) + self.cap_extra
 
     def local_pass(self, outputs, inputs, shard_logits, shard_index, records):
-        """Candidates of one shard -> records [batch, 1 + cap] (int64 view of the 64-bit words)."""
+        """Candidates of one shard -> records [batch, 2 + cap] (int64 view of the 64-bit words: count, entries,
+        and for top-p rows the shard's soft-max statistics in the last word)."""
         off = shard_index * self.shard_size
         vocab = max(0, min(self.shard_size, self.vocab_size - off))
         P = self._params(outputs, inputs, shard_logits, max(vocab, 1), self.shard_size)
@@ -85,7 +102,7 @@ class VocabParallelSampler(DynamicDecodeLayer):
         self.launches += 1
 
     def _buffers(self, B):
-        shape = (B, 1 + self.cap)
+        shape = (B, 2 + self.cap)
         if self._records is None or tuple(self._records.shape) != shape:
             self._records = torch.zeros(shape, dtype=torch.int64, device=self.device)
             self._gathered = torch.zeros((self.n_shards,) + shape, dtype=torch.int64, device=self.device)

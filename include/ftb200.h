@@ -291,20 +291,29 @@ int ftb200_beam_workspace_bytes(int local_batch_size, int beam_width, size_t* by
 int ftb200_beam_search_step(const ftb200_beam_params* p);
 
 /* ------------------------------------------------------------------------------------------
- * Vocabulary-parallel top-k sampling: each GPU holds a column shard [local_batch, V/n] of the logits
+ * Vocabulary-parallel sampling: each GPU holds a column shard [local_batch, V/n] of the logits
  * (the tensor-parallel lm_head before FT's all-gather, models/multi_gpu_gpt/ParallelGpt.cc:1394-1435).
  * Instead of gathering the full fp32 logits and sampling redundantly on every rank, each rank
- *   1. ftb200_vocab_parallel_local: runs the fused penalties + top-k selection on its shard and emits,
- *      per row, one record of (1 + cap) 64-bit words: the count, then (value, global column) entries
- *      for every column whose value reaches the shard's k-th value (whole tie class included);
- *   2. exchanges the records with ONE all-gather (ncclAllGather of local_batch*(1+cap)*8 bytes);
+ *   1. ftb200_vocab_parallel_local: runs the fused penalties + selection on its shard and emits, per
+ *      row, one record of (2 + cap) 64-bit words: the count, then up to cap (value, global column)
+ *      entries, then one statistics word.  Top-k rows: every column whose value reaches the shard's
+ *      k-th value (whole tie class included).  Top-p rows: the shard's largest columns (cap - 64 of
+ *      them when cap > 128, else cap / 2) and, in the statistics word, two floats (maximum of the
+ *      shard's final values << 32 | sum of exp(value - maximum));
+ *   2. exchanges the records with ONE all-gather (ncclAllGather of local_batch*(2+cap)*8 bytes);
  *   3. ftb200_vocab_parallel_merge: merges the n records of a row and draws with the row's curand
  *      state.  All ranks hold the same states, so all ranks produce the same id - no broadcast.
- * The ids equal what ftb200_decode_step_sampling returns on the gathered row (and therefore the
- * reference's).  `p` is the same argument block; in step 1 `logits`/`vocab_size`/`vocab_size_padded`
- * describe the shard and token ids (history, bad words, end id) stay global; `vocab_offset` is the
- * shard's first column.  Top-k rows without log-probs only.  A row with more than `cap` columns in play
- * on some shard is reported through *overflow_count (device int, incremented) and gets id -1.
+ * Top-k rows: the ids equal what ftb200_decode_step_sampling returns on the gathered row (and
+ * therefore the reference's).  Top-p rows: the (maximum, sum) pairs are combined as an online
+ * soft-max combines them (reduce_md_op, kernels/online_softmax_beamsearch_kernels.cu:270-279), so the
+ * denominator is not summed in the single-GPU order; a draw within rounding of a boundary may pick
+ * the neighbouring column, everything else is the same id.
+ * `p` is the same argument block; in step 1 `logits`/`vocab_size`/`vocab_size_padded` describe the
+ * shard and token ids (history, bad words, end id) stay global; `vocab_offset` is the shard's first
+ * column.  No log-probs.  A row that cannot be decided from the records - more than `cap` columns in
+ * play on some shard, a top-p nucleus larger than the union of what the shards sent - is reported
+ * through *overflow_count (device int, incremented) and gets id -1: the caller repeats it with a
+ * larger cap or on gathered logits.
  * ------------------------------------------------------------------------------------------ */
 int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int vocab_offset, int cap, uint64_t* records);
 int ftb200_vocab_parallel_merge(const ftb200_sampling_params* p, const uint64_t* gathered, int n_ranks, int cap,

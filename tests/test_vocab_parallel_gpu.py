@@ -47,3 +47,65 @@ def test_shards_match_full_row(n_shards, shard, k, coarse, cuda_device):
         assert vp.overflow_count() == 0
         for key in ("output_ids", "finished", "sequence_length"):
             assert torch.equal(s_full[key], s_vp[key]), (s, key)
+
+
+@pytest.mark.parametrize("dtype,n_shards,sigma,max_undecided", [(torch.bfloat16, 4, 4.0, 0.2), (torch.float16, 2, 5.0, 0.2),
+                                                                (torch.float32, 8, 6.0, 0.2), (torch.bfloat16, 4, 1.2, 1.0)])
+def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, cuda_device):
+    """Mixed top-k / top-p rows over a sharded vocabulary against the unsharded kernel.  Top-k rows must be
+    identical.  Top-p rows combine per-shard soft-max statistics, so their denominator is summed in another
+    order: ids are compared, and the few rows the exchange cannot decide (reported, id -1) are excluded."""
+    from fastertransformer_b200 import DynamicDecodeLayer
+    from fastertransformer_b200.vocab_parallel import VocabParallelSampler
+    B, shard, mil, steps = 96, 4096, 6, 4
+    V = shard * n_shards
+    rng = np.random.default_rng(17 + n_shards)
+    args = {"runtime_top_k": rng.choice(np.asarray([0, 0, 8, 40], np.uint32), size=B),
+            "runtime_top_p": rng.choice(np.asarray([0.3, 0.6, 0.9], np.float32), size=B),
+            "temperature": np.asarray([0.9], np.float32), "repetition_penalty": np.asarray([1.2], np.float32),
+            "random_seed": (np.arange(B) * 5 + 3).astype(np.uint64)}
+    prompt = rng.integers(0, V, size=(mil, B)).astype(np.int32)
+
+    def state():
+        ids = torch.zeros(mil + steps, B, dtype=torch.int32, device=cuda_device)
+        ids[:mil] = torch.from_numpy(prompt).to(cuda_device)
+        return {"output_ids": ids, "finished": torch.zeros(B, dtype=torch.bool, device=cuda_device),
+                "sequence_length": torch.full((B,), mil, dtype=torch.int32, device=cuda_device)}
+
+    full = DynamicDecodeLayer(V, V, dtype, cuda_device)
+    full.setup(B, 1, args)
+    vp = VocabParallelSampler(V, shard, n_shards, dtype, cuda_device)
+    vp.setup(B, 1, args)
+    st_a, st_b = state(), state()
+    end = torch.full((B,), V - 1, dtype=torch.int32, device=cuda_device)
+    is_topp = (args["runtime_top_k"] == 0)
+    g = torch.Generator(device=cuda_device)
+    same_topp = total_topp = undecided = 0
+    for s in range(steps):
+        g.manual_seed(900 + s)
+        x = (torch.randn(B, V, generator=g, device=cuda_device) * sigma).to(dtype)
+        inp = {"step": mil + s, "max_input_length": mil, "end_id": end, "ite": 0, "local_batch_size": B}
+        full.forward(st_a, dict(inp, logits=x))
+        vp.forward_shards(st_b, inp, [x[:, i * shard:(i + 1) * shard].contiguous() for i in range(n_shards)])
+        a = st_a["output_ids"][mil + s].cpu().numpy()
+        b = st_b["output_ids"][mil + s].cpu().numpy()
+        assert np.array_equal(a[~is_topp], b[~is_topp]), "top-k rows must not depend on the sharding"
+        und = b == -1
+        assert not und[~is_topp].any()
+        undecided += int(und.sum())
+        ok = is_topp & ~und
+        same_topp += int((a[ok] == b[ok]).sum())
+        total_topp += int(ok.sum())
+        # keep both histories identical so that later steps stay comparable
+        st_b["output_ids"][mil + s].copy_(st_a["output_ids"][mil + s])
+        st_b["finished"].copy_(st_a["finished"])
+        st_b["sequence_length"].copy_(st_a["sequence_length"])
+    print("top-p rows: %d of %d ids equal to the unsharded kernel, %d undecided" % (same_topp, total_topp, undecided))
+    assert vp.overflow_count() == undecided
+    # (flat logits: the nucleus outgrows what the shards send - those rows have to come back undecided, not wrong)
+    assert undecided <= max_undecided * is_topp.sum() * steps
+    if max_undecided < 1.0:
+        assert total_topp > 0
+    else:
+        assert undecided > 0
+    assert same_topp >= 0.97 * total_topp, (same_topp, total_topp)
