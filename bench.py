@@ -398,7 +398,7 @@ def run_vocab_parallel(a, rank, world, local):
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 logits", "data": "synthetic",
             "config": {"workload": "c5: vocab 256000 in %d shards of %d, batch 2048, k=64, p=0.92, T=0.7" % (n_shards, shard),
-                       "allgather_bytes_per_rank": B * (1 + vp.cap) * 8, "ids_identical_on_all_ranks": bool(same),
+                       "allgather_bytes_per_rank": B * (2 + vp.cap) * 8, "ids_identical_on_all_ranks": bool(same),
                        "overflow_rows": vp.overflow_count()},
             "roofline": {"bound": "hbm", "achieved": alg / (ms / steps * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": alg / (ms / steps * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind},

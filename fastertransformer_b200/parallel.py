@@ -22,12 +22,13 @@ def float_key(x):
 
 
 def pack_record(values, k, cap, vocab_offset):
-    """Record of one row of one shard: [count, entries...] as uint64, entries = (~key(value) << 32 | global
-    column) for every column whose value reaches the shard's k-th largest value (whole tie class), sorted
-    by value descending then column.  count = 2^64-1 if more than `cap` columns qualify."""
+    """Record of one row of one shard: [count, cap entry slots, statistics word] as uint64, entries =
+    (~key(value) << 32 | global column) for every column whose value reaches the shard's k-th largest value
+    (whole tie class), sorted by value descending then column.  count = 2^64-1 if more than `cap` columns
+    qualify.  The statistics word (soft-max pair of a top-p row) stays 0 for top-k rows."""
     values = np.asarray(values, dtype=np.float32)
     alive = np.flatnonzero(values > -np.finfo(np.float32).max)
-    rec = np.zeros(1 + cap, dtype=np.uint64)
+    rec = np.zeros(2 + cap, dtype=np.uint64)
     if alive.size == 0:
         return rec
     order = alive[np.lexsort((alive, -values[alive].astype(np.float64)))]
