@@ -61,7 +61,7 @@ def _worker(rank, world, port, q):
     # (2) vocabulary-parallel records
     shard, cap = V // world, K + 32
     rec = np.stack([pack_record(logits[b, rank * shard:(rank + 1) * shard], K, cap, rank * shard) for b in range(B)])
-    gathered = [torch.zeros(B, 1 + cap, dtype=torch.int64) for _ in range(world)]
+    gathered = [torch.zeros(B, 2 + cap, dtype=torch.int64) for _ in range(world)]
     dist.all_gather(gathered, torch.from_numpy(rec.view(np.int64)))
     merged = np.stack([merge_records([g.numpy().view(np.uint64)[b] for g in gathered], V) for b in range(B)])
     vp_ids = _decode(merged, prompt, u, list(range(B)))
