@@ -52,7 +52,23 @@ __device__ __forceinline__ u64 global_timer_ns()
     return t;
 }
 
-// Diagnostic timeline: trace_mark(i) stores the time at which thread 0 passed mark i of the current row.
+// Diagnostic timeline: trace_mark(rec, i) stores the time at which thread 0 passed mark i of the current row.
+// Marks (per row ticket, after the four header words row / CTA / start / end):
+//   every soft-max row (top-p, top-k with log-probs)      two-pass top-k rows
+//     0  row set-up done                                    0  row set-up done
+//     1  maximum pass and special-column fetch done         1  slot-maximum pass and special-column fetch done
+//    15  special columns compared with the maximum          2  cut chosen
+//     2  row maximum known                                  3  filtered pass done
+//    12  per-thread patch lists built                       4  special columns visited
+//    13  ordered soft-max pass done (whole chunks)          5  sort and draw done
+//     3  soft-max pass done (row tail included)
+//    17  denominator reduced
+//    19  provisional cut searched
+//     4  provisional cut chosen
+//   value-class path (16-bit top-p rows): 20 class count done, 5 special columns listed, 22 their sort done,
+//     6 runs built (word 24 holds N | dense << 32 | runs << 40), 25 chunk aggregates done, 7 crossing found,
+//     27 class of the crossing known, 8 class members collected; 11 class path left for the general path
+//     (word 25: which check sent the row away).
 constexpr int kTraceWords = 32;  // per row ticket: row, CTA, start, end, 28 marks
 static __device__ void trace_mark(u64* rec, int i)
 {
@@ -3546,12 +3562,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
         u64*      rec = P.trace != nullptr ? P.trace + (size_t)t * kTraceWords : nullptr;
         if (rec != nullptr && threadIdx.x == 0) {
             rec[0] = (u64)r, rec[1] = (u64)blockIdx.x, rec[2] = global_timer_ns();
-            rec[30] = (u64)clock64();
         }
         process_row<DT>(P, S, r, gscratch, rec);
         if (rec != nullptr && threadIdx.x == 0) {
             rec[3] = global_timer_ns();
-            rec[31] = (u64)clock64();
         }
     }
 }
