@@ -10,7 +10,7 @@ _LAZY = {
     "lib": "._lib", "FtbError": "._lib", "SamplingParams": "._lib", "check": "._lib",
     "BeamParams": "._lib", "BeamHyps": "._lib",
     "DynamicDecodeLayer": ".decode_layer", "DynamicDecodeOp": ".th_decode_op",
-    "VocabParallelSampler": ".vocab_parallel",
+    "VocabParallelSampler": ".vocab_parallel", "log_prob_from_logits": ".logprob",
 }
 
 

@@ -43,6 +43,8 @@ def _load():
     l.ftb200_ban_bad_words.argtypes = [V, I, V, V, I, I, I, V, I, I, I, I, I, V]
     l.ftb200_stop_criteria.argtypes = [V, V, V, I, V, V, I, I, I, I, I, V, V, V]
     l.ftb200_wait_should_stop.argtypes = [V, I, I, V, I, C.POINTER(C.c_int)]
+    Z = C.c_size_t
+    l.ftb200_log_prob_from_logits.argtypes = [V, V, I, V, V, Z, Z, Z, Z, V, Z, V, I]
     return l
 
 

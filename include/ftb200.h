@@ -319,6 +319,24 @@ int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int vocab_offse
 int ftb200_vocab_parallel_merge(const ftb200_sampling_params* p, const uint64_t* gathered, int n_ranks, int cap,
                                 int* overflow_count);
 
+/* ------------------------------------------------------------------------------------------------
+ * Log-probability of given token ids under the soft-max of context logits, summed per sequence.
+ * Replaces invokeLogProbFromLogits<T> (kernels/logprob_kernels.h:23-35, kernels/logprob_kernels.cu:142-183)
+ * with the same argument order and meaning; `dtype` stands for the template parameter:
+ *   cum_log_probs[b] = sum over step < input_lengths[b] - 1 of
+ *                      log softmax(logits[step, b, :vocab_size])[input_ids[step + 1, b]]
+ * logits:    [max_input_length, batch_size, vocab_size_padded], or batch-major when batch_first != 0;
+ * input_ids: [max_input_length, batch_size], or [batch_size, max_input_length] when batch_first != 0;
+ * workspace: device memory of at least sizeof(float) * max_input_length * batch_size bytes (the
+ *            per-step log-probs land there in the reference's layout, log_probs_kernel :36-103).
+ * Differences: row offsets are 64-bit (the reference's are int and wrap past 2^31 elements); an id
+ * outside [0, vocab_size_padded) gives NaN instead of an unchecked read; bf16 is accepted.
+ * ------------------------------------------------------------------------------------------ */
+int ftb200_log_prob_from_logits(float* cum_log_probs, const void* logits, int dtype, const int* input_ids,
+                                const int* input_lengths, size_t max_input_length, size_t batch_size,
+                                size_t vocab_size, size_t vocab_size_padded, void* workspace, size_t workspace_size,
+                                void* stream, int batch_first);
+
 #ifdef __cplusplus
 }
 #endif

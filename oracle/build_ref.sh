@@ -34,6 +34,7 @@ SRCS=(
     "$S/kernels/online_softmax_beamsearch_kernels.cu"
     "$S/kernels/beam_search_penalty_kernels.cu"
     "$S/kernels/beam_search_topk_kernels.cu"
+    "$S/kernels/logprob_kernels.cu"
     "$S/layers/DynamicDecodeLayer.cc"
     "$S/layers/sampling_layers/BaseSamplingLayer.cc"
     "$S/layers/sampling_layers/TopKSamplingLayer.cu"

@@ -937,3 +937,61 @@ extern "C" int oracle_beam_search_step(const ftb200_beam_params* p)
     }
     return 0;
 }
+
+// invokeLogProbFromLogits, kernels/logprob_kernels.cu:142-183: log_probs_kernel (:36-103) per (step, sequence)
+// with block_size threads (:165), then accumulate_log_probs (:105-140).  The partial maxima and sums follow the
+// kernel's thread striding and its block reductions; expf/logf stand for the fast-math __expf/__logf.
+// `log_probs` (may be null) receives the per-step values in the kernel's workspace layout.
+extern "C" int oracle_log_prob_from_logits(float* cum_log_probs, float* log_probs, const void* logits, int dtype,
+                                           const int* input_ids, const int* input_lengths, size_t max_input_length,
+                                           size_t batch_size, size_t vocab_size, size_t vocab_size_padded,
+                                           int batch_first)
+{
+    const int    nthr  = vocab_size < 1024 ? (int)((vocab_size + 31) / 32 * 32) : 1024;
+    const float  lowest = dtype == FTB200_F16 ? -65504.0f : -FLT_MAX;
+    const size_t steps = max_input_length - 1;
+    const RowView L{dtype, logits, vocab_size_padded};
+    std::vector<float> lp(steps * batch_size, 0.0f);
+#pragma omp parallel for schedule(dynamic)
+    for (long long r = 0; r < (long long)(steps * batch_size); ++r) {
+        const size_t b = batch_first ? (size_t)r / steps : (size_t)r % batch_size;
+        const size_t step = batch_first ? (size_t)r % steps : (size_t)r / batch_size;
+        if ((int)step >= input_lengths[b] - 1) {
+            continue;
+        }
+        const size_t row = batch_first ? b * max_input_length + step : step * batch_size + b;
+        float        mx  = lowest;  // the maximum is exact whatever the order
+        for (size_t v = 0; v < vocab_size; ++v) {
+            mx = std::fmax(mx, L.get(row, v));
+        }
+        std::vector<float> partial(nthr, 0.0f);
+        for (int t = 0; t < nthr; ++t) {
+            float s = 0.0f;
+            for (size_t v = t; v < vocab_size; v += nthr) {
+                s += std::exp(L.get(row, v) - mx);
+            }
+            partial[t] = s;
+        }
+        const float  sum = butterfly_block_sum(partial, nthr);
+        const size_t out = batch_first ? b * steps + step : step * batch_size + b;
+        const size_t tok = batch_first ? b * max_input_length + step + 1 : (step + 1) * batch_size + b;
+        lp[out]          = L.get(row, (size_t)input_ids[tok]) - mx - std::log(sum + 1e-9f);
+    }
+    for (size_t b = 0; b < batch_size; ++b) {
+        std::vector<float> partial(nthr, 0.0f);
+        const size_t       stride = batch_first ? 1 : batch_size;
+        const float*       p = lp.data() + (batch_first ? b * steps : b);
+        for (int t = 0; t < nthr; ++t) {
+            float s = 0.0f;
+            for (long long step = t; step < (long long)input_lengths[b] - 1 && step < (long long)steps; step += nthr) {
+                s += p[(size_t)step * stride];
+            }
+            partial[t] = s;
+        }
+        cum_log_probs[b] = butterfly_block_sum(partial, nthr);
+    }
+    if (log_probs) {
+        std::memcpy(log_probs, lp.data(), lp.size() * sizeof(float));
+    }
+    return 0;
+}

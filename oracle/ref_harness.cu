@@ -18,6 +18,7 @@
 #include <string>
 
 #include "src/fastertransformer/kernels/beam_search_topk_kernels.h"
+#include "src/fastertransformer/kernels/logprob_kernels.h"
 #include "src/fastertransformer/kernels/sampling_topk_kernels.h"
 #include "src/fastertransformer/layers/DynamicDecodeLayer.h"
 #include "src/fastertransformer/utils/Tensor.h"
@@ -338,6 +339,25 @@ int ftref_curand_uniforms(const void* states, int n, int n_draws, float* out_dev
 {
     ftref_uniform_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
         (const curandState_t*)states, n, n_draws, out_dev);
+    return (int)cudaGetLastError();
+}
+
+/* invokeLogProbFromLogits<T> (kernels/logprob_kernels.cu:142-183) on device pointers; dtype 0 = float, 1 = half. */
+int ftref_log_prob_from_logits(float* cum_log_probs, const void* logits, int dtype, const int* input_ids,
+                               const int* input_lengths, size_t max_input_length, size_t batch_size,
+                               size_t vocab_size, size_t vocab_size_padded, void* workspace, size_t workspace_size,
+                               void* stream, int batch_first)
+{
+    if (dtype == 0) {
+        ft::invokeLogProbFromLogits(cum_log_probs, (const float*)logits, input_ids, input_lengths, max_input_length,
+                                    batch_size, vocab_size, vocab_size_padded, workspace, workspace_size,
+                                    (cudaStream_t)stream, batch_first != 0);
+    }
+    else {
+        ft::invokeLogProbFromLogits(cum_log_probs, (const half*)logits, input_ids, input_lengths, max_input_length,
+                                    batch_size, vocab_size, vocab_size_padded, workspace, workspace_size,
+                                    (cudaStream_t)stream, batch_first != 0);
+    }
     return (int)cudaGetLastError();
 }
 

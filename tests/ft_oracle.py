@@ -28,6 +28,8 @@ def oracle_lib():
         _lib.oracle_length_criterion.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
         _lib.oracle_stop_words.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                            C.c_int]
+        Z = C.c_size_t
+        _lib.oracle_log_prob_from_logits.argtypes = [V, V, V, C.c_int, V, V, Z, Z, Z, Z, C.c_int]
     return _lib
 
 
@@ -175,3 +177,25 @@ class OracleDynamicDecodeLayer:
         if olp is not None:
             P.output_log_probs = olp.ctypes.data + ((step - mil) * B + lo) * 4
         self.lib.oracle_decode_step_sampling(C.byref(P))
+
+
+def oracle_log_prob_from_logits(logits, input_ids, input_lengths, vocab_size, batch_first=False,
+                                dtype_name=None):
+    """oracle_log_prob_from_logits on host arrays; returns (cum_log_probs [batch], log_probs in the
+    reference's workspace layout).  bf16 logits come as uint16 bit patterns with dtype_name='bfloat16'."""
+    lib = oracle_lib()
+    logits = np.ascontiguousarray(logits)
+    dtype_name = dtype_name or str(logits.dtype)
+    if batch_first:
+        batch, max_len, vp = logits.shape
+    else:
+        max_len, batch, vp = logits.shape
+    ids = np.ascontiguousarray(input_ids, dtype=np.int32)
+    lens = np.ascontiguousarray(input_lengths, dtype=np.int32)
+    cum = np.zeros(batch, np.float32)
+    lp = np.zeros(max(1, (max_len - 1) * batch), np.float32)
+    rc = lib.oracle_log_prob_from_logits(_p(cum), _p(lp), _p(logits), _DT[dtype_name], _p(ids), _p(lens), max_len,
+                                         batch, vocab_size, vp, int(batch_first))
+    assert rc == 0
+    shape = (batch, max_len - 1) if batch_first else (max_len - 1, batch)
+    return cum, lp[:(max_len - 1) * batch].reshape(shape)

@@ -65,6 +65,8 @@ def ref_lib():
         _lib.ftref_last_error.restype = C.c_char_p
         _lib.ftref_curand_init.argtypes = [C.c_void_p, C.c_int, C.c_ulonglong, C.c_void_p, C.c_void_p]
         _lib.ftref_curand_uniforms.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        V, Z = C.c_void_p, C.c_size_t
+        _lib.ftref_log_prob_from_logits.argtypes = [V, V, C.c_int, V, V, Z, Z, Z, Z, V, Z, V, C.c_int]
     return _lib
 
 
