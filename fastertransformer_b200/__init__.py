@@ -8,7 +8,7 @@ entry point without the built library raises ImportError: there is no CPU fallba
 
 _LAZY = {
     "lib": "._lib", "FtbError": "._lib", "SamplingParams": "._lib", "check": "._lib",
-    "BeamParams": "._lib", "BeamHyps": "._lib",
+    "BeamParams": "._lib", "BeamHyps": "._lib", "GatherTreeParams": "._lib",
     "DynamicDecodeLayer": ".decode_layer", "DynamicDecodeOp": ".th_decode_op",
     "VocabParallelSampler": ".vocab_parallel", "log_prob_from_logits": ".logprob",
 }

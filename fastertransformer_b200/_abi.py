@@ -50,3 +50,15 @@ class BeamParams(C.Structure):
         ("beam_hyps", C.POINTER(BeamHyps)),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
     ]
+
+
+class GatherTreeParams(C.Structure):
+    """ftb200_gather_tree_params (the fields of the reference's gatherTreeParam, in its order)."""
+    _fields_ = [
+        ("beams", C.c_void_p), ("max_sequence_lengths", C.c_void_p), ("max_sequence_length_final_step", C.c_int),
+        ("input_lengths", C.c_void_p), ("response_input_lengths", C.c_void_p), ("max_time", C.c_int),
+        ("batch_size", C.c_int), ("beam_width", C.c_int), ("step_ids", C.c_void_p), ("parent_ids", C.c_void_p),
+        ("end_tokens", C.c_void_p), ("max_input_length", C.c_int), ("prefix_soft_prompt_lengths", C.c_void_p),
+        ("p_prompt_tuning_prompt_lengths", C.c_void_p), ("max_input_without_prompt_length", C.c_int),
+        ("max_prefix_soft_prompt_length", C.c_int), ("output_ids", C.c_void_p), ("stream", C.c_void_p),
+    ]

@@ -12,7 +12,7 @@ class FtbError(RuntimeError):
         self.status = status
 
 
-from ._abi import BeamHyps, BeamParams, SamplingParams  # noqa: E402,F401
+from ._abi import BeamHyps, BeamParams, GatherTreeParams, SamplingParams  # noqa: E402,F401
 
 
 def _load():
@@ -45,6 +45,10 @@ def _load():
     l.ftb200_wait_should_stop.argtypes = [V, I, I, V, I, C.POINTER(C.c_int)]
     Z = C.c_size_t
     l.ftb200_log_prob_from_logits.argtypes = [V, V, I, V, V, Z, Z, Z, Z, V, Z, V, I]
+    l.ftb200_decoding_initialize.argtypes = [V, V, V, V, I, V, I, I, I, V]
+    l.ftb200_gather_tree.argtypes = [C.POINTER(GatherTreeParams)]
+    l.ftb200_finalize.argtypes = [V, V, V, V, V, V, V, V, V, V, I, I, I, V]
+    l.ftb200_insert_unfinished_path.argtypes = [C.POINTER(BeamHyps), V, V, V, V, I, C.c_float, V, V, I, I, V]
     return l
 
 

@@ -337,6 +337,71 @@ int ftb200_log_prob_from_logits(float* cum_log_probs, const void* logits, int dt
                                 size_t vocab_size, size_t vocab_size_padded, void* workspace, size_t workspace_size,
                                 void* stream, int batch_first);
 
+/* ------------------------------------------------------------------------------------------------
+ * Caller-side steps either side of the per-step path (device pointers throughout).
+ * ------------------------------------------------------------------------------------------ */
+
+/* invokeDecodingInitialize<T> (kernels/decoding_kernels.h:25-34, decoding_kernels.cu:26-64): finished = 0,
+ * sequence_length = max_input_length, word_ids[i] = sentence_ids[i / beam_width] (when word_ids is given),
+ * cum_log_probs = 0 for beam 0 of each entry and -1e20 (-65504 for half) for the others.  `dtype` is the type
+ * of cum_log_probs. */
+int ftb200_decoding_initialize(uint8_t* finished, int* sequence_length, int* word_ids, void* cum_log_probs,
+                               int dtype, const int* sentence_ids, int batch_size, int beam_width,
+                               int max_input_length, void* stream);
+
+/* Mirrors gatherTreeParam, kernels/decoding_kernels.h:123-145, field for field. */
+typedef struct ftb200_gather_tree_params {
+    int*       beams;                          /* [max_time, batch_size, beam_width] out */
+    int*       max_sequence_lengths;           /* [batch_size, beam_width] in/out */
+    int        max_sequence_length_final_step;
+    const int* input_lengths;                  /* [batch_size, beam_width] or null */
+    int*       response_input_lengths;         /* [batch_size, beam_width] out, or null */
+    int        max_time;
+    int        batch_size;
+    int        beam_width;
+    const int* step_ids;                       /* [max_time, batch_size, beam_width] */
+    const int* parent_ids;                     /* same shape, or null (every parent 0) */
+    const int* end_tokens;                     /* [batch_size] */
+    int        max_input_length;
+    const int* prefix_soft_prompt_lengths;     /* [batch_size] or null */
+    const int* p_prompt_tuning_prompt_lengths; /* [batch_size] or null */
+    int        max_input_without_prompt_length;
+    int        max_prefix_soft_prompt_length;
+    int*       output_ids;                     /* [batch_size, beam_width, out_len] out, or null */
+    void*      stream;
+} ftb200_gather_tree_params;
+
+/* invokeGatherTree(gatherTreeParam) (kernels/decoding_kernels.cu:452-646): follows each beam's parents back
+ * from its last step, drops prompt and padding positions, pads with the entry's end token, leaves nothing but
+ * end tokens after the first one, and writes the transposed ids.  Set max_input_length = 1 and the prompt
+ * fields to null/0 for the two short overloads (:585-634).
+ * Differences: the reference lets every thread of an entry rewrite all of the entry's max_sequence_lengths
+ * (racy once an entry's beams span two warps); here each length is updated once, which is what the lockstep
+ * case gives, and response_input_lengths[i] uses beam i's own input length.  Writes at a negative time index
+ * (sequence shorter than its padding) are skipped instead of issued.  beam_width <= 1024. */
+int ftb200_gather_tree(const ftb200_gather_tree_params* p);
+
+/* invokeFinalize (kernels/decoding_kernels.h:155-168, decoding_kernels.cu:698-804): ranks the archived
+ * hypotheses of each entry by score (first index wins ties) and copies the best beam_width of them, without
+ * the start token.  topk_output_ids / topk_log_probs: [batch, 2 * beam_width, max_seq_len + 1]; output_ids /
+ * output_log_probs: [batch, beam_width, max_seq_len].  Entries past num_beams[b] resolve to archive slot 0
+ * (what the reference finds once its candidates are used up). */
+int ftb200_finalize(int* output_ids, int* sequence_lengths, float* cum_log_probs, float* output_log_probs,
+                    const int* topk_output_ids, const int* topk_sequence_lengths, const float* scores,
+                    const float* topk_cum_log_probs, const float* topk_log_probs, const int* num_beams,
+                    int beam_width, int max_seq_len, int batch_size, void* stream);
+
+/* invokeInsertUnfinishedPath (kernels/beam_search_topk_kernels.h:104-109, beam_search_topk_kernels.cu:788-843):
+ * appends the beam_width live beams of every entry that is not done to its archive, following parent ids back
+ * to step 0.  The BeamHypotheses fields the reference reads travel as arguments: `hyps` holds the archive
+ * (rows of max_seq_len + 1 here, as the reference indexes them in this kernel), the *_src tables are
+ * [step, batch_size * beam_width].  An out-of-range parent id is clamped instead of followed.
+ * beam_width <= 512. */
+int ftb200_insert_unfinished_path(const ftb200_beam_hyps* hyps, const int* output_ids_src, const int* parent_ids_src,
+                                  const int* sequence_lengths_src, const float* log_probs_src, int max_seq_len,
+                                  float length_penalty, const uint8_t* finished, const float* cum_log_probs,
+                                  int batch_size, int beam_width, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

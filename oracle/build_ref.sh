@@ -35,6 +35,7 @@ SRCS=(
     "$S/kernels/beam_search_penalty_kernels.cu"
     "$S/kernels/beam_search_topk_kernels.cu"
     "$S/kernels/logprob_kernels.cu"
+    "$S/kernels/decoding_kernels.cu"
     "$S/layers/DynamicDecodeLayer.cc"
     "$S/layers/sampling_layers/BaseSamplingLayer.cc"
     "$S/layers/sampling_layers/TopKSamplingLayer.cu"

@@ -995,3 +995,195 @@ extern "C" int oracle_log_prob_from_logits(float* cum_log_probs, float* log_prob
     }
     return 0;
 }
+
+// ---- caller-side steps ---------------------------------------------------------------------------------------
+
+// decodingInitialize, kernels/decoding_kernels.cu:26-47.  cum_log_probs comes back as float whatever `dtype`
+// (the value the typed store would hold).
+extern "C" int oracle_decoding_initialize(uint8_t* finished, int* sequence_length, int* word_ids,
+                                          float* cum_log_probs, int dtype, const int* sentence_ids, int batch_size,
+                                          int beam_width, int max_input_length)
+{
+    float floor_v = -1e20f;
+    if (dtype == FTB200_F16) {
+        floor_v = -65504.0f;
+    }
+    else if (dtype == FTB200_BF16) {
+        uint32_t u;
+        std::memcpy(&u, &floor_v, 4);
+        u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;  // round to nearest even on 16 bits
+        std::memcpy(&floor_v, &u, 4);
+    }
+    for (int i = 0; i < batch_size * beam_width; ++i) {
+        finished[i]        = 0;
+        sequence_length[i] = max_input_length;
+        if (word_ids != nullptr) {
+            word_ids[i] = sentence_ids[i / beam_width];
+        }
+        cum_log_probs[i] = i % beam_width == 0 ? 0.0f : floor_v;
+    }
+    return 0;
+}
+
+// gatherTree, kernels/decoding_kernels.cu:452-583, one (entry, beam) at a time.  The length update that every
+// thread of an entry repeats (:496-511) is done once per entry: the outcome when the entry's threads run in
+// lockstep.
+extern "C" int oracle_gather_tree(const ftb200_gather_tree_params* p)
+{
+    const int K = p->beam_width, B = p->batch_size;
+    const int max_input_length = p->input_lengths == nullptr ? 0 : p->max_input_length;
+    const int trimmed = p->max_prefix_soft_prompt_length + (p->max_input_length - p->max_input_without_prompt_length);
+    for (int batch = 0; batch < B; ++batch) {
+        const int prompt_len = p->prefix_soft_prompt_lengths ? p->prefix_soft_prompt_lengths[batch] : 0;
+        const int virt = p->p_prompt_tuning_prompt_lengths ? p->p_prompt_tuning_prompt_lengths[batch] : 0;
+        int       max_len = -1;
+        for (int j = 0; j < K; ++j) {
+            const int tmp_len = p->max_sequence_lengths[batch * K + j] + p->max_sequence_length_final_step;
+            p->max_sequence_lengths[batch * K + j] = tmp_len - trimmed;
+            if (p->response_input_lengths) {
+                p->response_input_lengths[batch * K + j] =
+                    (p->input_lengths ? p->input_lengths[batch * K + j] : 0) - virt - prompt_len;
+            }
+            max_len = std::max(max_len, tmp_len);
+        }
+        const int top = std::min(p->max_time, max_len);
+        if (top <= 0) {
+            continue;
+        }
+        const int end = p->end_tokens[batch];
+        for (int beam = 0; beam < K; ++beam) {
+            const int i = batch * K + beam;
+            const int input_len = (p->input_lengths ? p->input_lengths[i] : 0) - virt;
+            auto      ix = [&](int t, int bm) { return (size_t)B * K * t + (size_t)K * batch + bm; };
+            const int shift = max_input_length - input_len + prompt_len;
+            if (top - 1 - shift >= 0) {
+                p->beams[ix(top - 1 - shift, beam)] = p->step_ids[ix(top - 1, beam)];
+            }
+            int  parent = p->parent_ids ? p->parent_ids[ix(top - 1, beam)] % K : 0;
+            bool found_bad = false;
+            for (int level = top - 2; level >= 0; --level) {
+                if (level < prompt_len || (level >= input_len && level < max_input_length)) {
+                    continue;
+                }
+                const int tgt = level >= max_input_length ? level - shift : level - prompt_len;
+                if (parent < 0 || parent > K) {
+                    p->beams[ix(tgt, beam)] = end;
+                    parent                  = -1;
+                    found_bad               = true;
+                }
+                else {
+                    p->beams[ix(tgt, beam)] = p->step_ids[ix(level, parent)];
+                    parent                  = p->parent_ids ? p->parent_ids[ix(level, parent)] % K : 0;
+                }
+            }
+            for (int t = std::max(0, max_len - shift); t < p->max_time - p->max_prefix_soft_prompt_length; ++t) {
+                p->beams[ix(t, beam)] = end;
+            }
+            if (!found_bad) {
+                bool finished = false;
+                for (int t = max_input_length == 0 ? 1 : max_input_length; t < top; ++t) {
+                    if (finished) {
+                        p->beams[ix(t, beam)] = end;
+                    }
+                    else if (p->beams[ix(t, beam)] == end) {
+                        finished = true;
+                    }
+                }
+            }
+            const int out_len = p->max_time - trimmed;
+            if (p->output_ids) {
+                for (int j = 0; j < out_len; ++j) {
+                    p->output_ids[(size_t)i * out_len + j] = p->beams[(size_t)j * B * K + i];
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+// finalize, kernels/decoding_kernels.cu:698-771: beam_width rounds of "largest remaining score, first index wins".
+// Shared-memory slots past num_beams[b] are not initialised there; here they never match.
+extern "C" int oracle_finalize(int* output_ids, int* sequence_lengths, float* cum_log_probs, float* output_log_probs,
+                               const int* topk_output_ids, const int* topk_sequence_lengths, const float* scores,
+                               const float* topk_cum_log_probs, const float* topk_log_probs, const int* num_beams,
+                               int beam_width, int max_seq_len, int batch_size)
+{
+    const int K = beam_width;
+    for (int b = 0; b < batch_size; ++b) {
+        const int          n = std::max(0, std::min(num_beams[b], 2 * K));
+        std::vector<float> s(scores + (size_t)b * 2 * K, scores + (size_t)b * 2 * K + n);
+        std::vector<int>   rank(K, 0);
+        for (int i = 0; i < K; ++i) {
+            float mx = -FLT_MAX;
+            for (int j = 0; j < n; ++j) {
+                mx = std::max(mx, s[j]);
+            }
+            for (int j = 0; j < n; ++j) {
+                if (s[j] == mx) {
+                    rank[i] = j;
+                    s[j]    = -FLT_MAX;
+                    break;
+                }
+            }
+        }
+        for (int beam = 0; beam < K; ++beam) {
+            const size_t src = (size_t)b * 2 * K + rank[beam];
+            const int    len = topk_sequence_lengths[src];
+            sequence_lengths[b * K + beam] = len;
+            if (cum_log_probs) {
+                cum_log_probs[b * K + beam] = topk_cum_log_probs[src];
+            }
+            for (int i = 0; i < len; ++i) {
+                output_ids[((size_t)b * K + beam) * max_seq_len + i] = topk_output_ids[src * (max_seq_len + 1) + i + 1];
+                if (output_log_probs) {
+                    output_log_probs[((size_t)b * K + beam) * max_seq_len + i] =
+                        topk_log_probs[src * (max_seq_len + 1) + i + 1];
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+// insertUnfinishedPath, kernels/beam_search_topk_kernels.cu:788-832.
+extern "C" int oracle_insert_unfinished_path(const ftb200_beam_hyps* h, const int* output_ids_src,
+                                             const int* parent_ids_src, const int* sequence_lengths_src,
+                                             const float* log_probs_src, int max_seq_len, float length_penalty,
+                                             const uint8_t* finished, const float* cum_log_probs, int batch_size,
+                                             int beam_width)
+{
+    const int    K = beam_width;
+    const size_t BK = (size_t)batch_size * K, row = (size_t)max_seq_len + 1;
+    const bool   with_lp = h->log_probs != nullptr && log_probs_src != nullptr;
+    for (int bid = 0; bid < batch_size; ++bid) {
+        if (h->is_done[bid]) {
+            continue;
+        }
+        const int tgt_start = h->num_beams[bid];
+        for (int i = 0; i < K; ++i) {
+            const size_t src = (size_t)bid * K + i, tgt = (size_t)bid * K * 2 + i + tgt_start;
+            const int    length = sequence_lengths_src[src];
+            h->output_ids_tgt[tgt * row + length] = output_ids_src[length * BK + src];
+            if (with_lp) {
+                h->log_probs[tgt * row + length] = log_probs_src[length * BK + src];
+            }
+            int prev = parent_ids_src[length * BK + src];
+            for (int j = length - 1; j >= 0; --j) {
+                prev = std::min(std::max(prev, 0), K - 1);
+                const size_t g = j * BK + (size_t)bid * K + prev;
+                h->output_ids_tgt[tgt * row + j] = output_ids_src[g];
+                if (with_lp) {
+                    h->log_probs[tgt * row + j] = log_probs_src[g];
+                }
+                prev = parent_ids_src[g];
+            }
+            h->sequence_lengths_tgt[tgt] = length;
+            const int   n_tok = finished[src] ? length + 1 : length;
+            const float cum = cum_log_probs[src];
+            h->normed_scores[tgt] = (length_penalty == 0.0f || n_tok == 1) ? cum : cum / powf((float)n_tok, length_penalty);
+            h->cum_log_probs[tgt] = cum;
+            h->num_beams[bid]++;
+        }
+    }
+    return 0;
+}

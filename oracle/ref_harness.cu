@@ -18,6 +18,7 @@
 #include <string>
 
 #include "src/fastertransformer/kernels/beam_search_topk_kernels.h"
+#include "src/fastertransformer/kernels/decoding_kernels.h"
 #include "src/fastertransformer/kernels/logprob_kernels.h"
 #include "src/fastertransformer/kernels/sampling_topk_kernels.h"
 #include "src/fastertransformer/layers/DynamicDecodeLayer.h"
@@ -358,6 +359,102 @@ int ftref_log_prob_from_logits(float* cum_log_probs, const void* logits, int dty
                                     batch_size, vocab_size, vocab_size_padded, workspace, workspace_size,
                                     (cudaStream_t)stream, batch_first != 0);
     }
+    return (int)cudaGetLastError();
+}
+
+/* invokeDecodingInitialize<T> (kernels/decoding_kernels.cu:49-64); dtype 0 float, 1 half, 2 bf16. */
+int ftref_decoding_initialize(bool* finished, int* sequence_length, int* word_ids, void* cum_log_probs, int dtype,
+                              const int* sentence_ids, int batch_size, int beam_width, int max_input_length,
+                              void* stream)
+{
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == 0) {
+        ft::invokeDecodingInitialize(finished, sequence_length, word_ids, (float*)cum_log_probs, sentence_ids,
+                                     batch_size, beam_width, max_input_length, st);
+    }
+    else if (dtype == 1) {
+        ft::invokeDecodingInitialize(finished, sequence_length, word_ids, (half*)cum_log_probs, sentence_ids,
+                                     batch_size, beam_width, max_input_length, st);
+    }
+    else {
+        ft::invokeDecodingInitialize(finished, sequence_length, word_ids, (__nv_bfloat16*)cum_log_probs, sentence_ids,
+                                     batch_size, beam_width, max_input_length, st);
+    }
+    return (int)cudaGetLastError();
+}
+
+/* invokeGatherTree(gatherTreeParam) (kernels/decoding_kernels.cu:636-646); the arguments are gatherTreeParam's
+ * fields in their order. */
+int ftref_gather_tree(int* beams, int* max_sequence_lengths, int max_sequence_length_final_step,
+                      const int* input_lengths, int* response_input_lengths, int max_time, int batch_size,
+                      int beam_width, const int* step_ids, const int* parent_ids, const int* end_tokens,
+                      int max_input_length, const int* prefix_soft_prompt_lengths,
+                      const int* p_prompt_tuning_prompt_lengths, int max_input_without_prompt_length,
+                      int max_prefix_soft_prompt_length, int* output_ids, void* stream)
+{
+    ft::gatherTreeParam param;
+    param.beams                           = beams;
+    param.max_sequence_lengths            = max_sequence_lengths;
+    param.max_sequence_length_final_step  = max_sequence_length_final_step;
+    param.input_lengths                   = input_lengths;
+    param.response_input_lengths          = response_input_lengths;
+    param.max_time                        = max_time;
+    param.batch_size                      = batch_size;
+    param.beam_width                      = beam_width;
+    param.step_ids                        = step_ids;
+    param.parent_ids                      = parent_ids;
+    param.end_tokens                      = end_tokens;
+    param.max_input_length                = max_input_length;
+    param.prefix_soft_prompt_lengths      = prefix_soft_prompt_lengths;
+    param.p_prompt_tuning_prompt_lengths  = p_prompt_tuning_prompt_lengths;
+    param.max_input_without_prompt_length = max_input_without_prompt_length;
+    param.max_prefix_soft_prompt_length   = max_prefix_soft_prompt_length;
+    param.output_ids                      = output_ids;
+    param.stream                          = (cudaStream_t)stream;
+    ft::invokeGatherTree(param);
+    return (int)cudaGetLastError();
+}
+
+/* invokeFinalize (kernels/decoding_kernels.cu:773-804). */
+int ftref_finalize(int* output_ids, int* sequence_lengths, float* cum_log_probs, float* output_log_probs,
+                   const int* topk_output_ids, const int* topk_sequence_lengths, const float* scores,
+                   const float* topk_cum_log_probs, const float* topk_log_probs, const int* num_beams, int beam_width,
+                   int max_seq_len, int batch_size, void* stream)
+{
+    ft::invokeFinalize(output_ids, sequence_lengths, cum_log_probs, output_log_probs, topk_output_ids,
+                       topk_sequence_lengths, scores, topk_cum_log_probs, topk_log_probs, num_beams, beam_width,
+                       max_seq_len, batch_size, (cudaStream_t)stream);
+    return (int)cudaGetLastError();
+}
+
+/* invokeInsertUnfinishedPath (kernels/beam_search_topk_kernels.cu:834-843). */
+int ftref_insert_unfinished_path(int* output_ids_tgt, int* sequence_lengths_tgt, float* cum_log_probs_tgt,
+                                 float* normed_scores, float* log_probs_tgt, int* num_beams, bool* is_done,
+                                 const int* output_ids_src, const int* parent_ids_src,
+                                 const int* sequence_lengths_src, const float* log_probs_src, int max_seq_len,
+                                 float length_penalty, const bool* finished, const float* cum_log_probs,
+                                 int batch_size, int beam_width, void* stream)
+{
+    ft::BeamHypotheses h;
+    h.output_ids_tgt       = output_ids_tgt;
+    h.sequence_lengths_tgt = sequence_lengths_tgt;
+    h.cum_log_probs        = cum_log_probs_tgt;
+    h.normed_scores        = normed_scores;
+    h.log_probs            = log_probs_tgt;
+    h.num_beams            = num_beams;
+    h.is_done              = is_done;
+    h.output_ids_src       = output_ids_src;
+    h.parent_ids_src       = parent_ids_src;
+    h.sequence_lengths_src = sequence_lengths_src;
+    h.log_probs_src        = log_probs_src;
+    h.end_ids              = nullptr;
+    h.step                 = 0;
+    h.ite                  = 0;
+    h.batch_size           = batch_size;
+    h.local_batch_size     = batch_size;
+    h.max_seq_len          = max_seq_len;
+    h.length_penalty       = length_penalty;
+    ft::invokeInsertUnfinishedPath(h, finished, cum_log_probs, batch_size, beam_width, (cudaStream_t)stream);
     return (int)cudaGetLastError();
 }
 

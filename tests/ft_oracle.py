@@ -6,7 +6,7 @@ import subprocess
 
 import numpy as np
 
-from fastertransformer_b200._abi import SamplingParams
+from fastertransformer_b200._abi import BeamHyps, GatherTreeParams, SamplingParams
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORACLE_LIB = os.path.join(ROOT, "oracle", "libft_oracle.so")
@@ -30,6 +30,11 @@ def oracle_lib():
                                            C.c_int]
         Z = C.c_size_t
         _lib.oracle_log_prob_from_logits.argtypes = [V, V, V, C.c_int, V, V, Z, Z, Z, Z, C.c_int]
+        I = C.c_int
+        _lib.oracle_decoding_initialize.argtypes = [V, V, V, V, I, V, I, I, I]
+        _lib.oracle_gather_tree.argtypes = [C.POINTER(GatherTreeParams)]
+        _lib.oracle_finalize.argtypes = [V, V, V, V, V, V, V, V, V, V, I, I, I]
+        _lib.oracle_insert_unfinished_path.argtypes = [C.POINTER(BeamHyps), V, V, V, V, I, C.c_float, V, V, I, I]
     return _lib
 
 

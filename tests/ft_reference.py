@@ -67,6 +67,11 @@ def ref_lib():
         _lib.ftref_curand_uniforms.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         V, Z = C.c_void_p, C.c_size_t
         _lib.ftref_log_prob_from_logits.argtypes = [V, V, C.c_int, V, V, Z, Z, Z, Z, V, Z, V, C.c_int]
+        I = C.c_int
+        _lib.ftref_decoding_initialize.argtypes = [V, V, V, V, I, V, I, I, I, V]
+        _lib.ftref_gather_tree.argtypes = [V, V, I, V, V, I, I, I, V, V, V, I, V, V, I, I, V, V]
+        _lib.ftref_finalize.argtypes = [V, V, V, V, V, V, V, V, V, V, I, I, I, V]
+        _lib.ftref_insert_unfinished_path.argtypes = [V, V, V, V, V, V, V, V, V, V, V, I, C.c_float, V, V, I, I, V]
     return _lib
 
 
