@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(kDkThreads) gather_tree_kernel(GatherTree p)
                 else {
                     const int e            = (level - lo) * K + parent;
                     p.beams[at(tgt, beam)] = s_ids[e];
-                    parent                 = p.parent_ids == nullptr ? 0 : s_par[e] % K;
+                    const int v            = s_par[e];  // in [0, K) on a well-formed tree: skip the division
+                    parent                 = (unsigned)v < (unsigned)K ? v : v % K;
                 }
             }
             s_parent[beam] = parent;
