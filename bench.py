@@ -462,6 +462,72 @@ def run_reference(a, rank, world, local):
     }
 
 
+def run_log_probs(a, rank, world, local, reference=False):
+    """Context log-probs (invokeLogProbFromLogits): 512 positions x 32 sequences x vocab 50257 fp16, 1.65 GB of
+    logits per step per GPU (larger than L2, so no flush is needed); sequences shard over GPUs, no collective."""
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    L, B, V = 512, 32, 50257
+    steps, W = a.steps, a.warmup
+    if reference:
+        import ft_reference
+        if rank != 0:
+            return None
+        if not ft_reference.available():
+            return {"impl": "reference", "unavailable": "oracle/_ref/libft_decode_ref.so is not built on this box"}
+        fn = ft_reference.ref_lib().ftref_log_prob_from_logits
+    else:
+        from fastertransformer_b200 import lib
+        fn = lib.ftb200_log_prob_from_logits
+    g = torch.Generator(device=device)
+    g.manual_seed(40 + rank)
+    logits = torch.empty(L, B, V, dtype=torch.float16, device=device)
+    for t in range(0, L, 64):   # filled in slices: no fp32 copy of the whole tensor
+        logits[t:t + 64] = (torch.rand(64, B, V, generator=g, device=device) * 6 - 3).half()
+    ids = torch.randint(0, V, (L, B), generator=g, device=device, dtype=torch.int32)
+    lens = torch.full((B,), L, dtype=torch.int32, device=device)
+    ws = torch.zeros(L * B, dtype=torch.float32, device=device)
+    cum = torch.zeros(B, dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        rc = fn(cum.data_ptr(), logits.data_ptr(), 1, ids.data_ptr(), lens.data_ptr(), L, B, V, V, ws.data_ptr(),
+                ws.numel() * 4, stream, 0)
+        assert rc == 0, rc
+
+    sampler = ClockSampler(local)
+    for _ in range(W):
+        step()
+    barrier(world)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    clocks = sampler.stop()
+    ms = max_over_ranks(e0.elapsed_time(e1), world, device) / steps
+    peak, peak_kind = measured_peak()
+    alg = float(L - 1) * B * V * 2.0
+    tokens = float(L - 1) * B
+    line = {"metric": "context log-prob positions/sec (512 x 32 x vocab 50257 fp16)",
+            "value": world * tokens / (ms * 1e-3), "unit": "positions/s", "n_gpus": world, "steps": steps, "warmup": W,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp16 logits, fp32 soft-max statistics", "data": "synthetic",
+            "config": {"workload": "lp: log softmax(logits)[ids] summed per sequence, 512 positions x 32 sequences x "
+                                   "vocab 50257 fp16 per GPU", "l2": "1.65 GB of logits per step, larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": alg / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+                         "note": "algorithmic bytes = scored positions x vocab x 2 B; both kernels of the entry timed"},
+            "gpu_launches": 2 * steps, "clocks": clocks}
+    if reference:
+        line["impl"] = "reference"
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,9 +535,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="rows per GPU (default: the configuration's own)")
-    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"],
+    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5", "lp"],
                     help="c3 (default, the headline) | c1 / c2 the small sampling configurations | c4 beam search | "
-                         "c5 vocabulary-parallel")
+                         "c5 vocabulary-parallel | lp context log-probs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the fused kernel from an ncu capture (profiles/)")
@@ -489,6 +555,8 @@ def main():
         line = run_beam(a, rank, world, local, reference=a.impl == "reference")
     elif a.workload == "c5":
         line = run_vocab_parallel(a, rank, world, local)
+    elif a.workload == "lp":
+        line = run_log_probs(a, rank, world, local, reference=a.impl == "reference")
     elif a.impl == "reference":
         line = run_reference(a, rank, world, local)
     else:
