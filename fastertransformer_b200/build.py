@@ -95,6 +95,33 @@ def build_shim_driver():
     return out
 
 
+def build_th_op():
+    """Compile the torch custom class FasterTransformer.DynamicDecodeOp (th_op/DynamicDecodeOp.cc over the C++
+    decode layers) into lib/libth_ftb200.so, next to libftb200.so which it links."""
+    import torch
+    from torch.utils import cpp_extension
+    out = os.path.join(OUT, "libth_ftb200.so")
+    srcs = [os.path.join(HERE, "th_op", "DynamicDecodeOp.cc"), os.path.join(HERE, "shim", "DynamicDecodeLayer.cc")]
+    deps = srcs + [os.path.join(HERE, "shim", "DynamicDecodeLayer.h"), os.path.join(HERE, "shim", "ft_compat.h"), LIB]
+    if os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
+        return out
+    cuda_home = os.path.dirname(os.path.dirname(NVCC))
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-w",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)] + srcs
+    for inc in cpp_extension.include_paths() + [os.path.join(cuda_home, "include"), INC, os.path.join(HERE, "shim")]:
+        cmd += ["-I" + inc]
+    cmd += ["-L" + tlib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+            "-L" + OUT, "-lftb200", "-L" + os.path.join(cuda_home, "lib64"), "-lcudart",
+            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib, "-o", out]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("building the torch custom class failed")
+    return out
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
     print(build_shim_driver())
+    print(build_th_op())

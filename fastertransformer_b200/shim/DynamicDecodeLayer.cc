@@ -89,6 +89,17 @@ public:
 
     void setup(size_t batch_size, size_t beam_width, TensorMap* args);
     void forward(TensorMap* out, TensorMap* in);
+    void setStream(cudaStream_t stream)
+    {
+        stream_ = stream;
+        if (allocator_ != nullptr) {
+            allocator_->setStream(stream);
+        }
+    }
+    cudaStream_t getStream() const
+    {
+        return stream_;
+    }
     DecodeCore* cloneConfiguration() const
     {
         return new DecodeCore(mode_, dtype_, vocab_, vocab_padded_, stream_, allocator_, free_after_forward_);
@@ -611,6 +622,18 @@ void DynamicDecodeLayer<T>::setup(const size_t batch_size, const size_t beam_wid
 {
     core_->setup(batch_size, beam_width, runtime_args);
 }
+template<typename T>
+void DynamicDecodeLayer<T>::setStream(cudaStream_t stream)
+{
+    core_->setStream(stream);
+}
+
+template<typename T>
+cudaStream_t DynamicDecodeLayer<T>::getStream()
+{
+    return core_->getStream();
+}
+
 template<typename T>
 void DynamicDecodeLayer<T>::forward(TensorMap* output_tensors, TensorMap* input_tensors)
 {

@@ -50,6 +50,10 @@ public:
     void forward(std::unordered_map<std::string, Tensor>* output_tensors,
                  const std::unordered_map<std::string, Tensor>* input_tensors);
 
+    // BaseLayer's stream accessors (layers/BaseLayer.h:43-51): later calls run on the new stream.
+    void         setStream(cudaStream_t stream);
+    cudaStream_t getStream();
+
 private:
     std::unique_ptr<ftb200_detail::DecodeCore> core_;
 };

@@ -1,13 +1,37 @@
 """The cases of the reference's own test of its torch op (tests/unittests/th_op/test_th_decode_op.py: minimum
 length at sampling and at beam search, the id sequence under repetition / presence penalty), re-driven through
-fastertransformer_b200.th_decode_op.DynamicDecodeOp with the same positional argument lists."""
+the compiled torch custom class torch.classes.FasterTransformer.DynamicDecodeOp of this package
+(fastertransformer_b200/th_op, lib/libth_ftb200.so) and through its Python twin
+fastertransformer_b200.th_decode_op.DynamicDecodeOp, with the same positional argument lists."""
 import itertools
+import os
 
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
 VOCAB, END_ID = 1024, 0
+TH_LIB = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "fastertransformer_b200", "lib",
+                      "libth_ftb200.so")
+IMPL = "python"
+
+
+@pytest.fixture(params=["torch_class", "python"], autouse=True)
+def op_impl(request):
+    global IMPL
+    IMPL = request.param
+    yield
+    IMPL = "python"
+
+
+def make_op(dtype=torch.float):
+    if IMPL == "torch_class":
+        if not os.path.exists(TH_LIB):
+            pytest.fail("lib/libth_ftb200.so is not built: run python -m fastertransformer_b200.build")
+        torch.classes.load_library(TH_LIB)
+        return torch.classes.FasterTransformer.DynamicDecodeOp(VOCAB, VOCAB, 1, 1, dtype)
+    from fastertransformer_b200.th_decode_op import DynamicDecodeOp
+    return DynamicDecodeOp(VOCAB, VOCAB, 1, 1, dtype)
 
 
 def _vec(batch, value, dtype, cpu):
@@ -19,8 +43,7 @@ def _vec(batch, value, dtype, cpu):
 def run_decode(batch_size=4, beam_width=1, max_input_length=4, gen_length=3, top_k=None, top_p=None, temperature=None,
                repetition_penalty=None, presence_penalty=None, min_length=None, len_penalty=None,
                beam_search_diversity_rate=None, random_seed=None, logit_fn=None, use_random_input_tokens=True):
-    from fastertransformer_b200.th_decode_op import DynamicDecodeOp
-    op = DynamicDecodeOp(VOCAB, VOCAB, 1, 1, torch.float)
+    op = make_op()
     dev = torch.device("cuda", torch.cuda.current_device())
     ite, lbs, L = 0, batch_size, max_input_length + gen_length
     eos = _vec(batch_size, END_ID, torch.int, False)
@@ -114,3 +137,37 @@ def test_repetition_penalty_correctness(tc, method):
     out = run_decode(gen_length=gen, use_random_input_tokens=False, logit_fn=_descending_three, **tc, **method)
     got = out["output_token_ids"][:, tc["max_input_length"]:]
     assert bool((expect.to(got.device) == got).all())
+
+
+def test_compiled_class_and_python_twin_draw_the_same_ids():
+    global IMPL
+    if IMPL != "torch_class":
+        pytest.skip("runs once")
+    outs = []
+    for impl in ("torch_class", "python"):
+        IMPL = impl
+        outs.append(run_decode(batch_size=64, max_input_length=5, gen_length=12, top_k=20, top_p=0.7, temperature=0.8,
+                               repetition_penalty=1.3, random_seed=11))
+        outs.append(run_decode(batch_size=8, beam_width=4, max_input_length=5, gen_length=12, len_penalty=1.0,
+                               beam_search_diversity_rate=0.2))
+    IMPL = "torch_class"
+    for a, b in ((outs[0], outs[2]), (outs[1], outs[3])):
+        assert bool((a["output_token_ids"] == b["output_token_ids"]).all())
+        assert bool((a["output_sequence_lengths"] == b["output_sequence_lengths"]).all())
+
+
+def test_compiled_class_argument_checks():
+    if IMPL != "torch_class":
+        pytest.skip("the compiled class's own checks")
+    op = make_op()
+    with pytest.raises(RuntimeError):      # runtime arguments are host tensors (CHECK_OPTIONAL_CPU_INPUT)
+        op.setup(2, 1, torch.ones(2, dtype=torch.int, device="cuda"), None, None, None, None, None, None, None, None,
+                 None, None, None)
+    with pytest.raises(RuntimeError):      # tensor / pipeline parallel sizes other than 1
+        torch.classes.FasterTransformer.DynamicDecodeOp(VOCAB, VOCAB, 2, 1, torch.float)
+    with pytest.raises(RuntimeError):      # logits of another type than the op's
+        op.setup(2, 1, torch.ones(2, dtype=torch.int), None, None, None, None, None, None, None, None, None, None, None)
+        ids = torch.zeros(3, 2, 1, dtype=torch.int32, device="cuda")
+        op.forward(torch.zeros(2, 1, VOCAB, dtype=torch.half, device="cuda"), 1, 1, 0, 2,
+                   torch.zeros(2, dtype=torch.int32, device="cuda"), None, None, None, None, None, None, None, None, None,
+                   None, None, None, None, None, None, None, None, ids, None, None, None, None, None, None)
