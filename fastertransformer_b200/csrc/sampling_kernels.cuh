@@ -665,23 +665,103 @@ __device__ __noinline__ void hot_slotmax(const uint4* vp, int jn, u32* slots)
     hot_slotmax_body<DT>(vp, jn, slots);
 }
 
+// Slot maxima that a pass over every column at its raw value left behind, turned into maxima over the ordinary
+// columns: a slot whose maximum may be a special column's value before its penalty is read again (its ~vocab/2048
+// columns, two bytes each) with the special columns left out.  Returns false when more slots are affected than
+// the list holds; the caller then reads the row again.
+constexpr int kMaxDirtySlots = 256;
+template<int DT>
+__device__ __noinline__ bool clean_special_slots(const KParams& P, const Smem& S, const RowCtx& C, u32* slots)
+{
+    static_assert(DT != FTB200_F32, "16-bit logits only");
+    __shared__ u32 s_dirty[kMaxDirtySlots];
+    __shared__ u32 s_nd;
+    const Xf       X     = make_xf(P, S, C);
+    const int      tid   = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int      nfull = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / 8 : 0);
+    FTB_ASSUME_SHARED(slots);
+    if (tid == 0) {
+        s_nd = 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < P.hash_slots; i += kThreads) {
+        const u32 w = X.hash[i];
+        if (w == kHashEmpty) {
+            continue;
+        }
+        const int v = (int)(w >> 2), o = v - C.head;
+        if (o < 0 || (o >> 3) >= nfull) {
+            continue;
+        }
+        const int slot = (o & 7) * kThreads + ((o >> 3) & (kThreads - 1));
+        if (S.spre[i] >= temp_value<DT>(X, key16_inv(slots[slot] >> 16), 0)) {
+            const u32 at = atomicAdd(&s_nd, 1u);
+            if (at < (u32)kMaxDirtySlots) {
+                s_dirty[at] = (u32)slot;
+            }
+        }
+    }
+    __syncthreads();
+    const u32 nd = s_nd;
+    if (nd > (u32)kMaxDirtySlots) {
+        return false;
+    }
+    const unsigned short* row16 = (const unsigned short*)C.rowp;
+    for (u32 d = wid; d < nd; d += kWarps) {
+        const int slot = (int)s_dirty[d], e = slot / kThreads, ts = slot % kThreads;
+        u32       key = 0;
+#pragma unroll 1
+        for (int j = ts + kThreads * lane; j < nfull; j += kThreads * 32) {
+            const int v = C.head + j * 8 + e;
+            if (((S.flags[j >> 5] >> (j & 31)) & 1u) && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v)) {
+                continue;
+            }
+            const u32 k = key16((u32)__ldg(row16 + v));
+            key         = k > key ? k : key;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const u32 other = __shfl_xor_sync(0xffffffffu, key, o);
+            key             = other > key ? other : key;
+        }
+        if (lane == 0) {
+            slots[slot] = key << 16;  // a slot listed twice gets the same value twice
+        }
+    }
+    __syncthreads();
+    return true;
+}
+
+// With clean_slots (the slot maxima of the 16-byte-vector part of the row, already free of special columns) the
+// vector part is not read again.
 template<int DT>
 __device__ __noinline__ float stream_max(const KParams& P, const Smem& S, const RowCtx& C, bool include_flagged,
-                                         u32* raw_key_max = nullptr, u32* slots = nullptr)
+                                         u32* raw_key_max = nullptr, u32* slots = nullptr,
+                                         const u32* clean_slots = nullptr)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int EPV   = DT == FTB200_F32 ? 4 : 8;
     const int     tid   = threadIdx.x;
     const uint4*  vp    = vec_base<DT>(C);
     const bool    pk    = packed_ok<DT>(P, C);
-    const bool    fast  = (DT == FTB200_F32 ? (P.bias == nullptr && C.inv_t > 0.0f) : pk) && include_flagged;
+    const bool    fast  = (DT == FTB200_F32 ? (P.bias == nullptr && C.inv_t > 0.0f) : pk)
+                      && (include_flagged || (DT != FTB200_F32 && clean_slots != nullptr));
     const int     nfull = P.vocab >= P.vocab_padded ? C.nvec : (P.vocab - C.head > 0 ? (P.vocab - C.head) / EPV : 0);
     float         best  = -INFINITY;
     u32           kraw  = 0;
     const int     jfast = fast ? nfull : 0;
     if (jfast > 0) {
         // temperature is monotone for inv_t > 0: the largest raw value gives the largest final value
-        if (DT != FTB200_F32 && slots != nullptr) {
+        if (DT != FTB200_F32 && clean_slots != nullptr) {
+            u32 km = 0;
+            for (int i = 0; i < kSlotsPerThread; ++i) {
+                const u32 k = clean_slots[i * kThreads + tid] >> 16;
+                km          = k > km ? k : km;
+            }
+            kraw = km;
+            best = temp_value<DT>(X, key16_inv(km), 0);
+        }
+        else if (DT != FTB200_F32 && slots != nullptr) {
             // same pass, but the eight per-thread subset maxima are kept (ordered keys << 16)
             hot_slotmax<DT>(vp, jfast, slots);
             u32 km = 0;
@@ -2842,7 +2922,16 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
     trace_mark(O.trace, 15);
     __syncthreads();
     if (s_redo) {
-        tmax = stream_max<DT>(P, S, C, false);
+        // the largest column is a penalised or banned one: take the maximum over the others from the slot
+        // maxima where the pass left them, reading again only the slots a special column may top
+        bool from_slots = false;
+        if constexpr (DT != FTB200_F32) {
+            if (have_slots) {
+                from_slots = clean_special_slots<DT>(P, S, C, (u32*)S.hitq);
+            }
+        }
+        tmax = from_slots ? stream_max<DT>(P, S, C, false, nullptr, nullptr, (const u32*)S.hitq) :
+                            stream_max<DT>(P, S, C, false);
     }
     else {
         tmax = tall;
