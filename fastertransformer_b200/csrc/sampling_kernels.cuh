@@ -665,11 +665,13 @@ __device__ __noinline__ void hot_slotmax(const uint4* vp, int jn, u32* slots)
     hot_slotmax_body<DT>(vp, jn, slots);
 }
 
-// Slot maxima that a pass over every column at its raw value left behind, turned into maxima over the ordinary
-// columns: a slot whose maximum may be a special column's value before its penalty is read again (its ~vocab/2048
-// columns, two bytes each) with the special columns left out.  Returns false when more slots are affected than
-// the list holds; the caller then reads the row again.
-constexpr int kMaxDirtySlots = 256;
+// Slot maxima that a pass over every column at its raw value left behind, made safe for taking the maximum over
+// the ordinary columns: a slot whose maximum may be a special column's value before its penalty, and that lies
+// above the largest slot no special column can top, is read again (its ~vocab/2048 columns, two bytes each)
+// with the special columns left out.  The other such slots keep their value: they cannot hold the maximum.
+// Returns false when more slots are affected than the list holds; the caller then reads the row again.
+constexpr int kMaxDirtySlots = 64;
+static __device__ u64 block_max_u64(u64 v);
 template<int DT>
 __device__ __noinline__ bool clean_special_slots(const KParams& P, const Smem& S, const RowCtx& C, u32* slots)
 {
@@ -683,7 +685,7 @@ __device__ __noinline__ bool clean_special_slots(const KParams& P, const Smem& S
     if (tid == 0) {
         s_nd = 0;
     }
-    __syncthreads();
+    // bit 0 of a slot word (keys sit in the upper half) marks a slot that a special column may top
     for (int i = tid; i < P.hash_slots; i += kThreads) {
         const u32 w = X.hash[i];
         if (w == kHashEmpty) {
@@ -695,9 +697,26 @@ __device__ __noinline__ bool clean_special_slots(const KParams& P, const Smem& S
         }
         const int slot = (o & 7) * kThreads + ((o >> 3) & (kThreads - 1));
         if (S.spre[i] >= temp_value<DT>(X, key16_inv(slots[slot] >> 16), 0)) {
-            const u32 at = atomicAdd(&s_nd, 1u);
-            if (at < (u32)kMaxDirtySlots) {
-                s_dirty[at] = (u32)slot;
+            smem_or(&slots[slot], 1u);
+        }
+    }
+    __syncthreads();
+    u32 safe = 0;
+    for (int i = 0; i < kSlotsPerThread; ++i) {
+        const u32 k = slots[i * kThreads + tid];
+        safe        = (k & 1u) == 0 && k > safe ? k : safe;
+    }
+    safe = (u32)block_max_u64((u64)safe);
+    for (int i = 0; i < kSlotsPerThread; ++i) {
+        const int slot = i * kThreads + tid;
+        const u32 k    = slots[slot];
+        if (k & 1u) {
+            slots[slot] = k & ~1u;
+            if (k > safe) {
+                const u32 at = atomicAdd(&s_nd, 1u);
+                if (at < (u32)kMaxDirtySlots) {
+                    s_dirty[at] = (u32)slot;
+                }
             }
         }
     }
@@ -725,7 +744,7 @@ __device__ __noinline__ bool clean_special_slots(const KParams& P, const Smem& S
             key             = other > key ? other : key;
         }
         if (lane == 0) {
-            slots[slot] = key << 16;  // a slot listed twice gets the same value twice
+            slots[slot] = key << 16;
         }
     }
     __syncthreads();
@@ -2930,6 +2949,7 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
                 from_slots = clean_special_slots<DT>(P, S, C, (u32*)S.hitq);
             }
         }
+        trace_mark(O.trace, 16);
         tmax = from_slots ? stream_max<DT>(P, S, C, false, nullptr, nullptr, (const u32*)S.hitq) :
                             stream_max<DT>(P, S, C, false);
     }
