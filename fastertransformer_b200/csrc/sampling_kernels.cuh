@@ -58,7 +58,8 @@ __device__ __forceinline__ u64 global_timer_ns()
 //     0  row set-up done                                    0  row set-up done
 //     1  maximum pass and special-column fetch done         1  slot-maximum pass and special-column fetch done
 //    15  special columns compared with the maximum          2  cut chosen
-//     2  row maximum known                                  3  filtered pass done
+//    16  (largest column penalised) slot maxima cleaned      9  packed filter done (word 14: queued vectors)
+//     2  row maximum known                                  3  filtered pass done (word 18: candidates)
 //    12  per-thread patch lists built                       4  special columns visited
 //    13  ordered soft-max pass done (whole chunks)          5  sort and draw done
 //     3  soft-max pass done (row tail included)
@@ -455,7 +456,7 @@ constexpr int kWholeRow = 65536;
 template<int DT, class Thr, class Hit>
 __device__ __noinline__ void
 stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1, Thr&& thr, Hit&& hit, int span = kHotBatch,
-                float thr_hi = INFINITY)
+                float thr_hi = INFINITY, u64* dbg = nullptr)
 {
     const Xf X = make_xf(P, S, C);
     constexpr int   EPV   = DT == FTB200_F32 ? 4 : 8;
@@ -484,11 +485,13 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
     for (int jb = j0; jb < j1;) {
         const int   je    = j1 - jb < span ? j1 : jb + span;
         const float thr_y = thr();
+        const u32   thr2  = (fast && DT != FTB200_F32) ? raw_threshold_pair<DT>(P, C, thr_y) : 0u;
+        const bool  band  = DT != FTB200_F32 && thr_hi < INFINITY;
+        const u32   hi2   = (fast && band) ? raw_ceiling_pair<DT>(P, C, thr_hi) : 0u;
         if (fast) {
-            const u32 thr2 = DT == FTB200_F32 ? 0u : raw_threshold_pair<DT>(P, C, thr_y);
-            if (DT != FTB200_F32 && thr_hi < INFINITY) {
+            if (band) {
                 // a band of values: the hits of the packed filter are the columns between the two bounds
-                hot_filter<DT, true>(vp, jb, je, thr_y, thr2, inv, temp, hitq, nhit + par, raw_ceiling_pair<DT>(P, C, thr_hi));
+                hot_filter<DT, true>(vp, jb, je, thr_y, thr2, inv, temp, hitq, nhit + par, hi2);
             }
             else {
                 hot_filter<DT>(vp, jb, je, thr_y, thr2, inv, temp, hitq, nhit + par);
@@ -497,6 +500,12 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
         __syncthreads();
         // embedding bias or a non-positive temperature: every vector takes the exact path
         const int n = fast ? (int)nhit[par] : je - jb;
+        if (dbg != nullptr) {
+            trace_mark(dbg, 9);
+            if (threadIdx.x == 0) {
+                dbg[4 + 14] = (u64)n;
+            }
+        }
         if (fast && n > kHitCap) {
             // more hits than the queue holds: this round again, one load batch at a time
             __syncthreads();
@@ -510,29 +519,49 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
         if (tid == 0) {
             nhit[par ^ 1] = 0;
         }
+        // one column of a queued (or, without the filter, of every) vector: exact value, exact test
+        auto column = [&](int j, const uint4& r, int e, bool sp) {
+            const int v = head + j * EPV + e;
+            if (v < vocab) {
+                const u32   rb = raw_bits<DT>(r, e);
+                const float y  = temp_value<DT>(X, rb, v);
+                if (y >= thr_y) {
+                    // special columns are reported by visit_specials with their final value
+                    if (!(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
+                        if constexpr (std::is_invocable_v<Hit, int, float, u32>) {
+                            hit(v, y, rb);  // callers that bin by bit pattern
+                        }
+                        else {
+                            hit(v, y);
+                        }
+                    }
+                }
+            }
+        };
 #pragma unroll 1
         for (int i = tid; i < n; i += kThreads) {
             const int   j  = jb + (fast ? (int)hitq[i] : i);
             const bool  sp = (flags[j >> 5] >> (j & 31)) & 1u;
             const uint4 r  = ld_nc_v4(vp + j);
-            const int   vb = head + j * EPV;
-#pragma unroll 1
-            for (int e = 0; e < EPV; ++e) {
-                const int v = vb + e;
-                if (v < vocab) {
-                    float y = temp_value<DT>(X, raw_bits<DT>(r, e), v);
-                    if (y >= thr_y) {
-                        // special columns are reported by visit_specials with their final value
-                        if (!(sp && hash_lookup_raw(X.hash, X.hash_shift, X.hash_mask, v))) {
-                            if constexpr (std::is_invocable_v<Hit, int, float, u32>) {
-                                hit(v, y, raw_bits<DT>(r, e));  // callers that bin by bit pattern
-                            }
-                            else {
-                                hit(v, y);
-                            }
-                        }
+            u32         pm = (1u << EPV) - 1u;  // columns of the vector that can pass
+            if (DT != FTB200_F32 && fast) {
+                // the packed compare that queued the vector says which halves can pass
+                pm = 0;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const u32 word = pick_word(r, w);
+                    u32       m    = ge2_mask<DT>(word, thr2);
+                    if (band) {
+                        m &= le2_mask<DT>(word, hi2);
                     }
+                    pm |= ((m & 1u) | ((m >> 15) & 2u)) << (2 * w);
                 }
+            }
+#pragma unroll 1
+            while (pm != 0) {
+                const int e = __ffs(pm) - 1;
+                pm &= pm - 1;
+                column(j, r, e, sp);
             }
         }
         __syncthreads();
@@ -1776,11 +1805,14 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
             }
         }
     };
-    stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return thr_y; }, push, kWholeRow);
+    stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return thr_y; }, push, kWholeRow, INFINITY, O.trace);
     trace_mark(O.trace, 3);
     visit_specials<DT>(P, S, C, thr_y, push);
     __syncthreads();
     const int n = (int)s_n;
+    if (O.trace != nullptr && threadIdx.x == 0) {
+        O.trace[4 + 18] = (u64)n;
+    }
     if (s_ovf || n < k) {
         __syncthreads();
         return false;
