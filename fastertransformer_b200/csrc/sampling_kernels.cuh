@@ -1403,30 +1403,100 @@ static __device__ __noinline__ void topk_finish(const KParams& P, const Smem& S,
         }
     }
     __syncthreads();
+    // The sum and the walk are chains of dependent adds in the reference's order (one thread).  The walk stores
+    // every running value instead of testing it; the first one that ends the reference's loop is then found by
+    // all threads.  Operands are fetched eight at a time so that the chains do not wait for shared memory.
+    float* run = (float*)S.hist;  // [k_eff] running values; the bucket counts are not needed any more
+    FTB_ASSUME_SHARED(run);
+    __shared__ int s_walked;
     if (tid == 0) {
-        s_pick = -1;
+        s_pick   = k_eff > 0 ? k_eff - 1 : -1;
+        s_walked = 0;
         if (k_eff > 0) {
-            float sum = 0.0f;
-            for (int i = 0; i < k_eff; ++i) {
-                sum += S.val2[i];
-            }
-            float rand_num = u * top_p * sum;
-            int   pick     = k_eff - 1;
-            for (int i = 0; i < k_eff; ++i) {
-                rand_num = rand_num - S.val2[i];
-                if (rand_num <= 0.0f || i == k - 1) {
-                    pick = i;
-                    break;
+            const float* val = S.val2;
+            FTB_ASSUME_SHARED(val);
+            const int k8  = k_eff & ~7;
+            float     sum = 0.0f;
+            float     v[8], w[8];
+            if (k8 > 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = val[j];
                 }
             }
-            s_pick = pick;
-            s_e    = S.val2[pick];
-            s_sum  = sum;
-            s_lo   = pick;
-            s_hi   = pick + 1;
+            for (int i = 0; i < k8; i += 8) {
+                if (i + 8 < k8) {  // the next eight are on their way while these are added
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        w[j] = val[i + 8 + j];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    sum += v[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = w[j];
+                }
+            }
+            for (int i = k8; i < k_eff; ++i) {
+                sum += val[i];
+            }
+            float rand_num = u * top_p * sum;
+            int   walked   = 0;
+            if (k8 > 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = val[j];
+                }
+            }
+            // the terms are not negative, so the running value only falls: once a group of eight ends at or
+            // below zero the reference's loop has stopped inside it
+            for (int i = 0; i < k8 && !(rand_num <= 0.0f); i += 8) {
+                if (i + 8 < k8) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        w[j] = val[i + 8 + j];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    rand_num   = rand_num - v[j];
+                    run[i + j] = rand_num;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = w[j];
+                }
+                walked = i + 8;
+            }
+            if (walked == k8) {
+                for (int i = k8; i < k_eff && !(rand_num <= 0.0f); ++i) {
+                    rand_num = rand_num - val[i];
+                    run[i]   = rand_num;
+                    walked   = i + 1;
+                }
+            }
+            s_walked = walked;
+            s_sum    = sum;
         }
     }
     __syncthreads();
+    for (int i = tid, nw = s_walked; i < nw; i += kThreads) {
+        if (run[i] <= 0.0f || i == k - 1) {
+            atomicMin(&s_pick, i);
+            break;  // later entries of this thread are larger
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && s_pick >= 0) {
+        s_e  = S.val2[s_pick];
+        s_lo = s_pick;
+        s_hi = s_pick + 1;
+    }
+    __syncthreads();
+    trace_mark(O.trace, 21);
     const int pick = s_pick;
     if (pick < 0) {
         // no selectable token in the row: the reference reads out of bounds here; emit token 0
@@ -1446,6 +1516,7 @@ static __device__ __noinline__ void topk_finish(const KParams& P, const Smem& S,
         }
     }
     __syncthreads();
+    trace_mark(O.trace, 23);
     const int lo = s_lo, hi = s_hi;
     int       col;
     if (hi - lo == 1) {
@@ -1647,6 +1718,7 @@ static __device__ __noinline__ void topk_tail(const KParams& P, const Smem& S, c
 {
     const int tid = threadIdx.x;
     cand          = sort_candidates(S, cand, n);
+    trace_mark(O.trace, 10);
     if (P.vp_out != nullptr) {
         // Vocabulary-parallel local pass: hand over every column whose value reaches this shard's k-th
         // value, whole tie class included.  The global k-th value cannot be smaller than a shard's, so
