@@ -226,18 +226,38 @@ def run_ours(a, rank, world, local):
     host_pool = [torch.empty(B, w.vocab_padded, dtype=w.dtype).pin_memory() for _ in range(2)]
     for h, d in zip(host_pool, pool):
         h.copy_(d)
-    dev_logits = torch.empty_like(pool[0])
+    # two device buffers: the copy of the next step's logits (copy stream) runs under this step's kernel; every
+    # copy, every kernel and every read-back of the ids lies inside the timed region
+    dev_logits = [torch.empty_like(pool[0]) for _ in range(2)]
     ids_host = torch.empty(B, dtype=torch.int32).pin_memory()
+    copy_stream = torch.cuda.Stream(device=device)
+    main = torch.cuda.current_stream()
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def start_copy(i):
+        b = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[b])      # the kernel that read this buffer last has finished
+            dev_logits[b].copy_(host_pool[b], non_blocking=True)
+            copied[b].record(copy_stream)
+
     torch.cuda.synchronize()
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    for b in range(2):
+        consumed[b].record(main)
+    start_copy(0)
     for i in range(e2e_steps):
-        dev_logits.copy_(host_pool[i % 2], non_blocking=True)
+        if i + 1 < e2e_steps:
+            start_copy(i + 1)
+        main.wait_event(copied[i % 2])
         s = step_no[0]
-        one_step(dev_logits)
+        one_step(dev_logits[i % 2])
+        consumed[i % 2].record(main)
         ids_host.copy_(st["output_ids"][s], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        main.synchronize()
     e1.record()
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, device)
