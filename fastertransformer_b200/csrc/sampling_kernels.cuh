@@ -2451,15 +2451,17 @@ __device__ __noinline__ void hot_count_dense(const uint4* vp, int jn, const u32*
 
 constexpr int kMaxRuns  = 4096;  // runs held in shared memory
 constexpr int kMaxSpecs = 1024;  // special / edge columns above the cut
+constexpr int kMaxAbove = 256;   // ordinary columns above a class window that does not reach the row maximum
 
 template<int DT>
 __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, const RowCtx& C, const RowOut& O,
                                              float maxv, float denom, float rand_num, float cut0, u32 kmax16,
                                              bool want_lp, bool dense, u32 k_cut_given = 0xffffffffu)
 {
-    __shared__ u32   s_ns, s_fail, s_wsum[kWarps], s_ncls;
+    __shared__ u32   s_ns, s_fail, s_wsum[kWarps], s_ncls, s_nabove;
     __shared__ int   s_c1, s_sel, s_imin, s_imax;
     __shared__ float s_R;
+    __shared__ u64   s_above[kMaxAbove];  // columns above the class window: (~key(prob) << 32) | column
     const Xf         X   = make_xf(P, S, C);
     const int        tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const bool       complete = !(cut0 > -INFINITY);
@@ -2485,8 +2487,9 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         S.hist[i] = 0;
     }
     if (tid == 0) {
-        s_ns   = 0;
-        s_fail = 0;
+        s_ns     = 0;
+        s_fail   = 0;
+        s_nabove = 0;
     }
     __syncthreads();
     // The cut in the pattern domain: the smallest ordered key whose value reaches cut0.  Everything at or
@@ -2511,7 +2514,27 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         k_cut = lo;
     }
     if (kmax16 - k_cut >= (u32)kNB) {
-        { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 1; } return 0; }
+        // The patterns between the cut and the row maximum do not fit the window.  A peaked row has only a few
+        // columns up there: the window is anchored at the cut instead, and the columns above it are listed one
+        // by one (they join the runs like special columns do).  From here on kmax16 is the top of the window.
+        if (complete || k_cut_given != 0xffffffffu) {
+            { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 1; } return 0; }
+        }
+        kmax16 = k_cut + (u32)kNB - 1u;
+        const float y_above = temp_value<DT>(X, key16_inv(kmax16 + 1u), 0);
+        auto        above   = [&](int v, float y, u32 raw) {
+            if (key16(raw) > kmax16 && y > C.neg_max) {
+                const u32 pos = atomicAdd(&s_nabove, 1u);
+                if (pos < (u32)kMaxAbove) {
+                    s_above[pos] = ((u64)(~fkey(prob_of(y))) << 32) | (u32)v;
+                }
+            }
+        };
+        stream_filtered<DT>(P, S, C, 0, C.nvec, [&]() { return y_above; }, above, kWholeRow);
+        __syncthreads();
+        if (s_nabove > (u32)kMaxAbove) {
+            { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 1; } return 0; }
+        }
     }
     const u32   limit = kmax16 - k_cut + 1u;
     const float y_c   = (complete && k_cut_given == 0xffffffffu) ? -INFINITY : temp_value<DT>(X, key16_inv(k_cut), 0);
@@ -2579,6 +2602,22 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         });
     }
     __syncthreads();
+    {
+        const u32 na = s_nabove, base = s_ns;
+        if (base + na > (u32)kMaxSpecs) {
+            s_fail = 1;  // (every thread writes the same value)
+        }
+        else {
+            for (u32 i = tid; i < na; i += kThreads) {
+                spec[base + i] = s_above[i];
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && !s_fail) {
+            s_ns = base + na;
+        }
+        __syncthreads();
+    }
     trace_mark(O.trace, 5);
     if (s_fail) {
         { if (O.trace != nullptr && threadIdx.x == 0) { O.trace[4 + 25] = 3; } return 0; }
@@ -2897,8 +2936,18 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     // Special and edge columns of the class - all of them, also those below the cut: with probabilities
     // rounded to the logits type a class of equal probabilities can span several bit patterns and reach
     // below the counted range, and the rank of the crossing counts every column of the class.
+    // Those at or above the cut are in the list (with the ordinary columns above the window); the rest come
+    // from the table.
+    for (int j = tid; j < ns; j += kThreads) {
+        if ((u32)(spec[j] >> 32) == ~k_sel) {
+            const u32 pos = atomicAdd(&s_ncls, 1u);
+            if (pos < (u32)(2 * kMaxRuns)) {
+                cls[pos] = (u32)(spec[j] & 0xffffffffu);
+            }
+        }
+    }
     visit_specials<DT>(P, S, C, -INFINITY, [&](int v, float y) {
-        if (y > C.neg_max && fkey(prob_of(y)) == k_sel) {
+        if (y > C.neg_max && !(y >= y_c) && fkey(prob_of(y)) == k_sel) {
             const u32 pos = atomicAdd(&s_ncls, 1u);
             if (pos < (u32)(2 * kMaxRuns)) {
                 cls[pos] = (u32)v;
@@ -3229,16 +3278,51 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         // value-class path: first with the provisional cut, then with every pattern the class window holds
         const u32   k_bot = kraw >= (u32)(kNB - 1) ? kraw - (u32)(kNB - 1) : 0u;
         const float cut_b = k_bot == 0u ? -INFINITY : temp_value<DT>(make_xf(P, S, C), key16_inv(k_bot), 0);
-        float       cut_a = b_cut == 0 ? -INFINITY :
+        const float cut_p = b_cut == 0 ? -INFINITY :
                                          maxv - (float)(kNB - b_cut) / (float)kLinScale - 1e-3f * fabsf(maxv) - 1e-3f;
-        cut_a             = fmaxf(cut_a, cut_b);
+        const float cut_a = fmaxf(cut_p, cut_b);
         // columns above the provisional cut, from the 1-in-16 sample: a dense row skips the hit queue
-        u32 above = 0;
+        // ... and above the top of a class window anchored at the provisional cut (when that one ends below the
+        // row maximum)
+        bool anchored = false;
+        int  b_wtop   = kNB;
+        if (cut_p > -INFINITY && cut_p < cut_b) {
+            const Xf Xc = make_xf(P, S, C);
+            u32      lo = 0, hi = kraw;  // lowest pattern whose value reaches the cut
+            while (lo < hi) {
+                const u32 mid = (lo + hi) >> 1;
+                if (temp_value<DT>(Xc, key16_inv(mid), 0) >= cut_p) {
+                    hi = mid;
+                }
+                else {
+                    lo = mid + 1;
+                }
+            }
+            if (lo + (u32)kNB <= kraw) {
+                anchored = true;
+                b_wtop   = lin_bucket(temp_value<DT>(Xc, key16_inv(lo + (u32)kNB), 0), maxv);
+            }
+        }
+        u32 above = 0, above_w = 0;
         for (int i = tid; i < kNB; i += kThreads) {
-            above += i >= b_cut ? S.hist[i] * (i > kTopBucket ? 1u : 16u) : 0u;
+            const u32 c = S.hist[i] * (i > kTopBucket ? 1u : 16u);
+            above += i >= b_cut ? c : 0u;
+            above_w += i >= b_wtop ? c : 0u;
         }
         above            = block_sum_u32(above);
-        const bool dense = cut_a <= cut_b || above * 40u > (u32)P.vocab;
+        above_w          = block_sum_u32(above_w);
+        const bool many  = above * 40u > (u32)P.vocab;
+        const bool dense = cut_a <= cut_b || many;
+        if (anchored && above_w <= (u32)(kMaxAbove / 2)) {
+            // the nucleus reaches below the window of the maximum and the row is peaked: a window anchored at the
+            // cut, the few columns above it listed one by one
+            if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_p, kraw, want_lp, many)) {
+                return;
+            }
+            if (O.trace != nullptr && tid == 0) {
+                O.trace[4 + 26] = O.trace[4 + 25];  // why the anchored window gave up
+            }
+        }
         if (row_topp_classes<DT>(P, S, C, O, maxv, denom, rand_num, cut_a, kraw, want_lp, dense)) {
             return;
         }
