@@ -2773,10 +2773,31 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         }
         return lo;
     };
+    // run at the first position of every chunk (the pattern counts are not needed any more): a lane then looks
+    // for its own first run between two neighbouring entries, a handful of runs instead of all of them
+    int* run_at = (int*)S.hist;
+    FTB_ASSUME_SHARED(run_at);
+    for (int c = tid; c <= nch; c += kThreads) {
+        run_at[c] = c < nch ? run_of((u32)c * 256u) : M - 1;
+    }
+    __syncthreads();
     // the 8 consecutive values of this lane in chunk c
     auto load8 = [&](int c, float* x) {
         const u32 p0 = (u32)c * 256u + (u32)lane * 8u;
-        int       i  = p0 < N ? run_of(p0) : 0;
+        int       i  = 0;
+        if (p0 < N) {
+            int lo = run_at[c], hi = run_at[c + 1];
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (run_st[mid] <= p0) {
+                    lo = mid;
+                }
+                else {
+                    hi = mid - 1;
+                }
+            }
+            i = lo;
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const u32 p = p0 + (u32)e;
