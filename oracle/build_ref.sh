@@ -4,7 +4,7 @@
 # oracle/ref_harness.cu.  Nothing is copied out of the reference tree; only
 # object files and the shared library land in oracle/_ref/ (git-ignored).
 #
-# usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default /root/reference)
+# usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default: $FT_REFERENCE_ROOT, else the build host's checkout)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 REF="${1:-${FT_REFERENCE_ROOT:-/root/reference}}"

@@ -5,7 +5,7 @@ compiled or run): the 3x8 toy logits (probabilities 0.4/0.3/0.2/0.1 on four colu
 every TYPED_TEST(SamplingDecodeTest, ...), the runtime top-k / top-p arguments and the set of ids each
 (step, row) may produce.  Output: tests/golden/sampling_layer_kat.json.
 
-usage: python tests/golden/make_sampling_layer_kat.py [FT_ROOT]     (default /root/reference)
+usage: python tests/golden/make_sampling_layer_kat.py [FT_ROOT]     (default: the build host's checkout)
 """
 import json
 import os
