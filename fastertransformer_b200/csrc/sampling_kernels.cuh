@@ -3906,7 +3906,10 @@ __device__ __noinline__ void vp_merge_topp_row(const KParams& P, const Smem& S, 
     const bool       fin    = P.finished != nullptr ? P.finished[r] != 0 : false;
     const float      top_p  = P.topp_ps[r];
     __syncthreads();
+    __shared__ curandState_t s_before;  // the generator before this row's draw: an undecided row gets it back,
+                                        // so that repeating the row draws the same number
     if (tid == 0) {
+        s_before = P.topp_states[r];
         s_u   = draw_uniform(P.topp_states, r);  // every row of the top-p layer draws, finished or not
         s_n   = 0;
         s_bad = 0;
@@ -3980,7 +3983,8 @@ __device__ __noinline__ void vp_merge_topp_row(const KParams& P, const Smem& S, 
         if (s_bad || n == 0 || !(M > -INFINITY)) {
             if (tid == 0) {
                 atomicAdd(overflow, 1);
-                *id_out = -1;
+                *id_out            = -1;
+                P.topp_states[r] = s_before;
             }
             __syncthreads();
             return;
@@ -4065,7 +4069,8 @@ __device__ __noinline__ void vp_merge_topp_row(const KParams& P, const Smem& S, 
         if (sel == -2) {
             if (tid == 0) {
                 atomicAdd(overflow, 1);
-                *id_out = -1;
+                *id_out            = -1;
+                P.topp_states[r] = s_before;
             }
             __syncthreads();
             return;
@@ -4090,7 +4095,8 @@ __device__ __noinline__ void vp_merge_topp_row(const KParams& P, const Smem& S, 
                 // the class of the crossing may continue in columns that were not sent
                 if (tid == 0) {
                     atomicAdd(overflow, 1);
-                    *id_out = -1;
+                    *id_out            = -1;
+                    P.topp_states[r] = s_before;
                 }
                 __syncthreads();
                 return;
@@ -4140,6 +4146,7 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float                              s_u;
     __shared__ u32                                s_n;
+    __shared__ curandState_t                      s_before_k;  // generator of a top-k row before its draw
     Smem                                          S;
     S.cand  = (u64*)smem_raw;
     S.hist  = (u32*)(S.cand + kCap);
@@ -4171,8 +4178,9 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
             continue;
         }
         if (tid == 0) {
-            s_u = draw_uniform(P.topk_states, r);
-            s_n = 0;
+            s_before_k = P.topk_states[r];
+            s_u        = draw_uniform(P.topk_states, r);
+            s_n        = 0;
         }
         __syncthreads();
         bool bad = false;
@@ -4201,7 +4209,8 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
         if (bad) {
             if (tid == 0) {
                 atomicAdd(overflow, 1);
-                *O.id_out = -1;
+                *O.id_out        = -1;
+                P.topk_states[r] = s_before_k;  // repeating the row draws the same number
             }
             continue;
         }

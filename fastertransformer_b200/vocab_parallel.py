@@ -23,13 +23,20 @@ from .decode_layer import CURAND_STATE_BYTES, DynamicDecodeLayer, _DT
 
 
 class VocabParallelSampler(DynamicDecodeLayer):
-    def __init__(self, vocab_size, shard_size, n_shards, dtype, device, cap_extra=64, group=None, topp_candidates=448):
+    def __init__(self, vocab_size, shard_size, n_shards, dtype, device, cap_extra=64, group=None, topp_candidates=448,
+                 resolve_undecided=True):
         """`topp_candidates`: columns every shard sends for a top-p row (its largest ones, plus its soft-max
-        statistics).  A row whose nucleus needs more than the union holds comes back with id -1 and is counted
-        by overflow_count(); the caller repeats such rows with a larger value or on gathered logits."""
+        statistics).  A row whose nucleus needs more than the union holds comes back from the merge with id -1,
+        its generator untouched, and is counted by overflow_count().  With `resolve_undecided` such rows get a
+        second round in the same call: their shard rows are gathered (one more all-gather, of the undecided rows
+        only) and sampled by the unsharded kernel - the id the single-GPU path gives.  Without it the caller
+        repeats them."""
         super().__init__(vocab_size, shard_size * n_shards, dtype, device)
         self.shard_size, self.n_shards, self.cap_extra, self.group = shard_size, n_shards, cap_extra, group
         self.topp_candidates = int(topp_candidates)
+        self.resolve_undecided = bool(resolve_undecided)
+        self.resolved_rows = 0
+        self._seen_overflow = 0
         self._records = None
         self._gathered = None
         self._overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -109,12 +116,20 @@ class VocabParallelSampler(DynamicDecodeLayer):
         return self._records, self._gathered
 
     def forward_rank(self, outputs, inputs, shard_logits, rank):
-        """One rank of a tensor-parallel group: local pass, one all-gather, merge."""
+        """One rank of a tensor-parallel group: local pass, one all-gather, merge; then, if rows stayed
+        undecided, their logits are gathered and they are sampled unsharded (every rank gets the same rows: the
+        merge is the same computation everywhere)."""
         import torch.distributed as dist
         rec, gathered = self._buffers(shard_logits.shape[0])
         self.local_pass(outputs, inputs, shard_logits, rank, rec)
         dist.all_gather_into_tensor(gathered.view(-1), rec.view(-1), group=self.group)
         self.merge(outputs, inputs, gathered, shard_logits)
+        rows = self._undecided_rows(outputs, inputs)
+        if rows is not None:
+            mine = shard_logits.index_select(0, rows).contiguous()
+            parts = torch.empty((self.n_shards,) + tuple(mine.shape), dtype=mine.dtype, device=mine.device)
+            dist.all_gather_into_tensor(parts.view(-1), mine.view(-1), group=self.group)
+            self._resolve(outputs, inputs, rows, parts.permute(1, 0, 2).reshape(rows.numel(), -1).contiguous())
 
     def forward_shards(self, outputs, inputs, shards):
         """All shards on this device (no communication): the arithmetic of forward_rank on every rank."""
@@ -123,6 +138,44 @@ class VocabParallelSampler(DynamicDecodeLayer):
             self.local_pass(outputs, inputs, sh, i, rec)
             gathered[i].copy_(rec)
         self.merge(outputs, inputs, gathered, shards[0])
+        rows = self._undecided_rows(outputs, inputs)
+        if rows is not None:
+            self._resolve(outputs, inputs, rows, torch.cat([sh.index_select(0, rows) for sh in shards], dim=1).contiguous())
+
+    def _undecided_rows(self, outputs, inputs):
+        """Row indices (device tensor) the merge of this step left undecided, or None.  Reads the overflow
+        counter, which synchronises the stream - the price of the second round; switch it off with
+        resolve_undecided=False."""
+        if not self.resolve_undecided or not self._has_topp():
+            return None  # (top-k rows overflow only on tie classes wider than the record: reported, not repeated)
+        total = int(self._overflow.item())
+        new, self._seen_overflow = total - self._seen_overflow, total
+        if new == 0:
+            return None
+        ids = outputs["output_ids"][int(inputs["step"])].reshape(-1)
+        return (ids == -1).nonzero().reshape(-1)
+
+    def _resolve(self, outputs, inputs, rows, full_rows):
+        """Sample the given rows from their full-vocabulary logits [len(rows), vocab_padded] with the unsharded
+        kernel, one call per row (ite = row, local batch 1: every per-row array is entered at that row)."""
+        Vp = self.shard_size * self.n_shards
+        B = outputs["output_ids"].shape[-1]
+        for j, r in enumerate(rows.tolist()):
+            P = self._params(outputs, inputs, full_rows[j:j + 1], self.vocab_size, Vp)
+            P.batch_size, P.local_batch_size, P.ite = B, 1, r
+            for name, width in (("end_ids", 4), ("input_lengths", 4), ("temperature", 4), ("repetition_penalty", 4),
+                                ("min_lengths", 4), ("topk_states", CURAND_STATE_BYTES), ("topk_ks", 4), ("topk_ps", 4),
+                                ("topk_skip", 1), ("topp_states", CURAND_STATE_BYTES), ("topp_ps", 4), ("topp_skip", 1),
+                                ("topp_initial_ps", 4), ("topp_decay", 4), ("topp_min", 4), ("topp_reset_ids", 4),
+                                ("sequence_length", 4), ("finished", 1)):
+                base = getattr(P, name)
+                if base:
+                    setattr(P, name, base + r * width)
+            if P.bad_words and not P.bad_words_shared:
+                P.bad_words = P.bad_words + r * 2 * P.bad_words_len * 4
+            check(lib.ftb200_decode_step_sampling(C.byref(P)))
+            self.launches += 1
+            self.resolved_rows += 1
 
     def overflow_count(self):
         return int(self._overflow.item())

@@ -312,8 +312,11 @@ int ftb200_beam_search_step(const ftb200_beam_params* p);
  * shard and token ids (history, bad words, end id) stay global; `vocab_offset` is the shard's first
  * column.  No log-probs.  A row that cannot be decided from the records - more than `cap` columns in
  * play on some shard, a top-p nucleus larger than the union of what the shards sent - is reported
- * through *overflow_count (device int, incremented) and gets id -1: the caller repeats it with a
- * larger cap or on gathered logits.
+ * through *overflow_count (device int, incremented) and gets id -1; its curand state, finished flag
+ * and sequence length are left as they were, so the caller can repeat it - with a larger cap, or by
+ * gathering that row's logits and calling ftb200_decode_step_sampling with ite = row,
+ * local_batch_size = 1 (what fastertransformer_b200.VocabParallelSampler does) - and get the draw
+ * the single-GPU path makes.
  * ------------------------------------------------------------------------------------------ */
 int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int vocab_offset, int cap, uint64_t* records);
 int ftb200_vocab_parallel_merge(const ftb200_sampling_params* p, const uint64_t* gathered, int n_ranks, int cap,

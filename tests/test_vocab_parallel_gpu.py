@@ -49,12 +49,15 @@ def test_shards_match_full_row(n_shards, shard, k, coarse, cuda_device):
             assert torch.equal(s_full[key], s_vp[key]), (s, key)
 
 
+@pytest.mark.parametrize("resolve", [True, False], ids=["second_round", "report_only"])
 @pytest.mark.parametrize("dtype,n_shards,sigma,max_undecided", [(torch.bfloat16, 4, 4.0, 0.2), (torch.float16, 2, 5.0, 0.2),
                                                                 (torch.float32, 8, 6.0, 0.2), (torch.bfloat16, 4, 1.2, 1.0)])
-def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, cuda_device):
+def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, resolve, cuda_device):
     """Mixed top-k / top-p rows over a sharded vocabulary against the unsharded kernel.  Top-k rows must be
     identical.  Top-p rows combine per-shard soft-max statistics, so their denominator is summed in another
-    order: ids are compared, and the few rows the exchange cannot decide (reported, id -1) are excluded."""
+    order: ids are compared.  The rows the exchange cannot decide either get a second round on their gathered
+    logits (then they are the unsharded kernel's ids, and no -1 is left) or are reported with id -1 and an
+    untouched generator."""
     from fastertransformer_b200 import DynamicDecodeLayer
     from fastertransformer_b200.vocab_parallel import VocabParallelSampler
     B, shard, mil, steps = 96, 4096, 6, 4
@@ -74,7 +77,7 @@ def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, cuda_d
 
     full = DynamicDecodeLayer(V, V, dtype, cuda_device)
     full.setup(B, 1, args)
-    vp = VocabParallelSampler(V, shard, n_shards, dtype, cuda_device)
+    vp = VocabParallelSampler(V, shard, n_shards, dtype, cuda_device, resolve_undecided=resolve)
     vp.setup(B, 1, args)
     st_a, st_b = state(), state()
     end = torch.full((B,), V - 1, dtype=torch.int32, device=cuda_device)
@@ -85,6 +88,7 @@ def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, cuda_d
         g.manual_seed(900 + s)
         x = (torch.randn(B, V, generator=g, device=cuda_device) * sigma).to(dtype)
         inp = {"step": mil + s, "max_input_length": mil, "end_id": end, "ite": 0, "local_batch_size": B}
+        before = vp.topp.curand.clone()
         full.forward(st_a, dict(inp, logits=x))
         vp.forward_shards(st_b, inp, [x[:, i * shard:(i + 1) * shard].contiguous() for i in range(n_shards)])
         a = st_a["output_ids"][mil + s].cpu().numpy()
@@ -92,6 +96,15 @@ def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, cuda_d
         assert np.array_equal(a[~is_topp], b[~is_topp]), "top-k rows must not depend on the sharding"
         und = b == -1
         assert not und[~is_topp].any()
+        if resolve:
+            assert not und.any()
+            # every row drew exactly once: the generators march in step with the unsharded layer's
+            assert torch.equal(vp.topp.curand, full.topp.curand)
+        else:
+            # an undecided row keeps the generator it had, so that its repetition draws the same number
+            rows = torch.from_numpy(np.nonzero(und)[0]).to(cuda_device)
+            assert torch.equal(vp.topp.curand.view(B, -1)[rows], before.view(B, -1)[rows])
+            vp.topp.curand.copy_(full.topp.curand)
         undecided += int(und.sum())
         ok = is_topp & ~und
         same_topp += int((a[ok] == b[ok]).sum())
@@ -100,12 +113,18 @@ def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, cuda_d
         st_b["output_ids"][mil + s].copy_(st_a["output_ids"][mil + s])
         st_b["finished"].copy_(st_a["finished"])
         st_b["sequence_length"].copy_(st_a["sequence_length"])
-    print("top-p rows: %d of %d ids equal to the unsharded kernel, %d undecided" % (same_topp, total_topp, undecided))
-    assert vp.overflow_count() == undecided
-    # (flat logits: the nucleus outgrows what the shards send - those rows have to come back undecided, not wrong)
-    assert undecided <= max_undecided * is_topp.sum() * steps
-    if max_undecided < 1.0:
-        assert total_topp > 0
+    print("top-p rows: %d of %d ids equal to the unsharded kernel, %d undecided, %d given a second round"
+          % (same_topp, total_topp, undecided, vp.resolved_rows))
+    if resolve:
+        assert undecided == 0 and vp.overflow_count() == vp.resolved_rows
+        if max_undecided >= 1.0:
+            assert vp.resolved_rows > 0
     else:
-        assert undecided > 0
+        assert vp.overflow_count() == undecided and vp.resolved_rows == 0
+        # (flat logits: the nucleus outgrows what the shards send - those rows have to come back undecided, not wrong)
+        assert undecided <= max_undecided * is_topp.sum() * steps
+        if max_undecided < 1.0:
+            assert total_topp > 0
+        else:
+            assert undecided > 0
     assert same_topp >= 0.97 * total_topp, (same_topp, total_topp)
