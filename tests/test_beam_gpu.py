@@ -103,6 +103,12 @@ def test_random_beam_configurations_against_reference(seed, cuda_device):
     V = int(rng.choice([257, 1031, 4096, 32000]))
     mil, steps = int(rng.integers(2, 6)), int(rng.integers(2, 6))
     L = mil + steps + 1
+    if 32 % K != 0:
+        # The reference's update_kernel adds 1 to sequence_length[index] and reads its parent's entry without a
+        # barrier in between (layers/beam_search_layers/OnlineBeamSearchLayer.cu:40-46): the outcome is defined
+        # only while the beams of an entry share a warp.  Here everything stays inside one warp; the library
+        # gives the lockstep outcome for every shape.
+        B = min(B, 32 // K)
     args = {}
     if seed % 3 == 0:
         args["len_penalty"] = np.asarray([float(rng.choice([0.5, 1.0, 2.0]))], np.float32)

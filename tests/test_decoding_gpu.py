@@ -174,3 +174,22 @@ def test_decoding_initialize_against_reference(dtype, with_word_ids):
     dc.same(ours, dc.run_initialize("ref", 37, 5, 123, dtype, with_word_ids))
     dc.same(ours, dc.run_initialize("oracle", 37, 5, 123, dtype, with_word_ids))
     check_gold(dc.run_initialize("ours", 3, 4, 17, dtype), GOLDEN["initialize"][str(dtype)])
+
+
+def test_argument_checks():
+    import ctypes as C
+    import torch
+    from fastertransformer_b200 import GatherTreeParams, lib
+    z = torch.zeros(16, dtype=torch.int32, device="cuda")
+    P = GatherTreeParams(beams=z.data_ptr(), max_sequence_lengths=z.data_ptr(), max_time=1, batch_size=1,
+                         beam_width=2000, step_ids=z.data_ptr(), parent_ids=z.data_ptr(), end_tokens=z.data_ptr(),
+                         max_input_length=1)
+    assert lib.ftb200_gather_tree(C.byref(P)) == 5          # more beams than the kernel serves
+    P.beam_width, P.step_ids = 2, None
+    assert lib.ftb200_gather_tree(C.byref(P)) == 1
+    assert lib.ftb200_gather_tree(None) == 1
+    assert lib.ftb200_decoding_initialize(None, z.data_ptr(), None, z.data_ptr(), 0, None, 1, 1, 1, None) == 1
+    assert lib.ftb200_decoding_initialize(z.data_ptr(), z.data_ptr(), z.data_ptr(), z.data_ptr(), 0, None, 1, 1, 1,
+                                          None) == 1      # word_ids without sentence_ids
+    assert lib.ftb200_insert_unfinished_path(None, z.data_ptr(), z.data_ptr(), z.data_ptr(), None, 4, 0.0,
+                                             z.data_ptr(), z.data_ptr(), 1, 1, None) == 1

@@ -140,3 +140,12 @@ def test_argument_checks():
     assert f(c.data_ptr(), x.data_ptr(), 0, i.data_ptr(), n.data_ptr(), 2, 2, 9, 8, ws.data_ptr(), 16, None, 0) == 1
     assert f(c.data_ptr(), x.data_ptr(), 9, i.data_ptr(), n.data_ptr(), 2, 2, 8, 8, ws.data_ptr(), 16, None, 0) == 1
     assert f(c.data_ptr(), None, 0, i.data_ptr(), n.data_ptr(), 2, 2, 8, 8, ws.data_ptr(), 16, None, 0) == 1
+
+
+def test_single_position_sequences_score_nothing():
+    from fastertransformer_b200 import log_prob_from_logits
+    x = torch.randn(1, 5, 64, device="cuda")
+    ids = torch.zeros(1, 5, dtype=torch.int32, device="cuda")
+    n = torch.ones(5, dtype=torch.int32, device="cuda")
+    cum = log_prob_from_logits(x, ids, n)
+    assert cum.shape == (5,) and bool((cum == 0).all())
