@@ -1593,10 +1593,13 @@ __device__ __noinline__ void row_argmax(const KParams& P, const Smem& S, const R
         const u64 b = *(volatile u64*)&s_best;
         return b == 0 ? -INFINITY : fkey_inv((u32)(b >> 32));
     };
-    // one vector per thread seeds the maximum; after that a hit is a rare event
-    const int jseed = C.nvec < kThreads ? C.nvec : kThreads;
+    // one vector per thread seeds the maximum, one load batch sharpens it; the rest of the row is then filtered
+    // in one round against that bound (a column above the maximum of the first 16 k is a rare event)
+    const int jseed  = C.nvec < kThreads ? C.nvec : kThreads;
+    const int jbatch = C.nvec < kHotBatch ? C.nvec : kHotBatch;
     stream_filtered<DT>(P, S, C, 0, jseed, running, consider);
-    stream_filtered<DT>(P, S, C, jseed, C.nvec, running, consider);
+    stream_filtered<DT>(P, S, C, jseed, jbatch, running, consider);
+    stream_filtered<DT>(P, S, C, jbatch, C.nvec, running, consider, kWholeRow);
     fetch_specials<DT>(P, S, C);
     visit_specials<DT>(P, S, C, running(), consider);
     __syncthreads();
