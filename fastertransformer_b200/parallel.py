@@ -56,3 +56,16 @@ def merge_records(records, vocab):
         bits = np.where(keys & 0x80000000, keys & 0x7FFFFFFF, ~keys).astype(np.uint32)
         row[cols] = bits.view(np.float32)
     return row
+
+
+def gather_rows(shard_logits, rows, n_shards, group=None):
+    """Second round of the vocabulary-parallel path: the full-vocabulary logits of the rows the merge left
+    undecided.  Every rank passes its own `[batch, shard]` tensor and the same `rows` (the merge is the same
+    computation everywhere); one all-gather of `[len(rows), shard]` per rank, then the shards of a row are put
+    side by side.  Returns `[len(rows), n_shards * shard]`.  Works on any backend (the CPU tests run it on gloo)."""
+    import torch
+    import torch.distributed as dist
+    mine = shard_logits.index_select(0, rows).contiguous()
+    parts = [torch.empty_like(mine) for _ in range(n_shards)]
+    dist.all_gather(parts, mine, group=group)
+    return torch.cat(parts, dim=1).contiguous()

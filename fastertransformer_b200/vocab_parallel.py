@@ -20,6 +20,7 @@ import torch
 
 from ._lib import SamplingParams, check, lib
 from .decode_layer import CURAND_STATE_BYTES, DynamicDecodeLayer, _DT
+from .parallel import gather_rows
 
 
 class VocabParallelSampler(DynamicDecodeLayer):
@@ -126,10 +127,7 @@ class VocabParallelSampler(DynamicDecodeLayer):
         self.merge(outputs, inputs, gathered, shard_logits)
         rows = self._undecided_rows(outputs, inputs)
         if rows is not None:
-            mine = shard_logits.index_select(0, rows).contiguous()
-            parts = torch.empty((self.n_shards,) + tuple(mine.shape), dtype=mine.dtype, device=mine.device)
-            dist.all_gather_into_tensor(parts.view(-1), mine.view(-1), group=self.group)
-            self._resolve(outputs, inputs, rows, parts.permute(1, 0, 2).reshape(rows.numel(), -1).contiguous())
+            self._resolve(outputs, inputs, rows, gather_rows(shard_logits, rows, self.n_shards, self.group))
 
     def forward_shards(self, outputs, inputs, shards):
         """All shards on this device (no communication): the arithmetic of forward_rank on every rank."""

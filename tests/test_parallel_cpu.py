@@ -12,7 +12,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from fastertransformer_b200.parallel import merge_records, pack_record, shard_rows
+from fastertransformer_b200.parallel import gather_rows, merge_records, pack_record, shard_rows
 from ft_oracle import OracleDynamicDecodeLayer
 
 B, V, K, MIL = 6, 512, 7, 3
@@ -65,6 +65,10 @@ def _worker(rank, world, port, q):
     dist.all_gather(gathered, torch.from_numpy(rec.view(np.int64)))
     merged = np.stack([merge_records([g.numpy().view(np.uint64)[b] for g in gathered], V) for b in range(B)])
     vp_ids = _decode(merged, prompt, u, list(range(B)))
+    # (3) second round: full rows of the rows a merge would leave undecided (same list on every rank)
+    rows = torch.tensor([1, B - 1, 4])
+    full = gather_rows(torch.from_numpy(np.ascontiguousarray(logits[:, rank * shard:(rank + 1) * shard])), rows, world)
+    assert np.array_equal(full.numpy(), logits[rows.numpy()]), "gathered rows are not the full rows"
     q.put((rank, batch_ids, vp_ids))
     dist.barrier()
     dist.destroy_process_group()
