@@ -2634,6 +2634,10 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
     // probabilities: patterns first - the order inside a class of equal values changes no partial sum).
     constexpr int PER = kNB / kThreads;
     int           nA;
+    for (int i = tid; i < kMaxRuns; i += kThreads) {
+        run_st[i] = 0u;  // a position no pattern takes keeps length 0 and goes to a special column
+    }
+    __syncthreads();
     {
         u32 cnt[PER], mine = 0;
         for (int i = 0; i < PER; ++i) {
@@ -2686,21 +2690,43 @@ __device__ __noinline__ int row_topp_classes(const KParams& P, const Smem& S, co
         }
     }
     __syncthreads();
-    for (int j = tid; j < ns; j += kThreads) {
-        const u32 kp = (u32)(spec[j] >> 32);
-        int       lo = 0, hi = kNB;  // first pattern with a probability below this one
-        while (lo < hi) {
-            const int mid = (lo + hi) >> 1;
-            if ((u32)mid <= kmax16 && ~fkey(prob_of_bin(mid)) <= kp) {
-                lo = mid + 1;
-            }
-            else {
-                hi = mid;
+    // Both lists keep their order in the merged sequence, and a pattern sits at (its rank among the patterns)
+    // + (specials before it): the specials therefore fill the positions the patterns left free, in order.
+    {
+        constexpr int RPT  = kMaxRuns / kThreads;
+        const int     Mtot = nA + ns;
+        u32           freem = 0, mine = 0;
+        for (int i = 0; i < RPT; ++i) {
+            const int r = tid * RPT + i;
+            if (r < Mtot && run_st[r] == 0u) {
+                freem |= 1u << i;
+                ++mine;
             }
         }
-        const int nb     = lo < kNB ? (int)rank[lo] : nA;  // non-empty patterns with a probability >= this one
-        run_pr[j + nb]   = __float_as_uint(fkey_inv(~kp));
-        run_st[j + nb]   = 1u;
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        __syncthreads();
+        if (lane == 31) {
+            s_wsum[wid] = incl;
+        }
+        __syncthreads();
+        u32 j = incl - mine;
+        for (int i = 0; i < wid; ++i) {
+            j += s_wsum[i];
+        }
+        for (int i = 0; i < RPT; ++i) {
+            if ((freem >> i) & 1u) {
+                const int r = tid * RPT + i;
+                run_pr[r]   = __float_as_uint(fkey_inv(~(u32)(spec[j] >> 32)));
+                run_st[r]   = 1u;
+                ++j;
+            }
+        }
     }
     __syncthreads();
     const int M = nA + ns;
@@ -3335,7 +3361,8 @@ __device__ __noinline__ void row_softmax(const KParams& P, const Smem& S, const 
         }
         above            = block_sum_u32(above);
         above_w          = block_sum_u32(above_w);
-        const bool many  = above * 40u > (u32)P.vocab;
+        // (the pass over bit patterns costs about as much as queueing 10 k columns one by one)
+        const bool many  = above * 16u > (u32)P.vocab;
         const bool dense = cut_a <= cut_b || many;
         if (anchored && above_w <= (u32)(kMaxAbove / 2)) {
             // the nucleus reaches below the window of the maximum and the row is peaked: a window anchored at the
