@@ -538,11 +538,22 @@ stream_filtered(const KParams& P, const Smem& S, const RowCtx& C, int j0, int j1
                 }
             }
         };
+        // the next queued vector is on its way while this one is looked at
+        int   j_next = 0;
+        uint4 r_next = make_uint4(0u, 0u, 0u, 0u);
+        if (tid < n) {
+            j_next = jb + (fast ? (int)hitq[tid] : tid);
+            r_next = ld_nc_v4(vp + j_next);
+        }
 #pragma unroll 1
         for (int i = tid; i < n; i += kThreads) {
-            const int   j  = jb + (fast ? (int)hitq[i] : i);
+            const int   j  = j_next;
+            const uint4 r  = r_next;
+            if (i + kThreads < n) {
+                j_next = jb + (fast ? (int)hitq[i + kThreads] : i + kThreads);
+                r_next = ld_nc_v4(vp + j_next);
+            }
             const bool  sp = (flags[j >> 5] >> (j & 31)) & 1u;
-            const uint4 r  = ld_nc_v4(vp + j);
             u32         pm = (1u << EPV) - 1u;  // columns of the vector that can pass
             if (DT != FTB200_F32 && fast) {
                 // the packed compare that queued the vector says which halves can pass
