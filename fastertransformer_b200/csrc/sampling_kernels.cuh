@@ -1840,20 +1840,49 @@ __device__ __noinline__ bool row_topk2(const KParams& P, const Smem& S, const Ro
             }
         }
     }
-    for (int i = tid; i < kNB; i += kThreads) {
-        hist[i] = 0;
-    }
-    __syncthreads();
-    for (int i = 0; i < kSlotsPerThread; ++i) {
-        const u32 key = slots[i * kThreads + tid];
-        if ((key >> 20) == (u32)b1) {
-            smem_add(&hist[(key >> 8) & 0xfffu], 1u);
+    u32 key;
+    if (DT != FTB200_F32) {
+        // 16-bit keys have four bits left below the first level: sixteen counters, searched by every thread
+        __shared__ u32 s_sub[16];
+        if (tid < 16) {
+            s_sub[tid] = 0;
         }
+        __syncthreads();
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            const u32 kk = slots[i * kThreads + tid];
+            if ((kk >> 20) == (u32)b1) {
+                smem_add(&s_sub[(kk >> 16) & 0xfu], 1u);
+            }
+        }
+        __syncthreads();
+        const u32 need = (u32)K - above;
+        u32       acc  = 0;
+        int       b2   = 0;
+        for (int b = 15; b >= 0; --b) {
+            acc += s_sub[b];
+            if (acc >= need) {
+                b2 = b;
+                break;
+            }
+        }
+        key = ((u32)b1 << 20) | ((u32)b2 << 16);
     }
-    __syncthreads();
-    u32       above2 = 0;
-    const int b2     = find_count_from_top(hist, (u32)K - above, &above2);
-    const u32 key    = ((u32)b1 << 20) | ((u32)(b2 < 0 ? 0 : b2) << 8);
+    else {
+        for (int i = tid; i < kNB; i += kThreads) {
+            hist[i] = 0;
+        }
+        __syncthreads();
+        for (int i = 0; i < kSlotsPerThread; ++i) {
+            const u32 kk = slots[i * kThreads + tid];
+            if ((kk >> 20) == (u32)b1) {
+                smem_add(&hist[(kk >> 8) & 0xfffu], 1u);
+            }
+        }
+        __syncthreads();
+        u32       above2 = 0;
+        const int b2     = find_count_from_top(hist, (u32)K - above, &above2);
+        key              = ((u32)b1 << 20) | ((u32)(b2 < 0 ? 0 : b2) << 8);
+    }
     if (key == 0u) {
         return false;
     }
