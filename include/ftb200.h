@@ -240,6 +240,10 @@ int    ftb200_decode_step_sampling_static(const ftb200_sampling_params* p);
  * Temperature, penalty, min_length, diversity and length penalty are scalars per call, as in the
  * reference (DynamicDecodeLayer.cc:286-386 loops over sub-batches when they differ per row).
  * The logits are read, never written.
+ * sequence_length follows the parent beam as the reference's update_kernel does when the beams of a
+ * batch entry run in lockstep (every length incremented, then gathered); the reference itself has no
+ * barrier between the two (OnlineBeamSearchLayer.cu:40-46) and leaves timing-dependent lengths when
+ * the beams of an entry span two warps (beam widths that do not divide 32).
  * ------------------------------------------------------------------------------------------ */
 
 /* Mirrors BeamHypotheses, kernels/beam_search_topk_kernels.h:31-58 (device pointers; num_beams == null
