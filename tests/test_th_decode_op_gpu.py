@@ -42,8 +42,9 @@ def _vec(batch, value, dtype, cpu):
 
 def run_decode(batch_size=4, beam_width=1, max_input_length=4, gen_length=3, top_k=None, top_p=None, temperature=None,
                repetition_penalty=None, presence_penalty=None, min_length=None, len_penalty=None,
-               beam_search_diversity_rate=None, random_seed=None, logit_fn=None, use_random_input_tokens=True):
-    op = make_op()
+               beam_search_diversity_rate=None, random_seed=None, logit_fn=None, use_random_input_tokens=True,
+               dtype=torch.float):
+    op = make_op(dtype)
     dev = torch.device("cuda", torch.cuda.current_device())
     ite, lbs, L = 0, batch_size, max_input_length + gen_length
     eos = _vec(batch_size, END_ID, torch.int, False)
@@ -84,7 +85,7 @@ def run_decode(batch_size=4, beam_width=1, max_input_length=4, gen_length=3, top
             s = (step - max_input_length) % 2
             src, tgt = cache[s], cache[1 - s]
         logits = (torch.randn(batch_size, beam_width, VOCAB, device=dev, generator=g) if logit_fn is None
-                  else logit_fn(batch_size, beam_width, dev, g))
+                  else logit_fn(batch_size, beam_width, dev, g)).to(dtype)
         stop = op.forward(logits, step, max_input_length, ite, lbs, eos, a["top_ks"], a["top_ps"], a["temps"], a["reps"],
                           a["pres"], a["mins"], a["lens"], a["divs"], None, None, None, None, in_len, None, None, None, src,
                           out_ids.view(-1, batch_size, beam_width), finished, seq_len, cum, None, parent_ids, tgt)
@@ -171,3 +172,18 @@ def test_compiled_class_argument_checks():
         op.forward(torch.zeros(2, 1, VOCAB, dtype=torch.half, device="cuda"), 1, 1, 0, 2,
                    torch.zeros(2, dtype=torch.int32, device="cuda"), None, None, None, None, None, None, None, None, None,
                    None, None, None, None, None, None, None, None, ids, None, None, None, None, None, None)
+
+
+@pytest.mark.parametrize("dtype", [torch.half, torch.bfloat16], ids=["half", "bfloat16"])
+def test_compiled_class_16_bit_logits(dtype):
+    global IMPL
+    if IMPL != "torch_class":
+        pytest.skip("runs once")
+    outs = []
+    for impl in ("torch_class", "python"):
+        IMPL = impl
+        outs.append(run_decode(batch_size=32, max_input_length=5, gen_length=10, top_k=0, top_p=0.8, temperature=0.9,
+                               presence_penalty=0.3, random_seed=5, dtype=dtype))
+    IMPL = "torch_class"
+    assert bool((outs[0]["output_token_ids"] == outs[1]["output_token_ids"]).all())
+    assert bool((outs[0]["output_sequence_lengths"] == outs[1]["output_sequence_lengths"]).all())
