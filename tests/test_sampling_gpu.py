@@ -313,3 +313,30 @@ def test_random_large_vocabularies_against_reference(seed, cuda_device):
     ref = run_cuda_like(ref_layer, w, cuda_device, want_log_probs=log_probs, cast=ref_dt, with_criteria=False)
     mine = run_cuda_like(_layer(w, cuda_device), w, cuda_device, want_log_probs=log_probs)
     _compare(mine, ref, w.name)
+
+
+@pytest.mark.parametrize("name,kw", [("c3", dict(batch=48, steps=3)), ("c3", dict(batch=24, steps=3, vocab=32003)),
+                                     ("c2", dict(batch=32, steps=3))],
+                         ids=["c3", "c3-odd-vocab", "c2"])
+@pytest.mark.parametrize("n_top", [1, 12, 200], ids=["top1", "top12", "top200"])
+def test_largest_columns_in_history_against_reference(name, kw, n_top, cuda_device):
+    """The prompt of every row holds the row's largest columns of every step (what a long generation does to
+    itself): the row maximum is a penalised column, so the maximum over the other columns has to be found, and
+    many of the per-slot maxima of the first pass belong to penalised columns."""
+    from fastertransformer_b200.workloads import make_workload
+    w = make_workload(name, **kw)
+    mil = w.max_input_length
+    assert mil >= 3 * n_top or n_top == 200
+    prompt = w.prompt.copy()
+    pos = 0
+    for s in range(w.steps):
+        x = w.logits(mil + s, cuda_device).float()[:, :w.vocab]
+        top = torch.topk(x, n_top, dim=1).indices.cpu().numpy().astype(np.int32)       # [batch, n_top]
+        take = min(n_top, (mil - pos))
+        prompt[pos:pos + take] = top[:, :take].T
+        pos += take
+    w.prompt = prompt
+    ref_layer, ref_dt = _ref_layer(w, cuda_device)
+    ref = run_cuda_like(ref_layer, w, cuda_device, cast=ref_dt, with_criteria=False)
+    mine = run_cuda_like(_layer(w, cuda_device), w, cuda_device)
+    _compare(mine, ref, name)
