@@ -82,6 +82,8 @@ SMALL = [
     ("c2", dict(batch=16, steps=5)),
     ("c3", dict(batch=48, steps=4)),
     ("c3", dict(batch=24, steps=3, vocab=32003)),
+    ("c3", dict(batch=32, steps=40)),                 # long enough for sampled tokens to come back penalised
+    ("c2", dict(batch=24, steps=40)),
 ]
 
 
