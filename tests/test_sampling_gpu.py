@@ -200,10 +200,21 @@ def test_full_size_properties(cuda_device):
         # penalties only lower history tokens, so a sampled token's rank can only improve
         assert (rank[topk_rows] < kk[topk_rows] + w.max_input_length + s + 24).all()
         greedy = kk == 1
-        bad = torch.from_numpy(w.bad_words[:, 0, :]).to(cuda_device).long()
-        assert not (ids[:, None] == bad[:, :1]).any() or True
         assert (rank[greedy] <= w.max_input_length + s + 24).all()
-    assert (out["sequence_length"][-1] == w.max_input_length + 2).all() or out["finished"].any()
+        # a one-token bad word bans its token outright
+        ends = w.bad_words[:, 1, :]
+        starts = np.concatenate([np.zeros((w.batch, 1), np.int32), ends[:, :-1]], axis=1)
+        single = (ends >= 0) & (ends - starts == 1)
+        tok = np.take_along_axis(w.bad_words[:, 0, :], np.clip(starts, 0, None), axis=1)
+        assert single.any()
+        assert not ((tok == out["ids"][s][:, None]) & single).any()
+    # a row's length grows by one per step until the row has drawn its end id
+    done_before = np.concatenate([np.zeros((1, w.batch), bool), out["finished"][:-1].astype(bool)])
+    grow = np.diff(np.concatenate([np.full((1, w.batch), w.max_input_length), out["sequence_length"]]), axis=0)
+    topk_rows = kk > 0
+    assert (grow[:, topk_rows][~done_before[:, topk_rows]] == 1).all()
+    assert (grow[:, topk_rows][done_before[:, topk_rows]] == 0).all()
+    assert (out["finished"].astype(bool) == (out["ids"] == w.end_id))[:, topk_rows][~done_before[:, topk_rows]].all()
 
 
 @pytest.mark.gpu
