@@ -1,0 +1,1118 @@
+// Single-pass form of the fused decode-sampling step for 16-bit logits (half / bfloat16) without an
+// embedding bias: the kernel that serves the rows of a step first.  What it cannot decide from one pass
+// (and every row kind it does not cover) is put on a list that decode_sampling_kernel works off afterwards,
+// so the results are those of that kernel - and therefore the reference's - for every row.
+//
+// One CTA serves one row at a time; several CTAs share an SM, so that the fixed work of one row (set-up,
+// threshold search, the draw) runs under the streaming of the others.  Per row:
+//   1. a strided sample of 4096 columns gives, by bisection over the ordered 16-bit keys, a raw threshold
+//      that about 2k (at least 128) columns of the row are expected to reach;
+//   2. ONE pass over the row (16-byte loads, eight in flight per thread, one packed compare per two logits)
+//      queues the vectors that hold a column at or above the threshold;
+//   3. the queued vectors give the candidate columns and the count of every value class (bit pattern) above
+//      the threshold; penalised / banned columns (token history, bad words, min-length) are taken out and
+//      come back with their final values from a short list, as do the columns outside the aligned vectors;
+//   4. the draw of topk_stage2_sampling (kernels/sampling_topk_kernels.cu:255-311) walks the classes from the
+//      top - equal values add the same exponential, so the sorted sequence is (value, count) runs and no
+//      sort of the candidates is needed - and the tie order inside the class the draw lands in follows
+//      the reference's two-stage reduction (see resolve_topk_class).
+// A row whose candidates turn out to be fewer than k, or that overflows one of the fixed-size tables, is
+// left untouched (its generator state included) and goes to the list.
+#pragma once
+#include "sampling_kernels.cuh"
+
+namespace ftb200 {
+
+constexpr int kFCap      = 4096;  // candidate columns held in shared memory
+constexpr int kFBins     = 2048;  // value classes (bit patterns) above the threshold
+constexpr int kFSpecCap  = 128;   // listed columns (special or edge) at or above the threshold
+constexpr int kFClsCap   = 768;   // members of the class the draw lands in
+constexpr int kFRuns     = 1536;  // runs the draw may walk (classes + listed columns among the first k)
+constexpr int kFRunBytes = kFRuns * 8 + kFBins * 2;
+constexpr int kFSampleV  = 2;     // sampled vectors per thread (4096 columns per row)
+constexpr int kFUnroll   = 8;     // 16-byte loads in flight per thread
+
+// Shared-memory map of the single-pass kernel (dynamic shared memory, offsets fixed per launch).
+struct FMap {
+    u32*            cand;  // [kFCap]    (relative key << 20) | column
+    u32*            emask; // [mask_words] per aligned vector one byte: which of its columns are special; after the
+                           //              pass the same area holds the listed columns and the run arrays of the draw
+    u32*            hash;  // [hash_slots] (id << 2) | flags, open addressing
+    u32*            sval;  // [hash_slots] gathered raw word, then the final value of that column (float bits)
+    u32*            hist;  // [kFBins]   columns per value class above the threshold
+    u32*            stage; // [kFStageBytes / 4] token history, word list and last tokens of the row, as fetched
+};
+
+constexpr int kFMaxHist    = 1024;  // token-history entries the single-pass kernel stages
+constexpr int kFMaxWords   = 128;   // bad-word list length it stages
+constexpr int kFStageBytes = (kFMaxHist + 2 * kFMaxWords + 4) * 4;
+// bytes of the per-vector mask area: one byte per aligned vector, and room for what follows the pass
+__host__ __device__ inline size_t fast_mask_bytes(int vocab_padded)
+{
+    const size_t need = ((size_t)vocab_padded / 8 + 16 + 15) / 16 * 16;
+    const size_t post = (size_t)kFSpecCap * 8 + (size_t)kFRunBytes;
+    return need > post ? need : post;
+}
+__host__ __device__ inline size_t fast_smem_bytes(int hash_slots, int vocab_padded)
+{
+    return (size_t)kFCap * 4 + fast_mask_bytes(vocab_padded) + (size_t)hash_slots * 8 + (size_t)kFBins * 4
+           + (size_t)kFStageBytes;
+}
+
+__device__ __forceinline__ void cp_async4(u32 saddr, const void* g)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all()
+{
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// Row constants of the single-pass kernel (shared memory, written by thread 0).
+struct FRow {
+    const char* rowp;
+    int         head, nfull, r, end_id, k;
+    float       inv_t, theta, top_p, u;
+    __half      inv_t_h;
+    int*        id_out;
+    u64*        trace;  // this row's record of the diagnostic timeline, or null
+};
+
+static __device__ void f_hash_insert(u32* hash, int slots, int shift, int id, u32 flag, int vocab_padded)
+{
+    if (id < 0 || id >= vocab_padded) {
+        return;
+    }
+    FTB_ASSUME_SHARED(hash);
+    u32       h    = hash_slot(id, shift);
+    const u32 want = ((u32)id << 2) | flag;
+    for (int probe = 0; probe < slots; ++probe) {
+        const u32 old = smem_cas(&hash[h], kHashEmpty, want);
+        if (old == kHashEmpty) {
+            break;
+        }
+        if ((old >> 2) == (u32)id) {
+            smem_or(&hash[h], flag);
+            break;
+        }
+        h = (h + 1) & (slots - 1);
+    }
+}
+
+// Value of a raw 16-bit pattern after temperature (no bias on this path).
+template<int DT>
+__device__ __forceinline__ float f_value(u32 raw, bool temp, float inv_t, __half inv_t_h)
+{
+    if (DT == FTB200_F16) {
+        __half h = __ushort_as_half((unsigned short)raw);
+        if (temp) {
+            h = __hmul(h, inv_t_h);
+        }
+        return __half2float(h);
+    }
+    float x = __uint_as_float(raw << 16);
+    if (temp) {
+        x = x * inv_t;
+    }
+    return x;
+}
+
+// Slot of column `id` in the hash, -1 when it has none.
+__device__ __forceinline__ int f_hash_find(const u32* hash, int shift, int mask, int id)
+{
+    FTB_ASSUME_SHARED(hash);
+    u32 h = hash_slot(id, shift);
+    for (int probe = 0; probe <= mask; ++probe) {
+        const u32 v = hash[h];
+        if (v == kHashEmpty) {
+            return -1;
+        }
+        if ((v >> 2) == (u32)id) {
+            return (int)h;
+        }
+        h = (h + 1) & mask;
+    }
+    return -1;
+}
+
+// What the pass over the row leaves behind, all in shared memory.
+struct FSink {
+    u32*                 cand;   // [kFCap] (relative key << 20) | column of every ordinary column at or above the threshold
+    u32*                 hist;   // [kFBins] columns per relative key
+    u32*                 sval;   // per hash slot: raw bits of that special column
+    const u32*           hash;
+    const unsigned char* emask;  // per aligned vector: bit e set = column e of the vector is special
+    u32*                 ncand;
+    u32*                 bad;    // set when a relative key does not fit the class table
+    int                  shift, mask;
+};
+
+// One dense step of the side path: every lane below `n` takes one parked vector of its warp, finds the columns at
+// or above the threshold from the packed compares, leaves the raw values of special ones next to their hash
+// slots and turns the others into candidates (one reservation in the candidate list per step and warp).
+template<int DT>
+__device__ __forceinline__ void f_side_step(const uint4& v, int jj, bool live, int head, u32 thr_key, u32 thr2,
+                                            const FSink& K, u32& relmax)
+{
+    const int lane = threadIdx.x & 31;
+    u32       pm   = 0;
+    if (live) {
+        const u32 m0 = ge2_mask<DT>(v.x, thr2), m1 = ge2_mask<DT>(v.y, thr2);
+        const u32 m2 = ge2_mask<DT>(v.z, thr2), m3 = ge2_mask<DT>(v.w, thr2);
+        pm = ((m0 & 1u) | ((m0 >> 15) & 2u)) | (((m1 & 1u) | ((m1 >> 15) & 2u)) << 2)
+             | (((m2 & 1u) | ((m2 >> 15) & 2u)) << 4) | (((m3 & 1u) | ((m3 >> 15) & 2u)) << 6);
+        const u32 em = K.emask[jj];
+        u32       sp = pm & em;
+        pm &= ~em;
+        while (sp != 0) {  // rare: a special column at or above the threshold
+            const int e = __ffs(sp) - 1;
+            sp &= sp - 1;
+            const int slot = f_hash_find(K.hash, K.shift, K.mask, head + jj * 8 + e);
+            if (slot >= 0) {
+                K.sval[slot] = raw_bits<DT>(v, e);
+            }
+        }
+    }
+    const u32 n    = (u32)__popc(pm);
+    u32       incl = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u32 t = __shfl_up_sync(0xffffffffu, incl, o);
+        incl += lane >= o ? t : 0u;
+    }
+    const u32 total = __shfl_sync(0xffffffffu, incl, 31);
+    if (total == 0) {
+        return;
+    }
+    u32 base = 0;
+    if (lane == 0) {
+        base = atomicAdd(K.ncand, total);
+    }
+    base    = __shfl_sync(0xffffffffu, base, 0);
+    u32 pos = base + incl - n;
+    while (pm != 0) {
+        const int e = __ffs(pm) - 1;
+        pm &= pm - 1;
+        const u32 rel = key16(raw_bits<DT>(v, e)) - thr_key;
+        if (rel >= (u32)kFBins) {
+            *K.bad = 1;  // (the slot stays unwritten: the row is given up)
+        }
+        else {
+            relmax = rel > relmax ? rel : relmax;
+            if (pos < (u32)kFCap) {
+                K.cand[pos] = (rel << 20) | (u32)(head + jj * 8 + e);
+            }
+            smem_add(&K.hist[rel], 1u);
+        }
+        ++pos;
+    }
+}
+
+// The one pass over the row.  Eight 16-byte loads in flight per thread, one packed compare per two logits.
+// A vector with a column at or above the threshold is a rare event for a lane but a common one for a warp, so
+// a lane does not look at its own hit: it parks the vector in a small ring of its warp, and whenever 32
+// vectors are parked the warp takes them one per lane (f_side_step).  Nothing of the row is read a second time.
+constexpr int kFRing = 64;  // parked vectors per warp
+template<int DT>
+__device__ __noinline__ void f_stream(const uint4* vp, int nfull, int head, u32 thr_key, const FSink K, u32* relmax_out)
+{
+    __shared__ uint4          s_wbuf[kWarps][kFRing];
+    __shared__ unsigned short s_wj[kWarps][kFRing];
+    FTB_ASSUME_SHARED(K.cand);
+    FTB_ASSUME_SHARED(K.hist);
+    FTB_ASSUME_SHARED(K.sval);
+    FTB_ASSUME_SHARED(K.emask);
+    FTB_ASSUME_SHARED(K.ncand);
+    FTB_ASSUME_SHARED(K.bad);
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const u32 thr_raw = key16_inv(thr_key);
+    const u32 thr2    = thr_raw | (thr_raw << 16);
+    uint4* const          wbuf = s_wbuf[wid];
+    unsigned short* const wj   = s_wj[wid];
+    int  rd = 0, cnt = 0;  // ring read position and fill (the same in every lane)
+    u32  relmax = 0;
+    for (int jb = 0; jb < nfull; jb += kThreads * kFUnroll) {
+        uint4 q[kFUnroll];
+#pragma unroll
+        for (int u = 0; u < kFUnroll; ++u) {
+            const int j = jb + u * kThreads + tid;
+            if (j < nfull) {
+                q[u] = ld_nc_v4(vp + j);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kFUnroll; ++u) {
+            const int j   = jb + u * kThreads + tid;
+            bool      hit = false;
+            if (j < nfull) {
+                const u32 m = (ge2_mask<DT>(q[u].x, thr2) | ge2_mask<DT>(q[u].y, thr2))
+                              | (ge2_mask<DT>(q[u].z, thr2) | ge2_mask<DT>(q[u].w, thr2));
+                hit         = m != 0;
+            }
+            const u32 hits = __ballot_sync(0xffffffffu, hit);
+            if (hits == 0) {
+                continue;
+            }
+            if (hit) {
+                const int at = (rd + cnt + __popc(hits & ((1u << lane) - 1u))) & (kFRing - 1);
+                wbuf[at]     = q[u];
+                wj[at]       = (unsigned short)j;
+            }
+            cnt += __popc(hits);
+            if (cnt >= 32) {
+                __syncwarp();
+                const int at = (rd + lane) & (kFRing - 1);
+                f_side_step<DT>(wbuf[at], (int)wj[at], true, head, thr_key, thr2, K, relmax);
+                rd = (rd + 32) & (kFRing - 1);
+                cnt -= 32;
+                __syncwarp();
+            }
+        }
+    }
+    __syncwarp();
+    if (cnt > 0) {
+        const int  at   = (rd + lane) & (kFRing - 1);
+        const bool live = lane < cnt;
+        uint4      v    = make_uint4(0u, 0u, 0u, 0u);
+        int        jj   = 0;
+        if (live) {
+            v  = wbuf[at];
+            jj = (int)wj[at];
+        }
+        f_side_step<DT>(v, jj, live, head, thr_key, thr2, K, relmax);
+    }
+    relmax = __reduce_max_sync(0xffffffffu, relmax);
+    if (lane == 0 && relmax != 0) {
+        atomicMax(relmax_out, relmax);
+    }
+}
+
+// The `want`-th largest of the CTA's per-thread sample maxima (ordered 16-bit keys in smax[kThreads]), by
+// bisection inside one warp.  With `want` far below the number of threads it is, to within a few ranks, the
+// `want`-th largest of all sampled columns - on the low side, which only lets a few more candidates through.
+__device__ __forceinline__ u32 f_select_from_maxima(const unsigned short* smax, u32 want)
+{
+    FTB_ASSUME_SHARED(smax);
+    const int lane = threadIdx.x & 31;
+    u32       mine[kThreads / 32];
+#pragma unroll
+    for (int i = 0; i < kThreads / 32; ++i) {
+        mine[i] = smax[i * 32 + lane];
+    }
+    u32 lo = 0, hi = 0xffffu;
+#pragma unroll 1
+    for (int it = 0; it < 16; ++it) {
+        const u32 mid = (lo + hi + 1) >> 1;
+        u32       c   = 0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) {
+            c += mine[i] >= mid ? 1u : 0u;
+        }
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (c >= want) {
+            lo = mid;
+        }
+        else {
+            hi = mid - 1;
+        }
+    }
+    return lo;
+}
+
+// Tie order inside one value class for m <= kThreads members (the rules of resolve_topk_class, by counting
+// instead of sorting): member a of lane l = (col / bs1) % 8 has stage-1 rank
+//   lane_base[l] + #{b in lane l : t1(b) > t1(a), or t1 equal and col(b) < col(a)},  t1 = col % bs1;
+// members whose rank reaches k do not leave stage 1; the others are ordered by ((lane * k + rank) % bs2
+// descending, lane * k + rank ascending).  Returns the column at position `want` of that order, -1 when
+// there is none.  CTA-collective.
+static __device__ int f_resolve_small(const u32* cols, int m, int want, int k, int bs1, int bs2, const u32* lane_base,
+                                      u32* key2, int* s_ans)
+{
+    const int tid = threadIdx.x;
+    FTB_ASSUME_SHARED(cols);
+    FTB_ASSUME_SHARED(key2);
+    if (tid == 0) {
+        *s_ans = -1;
+    }
+    if (tid < m) {
+        const u32 c = cols[tid], lane = (c / (u32)bs1) & 7u, t1 = c % (u32)bs1;
+        u32       rk = 0;
+        for (int b = 0; b < m; ++b) {
+            const u32 cb = cols[b], lb = (cb / (u32)bs1) & 7u, tb = cb % (u32)bs1;
+            rk += (lb == lane && (tb > t1 || (tb == t1 && cb < c))) ? 1u : 0u;
+        }
+        const u32 r = lane_base[lane] + rk;
+        u32       key = 0xffffffffu;
+        if (r < (u32)k) {
+            const u32 i2 = lane * (u32)k + r;  // < 8 * 1024
+            key          = (((u32)bs2 - 1u - (i2 % (u32)bs2)) << 16) | i2;
+        }
+        key2[tid] = key;
+    }
+    __syncthreads();
+    if (tid < m) {
+        const u32 mine = key2[tid];
+        if (mine != 0xffffffffu) {
+            int rk = 0;
+            for (int b = 0; b < m; ++b) {
+                rk += key2[b] < mine ? 1 : 0;
+            }
+            if (rk == (want < m ? want : m - 1)) {
+                *s_ans = (int)cols[tid];
+            }
+        }
+    }
+    __syncthreads();
+    const int ans = *s_ans;
+    __syncthreads();
+    return ans;
+}
+
+// Header of a row.  It is put together one row ahead by thread 0, in stages spread over the row in front, so
+// that none of the dependent loads behind it (ticket -> row number -> per-row arguments and generator state) is
+// waited for.
+struct FHdr {
+    int    t;  // ticket; >= the number of rows when none is left
+    int    r, mode, fin, end_id, k;
+    float  top_p, u, inv_t, theta;
+    __half inv_t_h;
+};
+// landing zone of the next row's arguments (32-bit words; the two generator states sit on 16-byte boundaries)
+constexpr int kFPreWords = 48;
+enum { kPreStateK = 0, kPreStateP = 12, kPreSkipK = 24, kPreSkipP, kPreFin, kPreEnd, kPreK, kPrePk, kPrePp, kPreTemp,
+       kPreRep };
+
+__device__ __forceinline__ void cp_async16(u32 saddr, const void* g)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
+}
+
+// Arguments of row nr on their way into pre[] (thread 0 only).
+static __device__ void f_prefetch_header(const KParams& P, int nr, u32* pre)
+{
+    const u32 base = (u32)__cvta_generic_to_shared(pre);
+    auto word = [&](int slot, const void* p) {
+        cp_async4(base + 4u * (u32)slot, (const void*)((size_t)p & ~(size_t)3));
+    };
+    if (P.topk_states != nullptr) {
+        const char* st = (const char*)(P.topk_states + nr);
+        cp_async16(base + 4u * kPreStateK, st);
+        cp_async16(base + 4u * kPreStateK + 16u, st + 16);
+        cp_async16(base + 4u * kPreStateK + 32u, st + 32);
+        word(kPreK, P.topk_ks + nr);
+        word(kPrePk, P.topk_ps + nr);
+        if (P.topk_skip != nullptr) {
+            word(kPreSkipK, P.topk_skip + nr);
+        }
+    }
+    if (P.topp_states != nullptr) {
+        const char* st = (const char*)(P.topp_states + nr);
+        cp_async16(base + 4u * kPreStateP, st);
+        cp_async16(base + 4u * kPreStateP + 16u, st + 16);
+        cp_async16(base + 4u * kPreStateP + 32u, st + 32);
+        word(kPrePp, P.topp_ps + nr);
+        if (P.topp_skip != nullptr) {
+            word(kPreSkipP, P.topp_skip + nr);
+        }
+    }
+    if (P.finished != nullptr) {
+        word(kPreFin, P.finished + nr);
+    }
+    word(kPreEnd, P.end_ids + nr);
+    if (P.apply_temp) {
+        word(kPreTemp, P.temperature + nr);
+    }
+    if (P.apply_rep) {
+        word(kPreRep, P.rep_penalty + nr);
+    }
+    cp_async_commit();
+}
+
+// Header of ticket nt / row nr from what f_prefetch_header brought in (thread 0 only, after its copies landed).
+static __device__ void f_compose_header(const KParams& P, int nt, int nr, const u32* pre, FHdr& H)
+{
+    H.t = nt;
+    if (nt >= P.local_batch) {
+        return;
+    }
+    auto byte_at = [&](int slot, const void* p) { return (pre[slot] >> (8 * ((size_t)p & 3))) & 0xffu; };
+    int  mode = 0;
+    if (P.topk_states != nullptr && !(P.topk_skip != nullptr && byte_at(kPreSkipK, P.topk_skip + nr) != 0)) {
+        mode = 1;
+    }
+    else if (P.topp_states != nullptr && !(P.topp_skip != nullptr && byte_at(kPreSkipP, P.topp_skip + nr) != 0)) {
+        mode = 2;
+    }
+    H.r      = nr;
+    H.mode   = mode;
+    H.fin    = P.finished != nullptr ? (int)(byte_at(kPreFin, P.finished + nr) != 0) : 0;
+    H.end_id = (int)pre[kPreEnd];
+    int k    = (int)pre[kPreK];
+    H.k      = k < 1 ? 1 : (k > kMaxTopK ? kMaxTopK : k);
+    H.top_p  = __uint_as_float(mode == 1 ? pre[kPrePk] : pre[kPrePp]);
+    float inv_t = 1.0f;
+    if (P.apply_temp) {
+        inv_t = 1.0f / (__uint_as_float(pre[kPreTemp]) + 1e-6f);
+    }
+    H.inv_t   = inv_t;
+    H.inv_t_h = __float2half_rn(inv_t);
+    H.theta   = P.apply_rep ? __uint_as_float(pre[kPreRep]) : 1.0f;
+    H.u       = 0.0f;
+    if (mode != 0) {
+        // drawn from a copy: the state in memory moves on only when this kernel finishes the row
+        curandState_t st = *(const curandState_t*)(pre + (mode == 1 ? kPreStateK : kPreStateP));
+        H.u              = curand_uniform(&st);
+    }
+}
+
+// Geometry of a row.
+struct FGeo {
+    const char* rowp;
+    int         head, nfull;
+};
+__device__ __forceinline__ FGeo f_geometry(const KParams& P, int r)
+{
+    FGeo G;
+    G.rowp          = (const char*)P.logits + (size_t)r * P.vocab_padded * 2;
+    const size_t ad = (size_t)G.rowp;
+    const int    hd = (int)(((16 - (ad & 15)) & 15) / 2);
+    G.head          = hd < P.vocab_padded ? hd : P.vocab_padded;
+    const int vend  = P.vocab < P.vocab_padded ? P.vocab : P.vocab_padded;
+    G.nfull         = vend - G.head > 0 ? (vend - G.head) / 8 : 0;
+    return G;
+}
+
+
+// One row of the top-k layer.  Returns true when the row is done, false when it has to go to the list
+// (nothing of the row's state has been touched then).  CTA-collective.  `stage1` / `stage2` are the hooks
+// of the next row's header (run by thread 0 at points where the loads of the previous stage have had time
+// to land).
+template<int DT, class S1, class S2>
+__device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u64* trace, S1&& stage1, S2&& stage2)
+{
+    __shared__ u32            s_ncand, s_nspec, s_bad, s_ncls, s_lane_base[8], s_thr, s_relmax;
+    __shared__ unsigned short s_smax[kThreads];
+    __shared__ int            s_pick_idx, s_ans, s_nruns;
+    __shared__ float          s_vsel;
+    const int                 tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const bool                temp = P.apply_temp != 0;
+    u32* const                hash = S.hash;
+    u32* const                sval = S.sval;
+    u32* const                hist = S.hist;
+    u32* const                cand = S.cand;
+    FTB_ASSUME_SHARED(hash);
+    FTB_ASSUME_SHARED(sval);
+    FTB_ASSUME_SHARED(hist);
+    FTB_ASSUME_SHARED(cand);
+    const int    r     = H.r;
+    const FGeo   G     = f_geometry(P, r);
+    const uint4* vp    = (const uint4*)(G.rowp + (size_t)G.head * 2);
+    const int    nfull = G.nfull;
+    const size_t col   = (size_t)P.ite * P.local_batch + r;
+
+    // ---- everything the row's set-up needs is sent for at once: the sampled columns into registers, the
+    //      token history, the word list and the last three tokens into shared memory (asynchronous copies) ----
+    // sample: 16 blocks of 512 contiguous bytes spread over the row (one per warp and round), 4096 columns
+    uint4 smp[kFSampleV];
+#pragma unroll
+    for (int v = 0; v < kFSampleV; ++v) {
+        const int blk   = v * kWarps + wid;
+        const int start = (int)(((long long)blk * (nfull - 32)) / (kFSampleV * kWarps - 1)) & ~31;
+        smp[v]          = ld_nc_v4(vp + start + lane);
+    }
+    int* const stage_ids   = (int*)S.stage;                 // [kFMaxHist] history ids (-1: position not counted)
+    int* const stage_words = stage_ids + kFMaxHist;         // [2 * kFMaxWords] the row's word list
+    int* const stage_last  = stage_words + 2 * kFMaxWords;  // [3] tokens of steps step-3 .. step-1
+    FTB_ASSUME_SHARED(stage_ids);
+    FTB_ASSUME_SHARED(stage_words);
+    FTB_ASSUME_SHARED(stage_last);
+    const int  L     = P.bad_words != nullptr ? P.bad_words_len : 0;
+    const int* wbase = L > 0 ? (P.bad_words_shared ? P.bad_words : P.bad_words + (size_t)r * 2 * L) : nullptr;
+    const int  nhist = P.apply_rep ? P.step : 0;
+    {
+        // (input_lengths is read here, one dependent load: it is the same few cache lines for every row)
+        const int input_len = P.apply_rep ? (P.input_lengths != nullptr ? P.input_lengths[r] : P.max_input_len) : 0;
+        for (int t = tid; t < nhist; t += kThreads) {
+            if (t >= input_len && t < P.max_input_len) {
+                stage_ids[t] = -1;
+            }
+            else {
+                cp_async4((u32)__cvta_generic_to_shared(&stage_ids[t]), P.output_ids + (size_t)t * P.batch_size + col);
+            }
+        }
+        for (int i = tid; i < 2 * L; i += kThreads) {
+            cp_async4((u32)__cvta_generic_to_shared(&stage_words[i]), wbase + i);
+        }
+        if (tid < 3 && P.step - 3 + tid >= 0) {
+            cp_async4((u32)__cvta_generic_to_shared(&stage_last[tid]),
+                      P.output_ids + (size_t)(P.step - 3 + tid) * P.batch_size + col);
+        }
+        cp_async_commit();
+    }
+    u32* const emask32 = S.emask;
+    FTB_ASSUME_SHARED(emask32);
+    for (int i = tid; i < P.hash_slots; i += kThreads) {
+        hash[i] = kHashEmpty;
+        sval[i] = 0xffffffffu;  // no raw value seen: the column lies below the threshold
+    }
+    for (int i = tid; i < kFBins; i += kThreads) {
+        hist[i] = 0;
+    }
+    for (int i = tid; i < (nfull + 3) / 4; i += kThreads) {
+        emask32[i] = 0;
+    }
+    if (tid < 8) {
+        s_lane_base[tid] = 0;
+    }
+    if (tid == 0) {
+        s_ncand = 0, s_nspec = 0, s_bad = 0, s_ncls = 0, s_relmax = 0;
+    }
+    {
+        // largest sampled column of this thread, as an ordered key
+        u32 m2 = max2<DT>(max2<DT>(smp[0].x, smp[0].y), max2<DT>(smp[0].z, smp[0].w));
+#pragma unroll
+        for (int v = 1; v < kFSampleV; ++v) {
+            m2 = max2<DT>(m2, max2<DT>(max2<DT>(smp[v].x, smp[v].y), max2<DT>(smp[v].z, smp[v].w)));
+        }
+        const u32 ka = key16(m2 & 0xffffu), kb = key16(m2 >> 16);
+        s_smax[tid]  = (unsigned short)(ka > kb ? ka : kb);
+    }
+    cp_async_wait_all();  // history, word list and last tokens have landed
+    __syncthreads();
+    stage1();
+    trace_mark(trace, 0);
+
+    // ---- threshold from the sample (warp 0) while the other warps file the special columns: token history,
+    //      banned words, min-length mask (the rules of build_row; kernels/sampling_penalty_kernels.cu:385-410,
+    //      :493-499, kernels/ban_bad_words.cu:35-85) ----
+    const int k      = H.k;
+    const int ncols  = nfull * 8;
+    // columns the threshold should let through: 2k, at least k + 256 (the estimate from a few sampled maxima
+    // scatters widely); for k = 1 a handful is enough
+    const int target = k == 1 ? 64 : (2 * k > k + 256 ? 2 * k : k + 256);
+    u32       want_s = (u32)(((long long)target * (kFSampleV * kThreads * 8) + ncols - 1) / ncols);
+    want_s           = want_s < 3u ? 3u : want_s;
+    bool words_ok    = true;
+    if (wid == 0) {
+        const u32 t = f_select_from_maxima(s_smax, want_s);
+        if (lane == 0) {
+            s_thr = t;
+        }
+    }
+    else {
+        const int wt = tid - 32, wn = kThreads - 32;
+        for (int t = wt; t < nhist; t += wn) {
+            const int id = stage_ids[t];
+            if (id >= 0) {
+                f_hash_insert(hash, P.hash_slots, P.hash_shift, id, kFlagHist, P.vocab_padded);
+            }
+        }
+        for (int i = wt; i < L; i += wn) {
+            const int e1 = stage_words[L + i];
+            if (e1 < 0) {
+                continue;
+            }
+            const int s1 = i > 0 ? stage_words[L + i - 1] : 0, size = e1 - s1;
+            if (size > 4) {
+                words_ok = false;  // longer words: the general kernel's loop
+                continue;
+            }
+            bool b = size == 1;
+            if (size > 1 && P.step >= size - 1) {
+                b = true;
+                for (int j = 0; j < size - 1; ++j) {
+                    // generated token of step (step - (size - 1) + j)
+                    b = b && stage_last[3 - (size - 1) + j] == stage_words[s1 + j];
+                }
+            }
+            if (b) {
+                const int tok = stage_words[e1 - 1];
+                if (0 < tok && tok < P.vocab_padded) {
+                    f_hash_insert(hash, P.hash_slots, P.hash_shift, tok, kFlagDead, P.vocab_padded);
+                }
+            }
+        }
+        if (P.apply_minlen && wt == 0) {
+            if (P.seq_len[r] + 1 - P.max_input_len < P.min_lengths[r]) {
+                f_hash_insert(hash, P.hash_slots, P.hash_shift, H.end_id, kFlagDead, P.vocab_padded);
+            }
+        }
+    }
+    const bool long_words = __syncthreads_or(!words_ok);
+    stage2();
+    // per-vector byte: which columns of the vector are special
+    for (int i = tid; i < P.hash_slots; i += kThreads) {
+        const u32 w = hash[i];
+        if (w != kHashEmpty) {
+            const int rel = (int)(w >> 2) - G.head;
+            if (rel >= 0 && (rel >> 3) < nfull) {
+                smem_or(&emask32[rel >> 5], (1u << (rel & 7)) << (8 * ((rel >> 3) & 3)));
+            }
+        }
+    }
+    const u32   thr_key = s_thr;
+    const u32   thr_raw = key16_inv(thr_key);
+    const float thr_y   = f_value<DT>(thr_raw, temp, H.inv_t, H.inv_t_h);
+    const float neg_max = DT == FTB200_F16 ? -65504.0f : -FLT_MAX;
+    __syncthreads();
+    trace_mark(trace, 1);
+    if (long_words || want_s > 96u || !(thr_y > neg_max) || thr_key == 0u) {
+        return false;  // (uniform for the CTA)
+    }
+
+    // ---- the pass ----
+    {
+        FSink K;
+        K.cand = cand, K.hist = hist, K.sval = sval, K.hash = hash, K.emask = (const unsigned char*)emask32;
+        K.ncand = &s_ncand, K.bad = &s_bad, K.shift = P.hash_shift, K.mask = P.hash_slots - 1;
+        f_stream<DT>(vp, nfull, G.head, thr_key, K, &s_relmax);
+    }
+    __syncthreads();
+    trace_mark(trace, 2);
+    trace_mark(trace, 3);
+    trace_mark(trace, 4);
+    // ---- listed columns: special ones with their final value, and the row's edges ----
+    u64* const spec = (u64*)S.emask;  // [kFSpecCap] (~key(value) << 32) | column; the per-vector bytes are done with
+    FTB_ASSUME_SHARED(spec);
+    {
+        Xf X;
+        X.bias = nullptr, X.inv_t = H.inv_t, X.theta = H.theta, X.neg_max = neg_max, X.inv_t_h = H.inv_t_h;
+        X.apply_temp = P.apply_temp, X.apply_rep = P.apply_rep, X.penalty_type = P.penalty_type, X.vocab = P.vocab;
+        X.hash_shift = P.hash_shift, X.hash_mask = P.hash_slots - 1, X.hash = hash;
+        auto push = [&](int c, float y) {
+            if (y >= thr_y && y > neg_max) {
+                const u32 pos = atomicAdd(&s_nspec, 1u);
+                if (pos < (u32)kFSpecCap) {
+                    spec[pos] = ((u64)(~fkey(y)) << 32) | (u32)c;
+                }
+            }
+        };
+        for (int i = tid; i < P.hash_slots; i += kThreads) {
+            const u32 w = hash[i];
+            if (w == kHashEmpty) {
+                continue;
+            }
+            const int id = (int)(w >> 2);
+            if (id >= P.vocab) {
+                continue;
+            }
+            const int rel = id - G.head;
+            const u32 raw = (rel >= 0 && (rel >> 3) < nfull) ? sval[i] : (u32)__ldg((const unsigned short*)G.rowp + id);
+            if (raw == 0xffffffffu) {
+                continue;  // below the threshold before its penalty, and a penalty only lowers a value here
+            }
+            push(id, special_value<DT>(X, temp_value<DT>(X, raw, id), w & 3u));
+        }
+        const int tail0 = G.head + nfull * 8;
+        const int nedge = G.head + (P.vocab - tail0 > 0 ? P.vocab - tail0 : 0);
+        for (int i = tid; i < nedge; i += kThreads) {
+            const int v = i < G.head ? i : tail0 + (i - G.head);
+            if (v < P.vocab && hash_lookup_raw(hash, X.hash_shift, X.hash_mask, v) == 0) {
+                push(v, temp_value<DT>(X, (u32)__ldg((const unsigned short*)G.rowp + v), v));
+            }
+        }
+    }
+    __syncthreads();
+    trace_mark(trace, 5);
+    const int n_ord = (int)s_ncand, n_sp = (int)s_nspec;
+    if (s_bad || n_ord > kFCap || n_sp > kFSpecCap || n_ord + n_sp < k) {
+        return false;
+    }
+
+    // ---- the draw (warp 0): runs of equal values from the top, then the reference's sequential sum and walk ----
+    float* const          fe    = (float*)(spec + kFSpecCap);      // [kFRuns] value of the run
+    unsigned short* const fc    = (unsigned short*)(fe + kFRuns);  // [kFRuns] columns of the run
+    unsigned short* const crank = fc + kFRuns;                     // [kFBins] relative key of the a-th class from the top
+    float* const          flat  = (float*)hist;                    // [k] exponentials of the first k entries (the counts are
+                                                                   //     done with once the runs stand)
+    FTB_ASSUME_SHARED(fe);
+    FTB_ASSUME_SHARED(fc);
+    FTB_ASSUME_SHARED(crank);
+    FTB_ASSUME_SHARED(flat);
+    if (wid == 0) {
+        group_sort_u64<WarpSync, true>(spec, n_sp, lane, 32, WarpSync());
+        __syncwarp();
+        auto spec_above = [&](float v) {  // listed columns with a value strictly above v
+            int       lo = 0, hi = n_sp;
+            const u32 kc = ~fkey(v);
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if ((u32)(spec[mid] >> 32) < kc) {
+                    lo = mid + 1;
+                }
+                else {
+                    hi = mid;
+                }
+            }
+            return lo;
+        };
+        // classes from the top bin down, 32 bins per trip, until they alone cover k columns (the listed columns
+        // can only add to that); a class sits at (its rank among the classes) + (listed columns above it)
+        int  nA = 0, covered = 0;
+        bool over = false;
+        for (int b0 = (int)s_relmax; b0 >= 0 && covered < k; b0 -= 32) {
+            const int b   = b0 - lane;
+            const u32 c   = b >= 0 ? hist[b] : 0u;
+            const u32 any = __ballot_sync(0xffffffffu, c != 0);
+            if (any == 0) {
+                continue;
+            }
+            if (c != 0) {
+                const float cv  = f_value<DT>(key16_inv(thr_key + (u32)b), temp, H.inv_t, H.inv_t_h);
+                const int   a   = nA + __popc(any & ((1u << lane) - 1u));
+                const int   pos = a + spec_above(cv);
+                if (pos < kFRuns) {
+                    fe[pos]  = cv;
+                    fc[pos]  = (unsigned short)c;
+                    crank[a] = (unsigned short)b;
+                }
+                else {
+                    over = true;
+                }
+            }
+            covered += (int)__reduce_add_sync(0xffffffffu, c);
+            nA += __popc(any);
+        }
+        over = __any_sync(0xffffffffu, over);
+        __syncwarp();
+        // a listed column sits at (its rank among the listed columns) + (classes at or above its value); below
+        // the last class taken the order no longer matters (k columns are covered before that)
+        if (!over) {
+            for (int i = lane; i < n_sp; i += 32) {
+                const float sv = fkey_inv(~(u32)(spec[i] >> 32));
+                int         lo = 0, hi = nA;  // classes (descending values) with value >= sv
+                while (lo < hi) {
+                    const int   mid = (lo + hi) >> 1;
+                    const float cv  = f_value<DT>(key16_inv(thr_key + (u32)crank[mid]), temp, H.inv_t, H.inv_t_h);
+                    if (cv >= sv) {
+                        lo = mid + 1;
+                    }
+                    else {
+                        hi = mid;
+                    }
+                }
+                const int pos = i + lo;
+                if (pos < kFRuns) {
+                    fe[pos] = sv;
+                    fc[pos] = 1;
+                }
+                else {
+                    over = true;
+                }
+            }
+            over = __any_sync(0xffffffffu, over);
+        }
+        const int nruns = nA + n_sp;
+        __syncwarp();
+        trace_mark(trace, 7);
+        if (!over) {
+            // the first k entries of the sorted sequence, as exponentials against the largest value: every run
+            // writes its copies (the sequence the reference's thread 0 walks, sampling_topk_kernels.cu:276-287)
+            const float vmax = fe[0];
+            int         at   = 0;  // entries in front of the current batch of runs
+            for (int p0 = 0; p0 < nruns && at < k; p0 += 32) {
+                const int p    = p0 + lane;
+                const int c    = p < nruns ? (int)fc[p] : 0;
+                int       incl = c;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    incl += lane >= o ? t : 0;
+                }
+                if (c != 0) {
+                    const float e   = __expf(fe[p] - vmax);
+                    const int   beg = at + incl - c;
+                    const int   end = beg + c < k ? beg + c : k;
+                    for (int i = beg; i < end; ++i) {
+                        flat[i] = e;
+                    }
+                }
+                at += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            __syncwarp();
+            trace_mark(trace, 8);
+            if (lane == 0) {
+                // dependent adds in the reference's order; operands come from shared memory eight at a time
+                const int k8  = k & ~7;
+                float     sum = 0.0f;
+                for (int i = 0; i < k8; i += 8) {
+                    const float4 a = *(const float4*)(flat + i), b = *(const float4*)(flat + i + 4);
+                    sum += a.x, sum += a.y, sum += a.z, sum += a.w;
+                    sum += b.x, sum += b.y, sum += b.z, sum += b.w;
+                }
+                for (int i = k8; i < k; ++i) {
+                    sum += flat[i];
+                }
+                float rand_num = H.u * H.top_p * sum;
+                int   pick     = k - 1;
+                for (int i = 0; i < k; i += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[j] = i + j < k ? flat[i + j] : 0.0f;
+                    }
+                    bool found = false;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (!found && i + j < k) {
+                            rand_num -= v[j];
+                            if (rand_num <= 0.0f || i + j == k - 1) {
+                                pick  = i + j;
+                                found = true;
+                            }
+                        }
+                    }
+                    if (found) {
+                        break;
+                    }
+                }
+                s_pick_idx = pick;
+                // value of the picked entry: the run that holds position `pick`
+                int acc = 0, prun = 0;
+                for (int p = 0; p < nruns; ++p) {
+                    acc += (int)fc[p];
+                    if (acc > pick) {
+                        prun = p;
+                        break;
+                    }
+                }
+                s_vsel = fe[prun];
+            }
+        }
+        if (lane == 0) {
+            s_nruns = over ? -1 : nruns;
+        }
+    }
+    __syncthreads();
+    trace_mark(trace, 9);
+    if (s_nruns < 0) {
+        return false;
+    }
+    // ---- the class the draw landed in: its members (all of them, also beyond the first k) and, per lane of
+    //      the reference's first stage, the number of larger candidates ----
+    const float vsel = s_vsel;
+    const u32   ksel = fkey(vsel);
+    if (DT == FTB200_F16 && temp && ksel == fkey(thr_y)) {
+        return false;  // half products round: patterns below the threshold may share the lowest class's value
+    }
+    // (the run arrays are not needed any more: the class members take their place)
+    u32* const cls  = (u32*)(spec + kFSpecCap);  // [kFClsCap]
+    u32* const key2 = cls + kFClsCap;   // [kThreads] scratch of the small resolve
+    FTB_ASSUME_SHARED(cls);
+    const u32 bs1 = P.max_top_k <= 16 ? 128 : 256;
+    const u32 bs2 = P.max_top_k <= 32 ? 128 : 256;
+    const int sh1 = bs1 == 128 ? 7 : 8;
+    {
+        u32 packd_lo = 0, packd_hi = 0;  // 8 x 8-bit counters (a thread sees at most kFCap / kThreads entries)
+        auto visit = [&](u32 kv, u32 c) {
+            if (kv == ksel) {
+                const u32 pos = atomicAdd(&s_ncls, 1u);
+                if (pos < (u32)kFClsCap) {
+                    cls[pos] = c;
+                }
+            }
+            else if (kv > ksel) {
+                const u32 l = (c >> sh1) & 7u;
+                if (l < 4) {
+                    packd_lo += 1u << (8 * l);
+                }
+                else {
+                    packd_hi += 1u << (8 * (l - 4));
+                }
+            }
+        };
+        for (int i = tid; i < n_ord; i += kThreads) {
+            const u32 e = cand[i];
+            visit(fkey(f_value<DT>(key16_inv(thr_key + (e >> 20)), temp, H.inv_t, H.inv_t_h)), e & 0xfffffu);
+        }
+        for (int i = tid; i < n_sp; i += kThreads) {
+            visit(~(u32)(spec[i] >> 32), (u32)(spec[i] & 0xffffffffu));
+        }
+        for (int l = 0; l < 8; ++l) {
+            u32 cnt = ((l < 4 ? packd_lo : packd_hi) >> (8 * (l & 3))) & 0xffu;
+            cnt     = __reduce_add_sync(0xffffffffu, cnt);
+            if (lane == 0 && cnt != 0) {
+                atomicAdd(&s_lane_base[l], cnt);
+            }
+        }
+    }
+    __syncthreads();
+    trace_mark(trace, 10);
+    const int m = (int)s_ncls;
+    // number of candidates above the class = position of its first member in the sorted sequence
+    int lo_cnt = 0;
+    for (int l = 0; l < 8; ++l) {
+        lo_cnt += (int)s_lane_base[l];
+    }
+    const int want = s_pick_idx - lo_cnt;
+    if (m > kFClsCap || m < 1 || want < 0 || want >= m) {
+        return false;  // (cannot happen for a consistent walk; the list takes the row if it does)
+    }
+    int idc;
+    if (m == 1) {
+        idc = (int)cls[0];
+    }
+    else if (m <= kThreads) {
+        idc = f_resolve_small(cls, m, want, k, (int)bs1, (int)bs2, s_lane_base, key2, &s_ans);
+    }
+    else {
+        // large classes: the sorting form, on 64-bit entries in the candidate area (its contents are done with)
+        u64* big = (u64*)cand;
+        for (int i = tid; i < m; i += kThreads) {
+            big[i] = (u64)cls[i];
+        }
+        __syncthreads();
+        idc = resolve_topk_class(big, m, want, k, (int)bs1, (int)bs2, s_lane_base);
+    }
+    if (tid == 0) {
+        if (idc < 0) {
+            idc = 0;
+        }
+        P.output_ids[(size_t)P.step * P.batch_size + col] = idc;
+        if (P.seq_len != nullptr && P.finished != nullptr) {
+            P.seq_len[r]  = P.seq_len[r] + 1;
+            P.finished[r] = idc == H.end_id ? 1 : 0;
+        }
+    }
+    return true;
+}
+
+template<int DT>
+__global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid_constant__ KParams P)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ FHdr                               s_hdr[2];
+    __shared__ __align__(16) u32                  s_pre[kFPreWords];
+    FMap                                          S;
+    S.cand = (u32*)smem_raw;
+    S.emask = S.cand + kFCap;
+    S.hash  = S.emask + fast_mask_bytes(P.vocab_padded) / 4;
+    S.sval  = S.hash + P.hash_slots;
+    S.hist  = S.sval + P.hash_slots;
+    S.stage = S.hist + kFBins;
+    const int tid = threadIdx.x;
+    // thread 0 keeps the next row's ticket and number between the stages
+    int nt = 0, nr = 0;
+    if (tid == 0) {
+        nt = (int)atomicAdd(P.ticket, 1u);
+        if (nt < P.local_batch) {
+            nr = P.row_order != nullptr ? P.row_order[nt] : nt;
+            f_prefetch_header(P, nr, s_pre);
+            cp_async_wait_all();
+        }
+        f_compose_header(P, nt, nr, s_pre, s_hdr[0]);
+    }
+    for (int cur = 0;; cur ^= 1) {
+        __syncthreads();
+        const FHdr& H = s_hdr[cur];
+        if (H.t >= P.local_batch) {
+            break;
+        }
+        const int  r   = H.r;
+        u64* const rec = P.trace != nullptr ? P.trace + (size_t)H.t * kTraceWords : nullptr;
+        if (tid == 0) {
+            if (rec != nullptr) {
+                rec[0] = (u64)r, rec[1] = (u64)blockIdx.x, rec[2] = global_timer_ns();
+                rec[4 + 25] = (u64)clock64();
+            }
+            nt = (int)atomicAdd(P.ticket, 1u);  // stage 0 of the next row's header
+        }
+        auto stage1 = [&]() {
+            if (tid == 0 && nt < P.local_batch) {
+                nr = P.row_order != nullptr ? P.row_order[nt] : nt;
+            }
+        };
+        auto stage2 = [&]() {
+            if (tid == 0 && nt < P.local_batch) {
+                f_prefetch_header(P, nr, s_pre);
+            }
+        };
+        bool       done   = false;
+        int* const id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
+        if (H.mode == 1 && !H.fin) {
+            const FGeo G  = f_geometry(P, r);
+            // (a penalty that can raise a value - repetition below 1, presence below 0 - would make columns
+            //  under the threshold candidates: those rows go to the general kernel)
+            const bool lowers = !P.apply_rep || (P.penalty_type == FTB200_PENALTY_MULTIPLICATIVE ? H.theta >= 1.0f :
+                                                 P.penalty_type == FTB200_PENALTY_ADDITIVE ? H.theta >= 0.0f : true);
+            const bool ok = lowers && G.nfull >= 2048 && G.nfull <= 65535 && H.inv_t > 0.0f && H.inv_t < 3.0e38f
+                            && (P.apply_rep ? P.step : 0) <= kFMaxHist
+                            && (P.bad_words != nullptr ? P.bad_words_len : 0) <= kFMaxWords;
+            if (ok) {
+                done = fast_topk_row<DT>(P, S, H, rec, stage1, stage2);
+                if (done && tid == 0) {
+                    curandState_t st = P.topk_states[r];
+                    (void)curand_uniform(&st);
+                    P.topk_states[r] = st;
+                }
+            }
+            else {
+                stage1();
+                stage2();
+            }
+        }
+        else {
+            stage1();
+            stage2();
+            if (H.mode == 0) {
+                done = true;
+            }
+            else if (H.mode == 1) {
+                // kernels/sampling_topk_kernels.cu:249-252: end id, no draw, length unchanged
+                if (tid == 0) {
+                    *id_out = H.end_id;
+                }
+                done = true;
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            if (rec != nullptr) {
+                rec[3] = global_timer_ns();
+                rec[4 + 26] = (u64)clock64();
+                rec[4 + 27] = done ? 1 : 0;
+            }
+            if (!done) {
+                P.redo_rows[atomicAdd(P.redo_count, 1u)] = r;
+            }
+            else if (P.topp_states != nullptr && P.topp_decay != nullptr) {
+                // top-p decay / reset (kernels/sampling_topp_kernels.cu:1381-1408), applied to every row of the call
+                const int id = *id_out;
+                float     p  = P.topp_ps[r];
+                if (id == P.topp_reset[r]) {
+                    p = P.topp_initial[r];
+                }
+                else {
+                    p = fmaxf(p * P.topp_decay[r], P.topp_min[r]);
+                }
+                P.topp_ps[r] = p;
+            }
+            // the next row's header: its arguments were sent for before this row's pass
+            cp_async_wait_all();
+            f_compose_header(P, nt, nr, s_pre, s_hdr[cur ^ 1]);
+        }
+    }
+}
+
+template<int DT>
+int fast_sampling_occupancy(size_t smem, int* per_sm)
+{
+    FTB_CUDA_CHECK(
+        cudaFuncSetAttribute(fast_sampling_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FTB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, fast_sampling_kernel<DT>, kThreads, smem));
+    return FTB200_OK;
+}
+
+template<int DT>
+int fast_sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st)
+{
+    fast_sampling_kernel<DT><<<grid, kThreads, smem, st>>>(K);
+    FTB_CUDA_CHECK(cudaGetLastError());
+    return FTB200_OK;
+}
+
+}  // namespace ftb200

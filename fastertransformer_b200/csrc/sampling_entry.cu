@@ -14,6 +14,15 @@ extern template int sampling_launch<FTB200_F32>(const KParams&, int, size_t, cud
 extern template int sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
 template<int DT>
+int fast_sampling_occupancy(size_t smem, int* per_sm);
+template<int DT>
+int fast_sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st);
+extern template int fast_sampling_occupancy<FTB200_F16>(size_t, int*);
+extern template int fast_sampling_occupancy<FTB200_BF16>(size_t, int*);
+extern template int fast_sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
+extern template int fast_sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
+size_t fast_smem_for(int hash_slots, int vocab_padded);
+template<int DT>
 int vp_merge_launch(const KParams& K, const u64* gathered, int nranks, int* overflow, int grid, cudaStream_t st);
 extern template int vp_merge_launch<FTB200_F32>(const KParams&, const u64*, int, int*, int, cudaStream_t);
 extern template int vp_merge_launch<FTB200_F16>(const KParams&, const u64*, int, int*, int, cudaStream_t);
@@ -42,6 +51,15 @@ static size_t scratch_stride_for(int vocab_padded)
     return ((size_t)vocab_padded + 255) / 256 * 256;
 }
 
+// Workspace: 256-byte header (row tickets, length of the row list), the list of rows the single-pass kernel
+// leaves to decode_sampling_kernel (one int per local row), then one candidate area per resident CTA.
+static size_t redo_list_bytes(int local_batch)
+{
+    return ((size_t)local_batch * sizeof(int) + 255) / 256 * 256;
+}
+
+static int g_fast_path = 1;  // see ftb200_set_single_pass
+
 }  // namespace ftb200
 
 using namespace ftb200;
@@ -56,7 +74,7 @@ extern "C" int ftb200_sampling_workspace_bytes(int dtype, int local_batch_size, 
     if ((size_t)local_batch_size < ctas) {
         ctas = (size_t)local_batch_size;
     }
-    *bytes = 256 + ctas * scratch_stride_for(vocab_size_padded) * sizeof(u64);
+    *bytes = 256 + redo_list_bytes(local_batch_size) + ctas * scratch_stride_for(vocab_size_padded) * sizeof(u64);
     return FTB200_OK;
 }
 
@@ -194,7 +212,10 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
         grid = p->local_batch_size;
     }
     K.ticket         = (u32*)p->workspace;
-    K.scratch        = (u64*)((char*)p->workspace + 256);
+    K.redo_count     = nullptr;
+    K.redo_rows      = nullptr;
+    K.row_count_dev  = nullptr;
+    K.scratch        = (u64*)((char*)p->workspace + 256 + redo_list_bytes(p->local_batch_size));
     K.scratch_stride = scratch_stride_for(p->vocab_size_padded);
     return FTB200_OK;
 }
@@ -220,6 +241,39 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
     }
     cudaStream_t st = (cudaStream_t)p->stream;
     FTB_CUDA_CHECK(cudaMemsetAsync(K.ticket, 0, 256, st));
+    // 16-bit logits without a bias, log-probs or timeline: the single-pass kernel serves the rows first and
+    // leaves a list of the rows it does not cover; decode_sampling_kernel then works that list off.
+    const bool single_pass = g_fast_path && p->dtype != FTB200_F32 && K.bias == nullptr && K.cum_log_probs == nullptr
+                             && K.out_log_probs == nullptr && p->vocab_size_padded <= (1 << 20)
+                             && p->vocab_size >= 16384 + 16;
+    if (single_pass) {
+        const size_t fsmem = fast_smem_for(K.hash_slots, p->vocab_size_padded);
+        int          fper  = 0;
+        rc = p->dtype == FTB200_F16 ? fast_sampling_occupancy<FTB200_F16>(fsmem, &fper) :
+                                      fast_sampling_occupancy<FTB200_BF16>(fsmem, &fper);
+        if (rc != FTB200_OK) {
+            return rc;
+        }
+        if (fper >= 1) {
+            KParams F    = K;
+            F.redo_count = K.ticket + 1;
+            F.redo_rows  = (int*)((char*)p->workspace + 256);
+            int fgrid    = sm_count() * fper;
+            fgrid        = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;
+            rc = p->dtype == FTB200_F16 ? fast_sampling_launch<FTB200_F16>(F, fgrid, fsmem, st) :
+                                          fast_sampling_launch<FTB200_BF16>(F, fgrid, fsmem, st);
+            if (rc != FTB200_OK) {
+                return rc;
+            }
+            note_launch(1);
+            K.ticket        = K.ticket + 2;
+            K.row_order     = F.redo_rows;
+            if (K.trace != nullptr) {
+                K.trace += (size_t)p->local_batch_size * 32;  // the general kernel's records follow the single-pass kernel's
+            }
+            K.row_count_dev = F.redo_count;
+        }
+    }
     switch (p->dtype) {
         case FTB200_F32: rc = sampling_launch<FTB200_F32>(K, grid, smem, st); break;
         case FTB200_F16: rc = sampling_launch<FTB200_F16>(K, grid, smem, st); break;
@@ -229,6 +283,12 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
         note_launch(1);
     }
     return rc;
+}
+
+extern "C" int ftb200_set_single_pass(int on)
+{
+    g_fast_path = on ? 1 : 0;
+    return FTB200_OK;
 }
 
 // ---- vocabulary-parallel sampling (the logits of a row are split over several GPUs by column) ------

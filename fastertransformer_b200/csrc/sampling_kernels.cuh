@@ -3934,6 +3934,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
         S.hitq  = (unsigned short*)(S.nhit + 4);
     }
     u64* gscratch = P.scratch + (size_t)blockIdx.x * P.scratch_stride;
+    // rows to serve: the whole local batch, or the list the single-pass kernel left behind
+    const int n_rows = P.row_count_dev != nullptr ? (int)*P.row_count_dev : P.local_batch;
     for (;;) {
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -3941,7 +3943,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_sampling_kernel(const __gr
         }
         __syncthreads();
         const int t = s_row;
-        if (t >= P.local_batch) {
+        if (t >= n_rows) {
             break;
         }
         // rows are handed out costliest first when the caller supplied an order (longest-processing-

@@ -55,6 +55,11 @@ struct KParams {
     int      vp_cap;
     int      vocab_offset;  // first token id of this shard of the vocabulary (0 when not sharded)
     u32*     ticket;
+    // Rows the single-pass kernel leaves to decode_sampling_kernel: it appends them to redo_rows and counts them
+    // in redo_count; decode_sampling_kernel launched with row_count_dev != null serves row_order[0 .. *row_count_dev).
+    u32*       redo_count;
+    int*       redo_rows;
+    const u32* row_count_dev;
     u64*     trace;           // optional per-row timeline: {row, CTA, start ns, end ns} per ticket, else null
     u64*     scratch;         // per-CTA candidate overflow area
     size_t   scratch_stride;  // u64 entries per CTA

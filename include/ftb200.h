@@ -174,6 +174,12 @@ int ftb200_last_launch_count(void);
  * call.  Pass null to switch the trace off (the default). */
 int ftb200_set_row_trace(uint64_t* device_buf);
 
+/* Diagnostic, no counterpart in the reference.  ftb200_decode_step_sampling serves 16-bit logits in two
+ * launches: a single-pass kernel (one read of each row, several rows in flight per SM) and then the general
+ * kernel on the rows the first one leaves behind.  ftb200_set_single_pass(0) sends every row to the general
+ * kernel (the results are the same either way; tests compare the two); 1 (the default) restores the pair. */
+int ftb200_set_single_pass(int on);
+
 /* ------------------------------------------------------------------------------------------
  * Bad-word ban as a stand-alone call (the fused step above already applies it; this entry serves
  * callers that use the kernel by itself, e.g. the beam-search path).  Writes -inf into the logits.
