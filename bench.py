@@ -165,6 +165,34 @@ def cpu_baseline(w, rows=64):
             "sample": "%d rows x 1 step of the same workload, %d repetitions, OpenMP over rows" % (rows, reps)}
 
 
+def workload_seed(wname, rank):
+    """Seed of the synthetic logits: the same for both arms, one stream per rank."""
+    return (1237 if wname == "c3" else 1234 + int(wname[1])) + rank
+
+
+def metric_name(wname, B, vocab):
+    if wname == "c3":
+        return "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256"
+    return "sampled tokens/sec and achieved HBM GB/s (config %s: batch %d, vocab %d)" % (wname[1], B, vocab)
+
+
+def workload_config(wname, B, vocab, first_step, K, n_buffers, world):
+    """The `config` object of the JSON line: identical for both arms on the same workload."""
+    label = {"c1": "c1: top-k 50, T 1.0, repetition 1.2, batch %d x vocab %d fp32",
+             "c2": "c2: top-p 0.9, T 0.8, presence 0.5, min_length 16, batch %d x vocab %d fp16",
+             "c3": "c3: mixed per-row top-k/top-p, batch %d x vocab %d bf16, repetition 1.1, "
+                   "8 bad words/row, length criterion"}[wname] % (B, vocab)
+    return {"workload": label, "rows_per_gpu": B, "history_tokens": "%d..%d" % (first_step, first_step + K),
+            "l2": "%d logits buffers rotate, every one larger than the 126 MB L2 or all of them together "
+                  "more than twice its size" % n_buffers,
+            "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU"}
+
+
+def n_buffers_for(B, vocab_padded, element_size):
+    # enough rotating buffers that a step never finds its logits in the 126 MB L2
+    return max(4, min(200, -(-300_000_000 // (B * vocab_padded * element_size))))
+
+
 def make_pool(w, device, dtype, n):
     pool = []
     for i in range(n):
@@ -181,15 +209,13 @@ def run_ours(a, rank, world, local):
     K, W = a.steps, a.warmup
     e2e_steps = min(K, 16)
     wname = a.workload if a.workload in ("c1", "c2") else "c3"
-    w = make_workload(wname, batch=a.batch, steps=W + K + e2e_steps + 40, seed=(1237 if wname == "c3" else 1234 + int(wname[1])) + rank)
+    w = make_workload(wname, batch=a.batch, steps=W + K + e2e_steps + 40, seed=workload_seed(wname, rank))
     B = w.batch
     layer = DynamicDecodeLayer(w.vocab, w.vocab_padded, w.dtype, device)
     layer.setup(B, 1, w.runtime_args)
     st = w.initial_state(device)
     inputs = w.static_inputs(device)
-    # enough rotating buffers that a step never finds its logits in the 126 MB L2
-    buf_bytes = B * w.vocab_padded * torch.empty(0, dtype=w.dtype).element_size()
-    N_BUFFERS = max(4, min(200, -(-300_000_000 // buf_bytes)))
+    N_BUFFERS = n_buffers_for(B, w.vocab_padded, torch.empty(0, dtype=w.dtype).element_size())
     pool = make_pool(w, device, w.dtype, N_BUFFERS)
     torch.cuda.synchronize()
 
@@ -279,8 +305,7 @@ def run_ours(a, rank, world, local):
     achieved = alg_bytes / (kern_ms_mean * 1e-3) / 1e9
     es = pool[0].element_size()
     line = {
-        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256" if wname == "c3"
-        else "sampled tokens/sec and achieved HBM GB/s (config %s: batch %d, vocab %d)" % (wname[1], B, w.vocab),
+        "metric": metric_name(wname, B, w.vocab),
         "value": world * B * K / (ms_total * 1e-3),
         "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W,
@@ -288,17 +313,13 @@ def run_ours(a, rank, world, local):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": {"c1": "fp32", "c2": "fp16 logits and probabilities", "c3": "bf16 logits, fp32 arithmetic"}[wname],
         "data": "synthetic",
-        "config": {"workload": {"c1": "c1: top-k 50, T 1.0, repetition 1.2, batch %d x vocab %d fp32",
-                                "c2": "c2: top-p 0.9, T 0.8, presence 0.5, min_length 16, batch %d x vocab %d fp16",
-                                "c3": "c3: mixed per-row top-k/top-p, batch %d x vocab %d bf16, repetition 1.1, "
-                                      "8 bad words/row, length criterion"}[wname] % (B, w.vocab),
-                   "rows_per_gpu": B, "history_tokens": "%d..%d" % (first_step, first_step + K),
-                   "l2": "%d logits buffers of %.1f MB rotate (%.0f MB in all, L2 is 126 MB)" % (
-                       N_BUFFERS, B * w.vocab_padded * es / 1e6, N_BUFFERS * B * w.vocab_padded * es / 1e6),
-                   "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU"},
+        "config": workload_config(wname, B, w.vocab, first_step, K, N_BUFFERS, world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": a.traffic if wname == "c3" and B == 1024 else None, "peak_kind": peak_kind,
-                     "kernel": "decode_sampling_kernel<%s>" % {"c1": "f32", "c2": "f16", "c3": "bf16"}[wname], "kernel_ms": kern_ms_mean,
+                     "kernel": ("decode_sampling_kernel<f32>" if wname == "c1" else
+                                "fused sampling step: fast_sampling_kernel<%s> (top-k rows) and (top-p rows) side by side, "
+                                "then decode_sampling_kernel on the rows they leave" % {"c2": "f16", "c3": "bf16"}[wname]),
+                     "kernel_ms": kern_ms_mean,
                      "algorithmic_bytes_per_launch": alg_bytes},
         "e2e": {"value": world * B * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": B * w.vocab_padded * es, "d2h_bytes_per_step": B * 4 + 4,
@@ -438,32 +459,34 @@ def run_vocab_parallel(a, rank, world, local):
 
 
 def run_reference(a, rank, world, local):
+    """The unmodified reference on the same workload: every rank runs its own batch (the rank's seed, as in the
+    other arm), value = all rows of all ranks / the slowest rank's time."""
     import ft_reference
     from fastertransformer_b200.workloads import make_workload
-    if rank != 0:
-        return None
     if not ft_reference.available():
         return {"impl": "reference", "unavailable": "oracle/_ref/libft_decode_ref.so is not built on this box"}
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     K, W = a.steps, a.warmup
     wname = a.workload if a.workload in ("c1", "c2") else "c3"
-    w = make_workload(wname, batch=a.batch, steps=W + K + 4)
+    w = make_workload(wname, batch=a.batch, steps=W + K + 4, seed=workload_seed(wname, rank))
     B = w.batch
     ref_dt = torch.float32 if w.dtype == torch.bfloat16 else w.dtype  # the reference has float and half only
     layer = ft_reference.RefDynamicDecodeLayer(w.vocab, w.vocab_padded, ref_dt, device)
     layer.setup(B, 1, w.runtime_args)
     st = w.initial_state(device)
     inputs = w.static_inputs(device)
-    pool = make_pool(w, device, ref_dt, 2)
+    n_buffers = n_buffers_for(B, w.vocab_padded, torch.empty(0, dtype=w.dtype).element_size())
+    pool = make_pool(w, device, ref_dt, min(n_buffers, 4))
     work = torch.empty_like(pool[0])
     sampler = ClockSampler(local, period=0.02)
     total_ms, n = 0.0, 0
+    barrier(world)
     for i in range(W + K):
         if i == W:
             sampler.start()
         step = w.max_input_length + i
-        work.copy_(pool[i % 2])  # the reference overwrites its logits; a model would produce fresh ones
+        work.copy_(pool[i % len(pool)])  # the reference overwrites its logits; a model would produce fresh ones
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -474,19 +497,18 @@ def run_reference(a, rank, world, local):
             total_ms += e0.elapsed_time(e1)
             n += 1
     clocks = sampler.stop()
-    val = B * n / (total_ms * 1e-3)
+    total_ms = max_over_ranks(total_ms, world, device)
+    val = world * B * n / (total_ms * 1e-3)
     return {
         "impl": "reference",
-        "metric": "sampled tokens/sec and achieved HBM GB/s (% of roofline) at batch 1024, vocab 128256" if wname == "c3"
-        else "sampled tokens/sec and achieved HBM GB/s (config %s: batch %d, vocab %d)" % (wname[1], B, w.vocab),
-        "value": val, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": total_ms / n,
+        "metric": metric_name(wname, B, w.vocab),
+        "value": val, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": total_ms / n,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp32 (up-cast of the bf16 logits; the reference has no bf16 path)" if wname == "c3"
         else str(ref_dt).replace("torch.", ""), "data": "synthetic",
-        "config": {"workload": wname + " as above" if wname != "c3" else "c3: mixed per-row top-k/top-p, batch %d x vocab %d, repetition 1.1, "
-                               "8 bad words/row, length criterion" % (B, w.vocab),
-                   "what": "unmodified FasterTransformer DynamicDecodeLayer<float> compiled for sm_100a "
-                           "(oracle/_ref), logits resident in HBM, CUDA events around each forward()"},
+        "config": workload_config(wname, B, w.vocab, w.max_input_length + W, K, n_buffers, world),
+        "reference": "unmodified FasterTransformer DynamicDecodeLayer compiled for sm_100a (oracle/_ref), logits "
+                     "resident in HBM, CUDA events around each forward(), every rank its own batch",
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference",
                          "sample": "the reference's own CUDA kernels on the GPU, full batch, %d steps" % n},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -23,12 +23,15 @@
 
 namespace ftb200 {
 
-constexpr int kFCap      = 4096;  // candidate columns held in shared memory
+constexpr int kFCap      = 3840;  // candidate columns held in shared memory
 constexpr int kFBins     = 2048;  // value classes (bit patterns) above the threshold
 constexpr int kFSpecCap  = 128;   // listed columns (special or edge) at or above the threshold
 constexpr int kFClsCap   = 768;   // members of the class the draw lands in
 constexpr int kFRuns     = 1536;  // runs the draw may walk (classes + listed columns among the first k)
-constexpr int kFRunBytes = kFRuns * 8 + kFBins * 2;
+constexpr int kFRunBytes = kFRuns * 6 + kFBins * 2;  // top-k draw: value, count per run; class ranks
+constexpr int kFPRuns    = 1792;  // top-p: runs of the replayed scan (probability, first position)
+constexpr int kFPSpecCap = 1024;  // top-p: listed columns above the cut
+constexpr int kFPClsCap  = 2048;  // top-p: members of the class the scan stops in
 constexpr int kFSampleV  = 2;     // sampled vectors per thread (4096 columns per row)
 constexpr int kFUnroll   = 8;     // 16-byte loads in flight per thread
 
@@ -41,21 +44,26 @@ struct FMap {
     u32*            sval;  // [hash_slots] gathered raw word, then the final value of that column (float bits)
     u32*            hist;  // [kFBins]   columns per value class above the threshold
     u32*            stage; // [kFStageBytes / 4] token history, word list and last tokens of the row, as fetched
+    uint4*          wbuf;  // [kWarps * kFRing] vectors parked during a pass (static shared memory of the kernel)
+    unsigned short* wj;    // [kWarps * kFRing]
 };
 
 constexpr int kFMaxHist    = 1024;  // token-history entries the single-pass kernel stages
 constexpr int kFMaxWords   = 128;   // bad-word list length it stages
-constexpr int kFStageBytes = (kFMaxHist + 2 * kFMaxWords + 4) * 4;
+constexpr int kFStageBytes = 8192;  // >= (kFMaxHist + 2 * kFMaxWords + 4) * 4; later kFPSpecCap listed columns of a top-p row
 // bytes of the per-vector mask area: one byte per aligned vector, and room for what follows the pass
 __host__ __device__ inline size_t fast_mask_bytes(int vocab_padded)
 {
     const size_t need = ((size_t)vocab_padded / 8 + 16 + 15) / 16 * 16;
-    const size_t post = (size_t)kFSpecCap * 8 + (size_t)kFRunBytes;
+    size_t post = (size_t)kFSpecCap * 8 + (size_t)kFRunBytes;
+    post        = post > (size_t)kFPRuns * 8 ? post : (size_t)kFPRuns * 8;
+    post        = post > (size_t)kFPClsCap * 4 ? post : (size_t)kFPClsCap * 4;
     return need > post ? need : post;
 }
-__host__ __device__ inline size_t fast_smem_bytes(int hash_slots, int vocab_padded)
+__host__ __device__ inline size_t fast_smem_bytes(int hash_slots, int vocab_padded, bool /*topp*/)
 {
-    return (size_t)kFCap * 4 + fast_mask_bytes(vocab_padded) + (size_t)hash_slots * 8 + (size_t)kFBins * 4
+    const size_t sv = hash_slots > kFBins ? hash_slots : kFBins;  // the value area doubles as a class table
+    return (size_t)kFCap * 4 + fast_mask_bytes(vocab_padded) + (size_t)hash_slots * 4 + sv * 4 + (size_t)kFBins * 4
            + (size_t)kFStageBytes;
 }
 
@@ -148,32 +156,51 @@ struct FSink {
     const unsigned char* emask;  // per aligned vector: bit e set = column e of the vector is special
     u32*                 ncand;
     u32*                 bad;    // set when a relative key does not fit the class table
-    int                  shift, mask;
+    uint4*               wbuf;   // [kWarps][kFRing] vectors parked by the lanes of a warp
+    unsigned short*      wj;     // [kWarps][kFRing] their vector indices
+    int                  shift, mask, cap;
 };
 
-// One dense step of the side path: every lane below `n` takes one parked vector of its warp, finds the columns at
-// or above the threshold from the packed compares, leaves the raw values of special ones next to their hash
-// slots and turns the others into candidates (one reservation in the candidate list per step and warp).
-template<int DT>
-__device__ __forceinline__ void f_side_step(const uint4& v, int jj, bool live, int head, u32 thr_key, u32 thr2,
+// One dense step of the side path: every live lane takes one parked vector of its warp, finds the columns at or
+// above the threshold from the packed compares, leaves the raw values of special ones next to their hash slots
+// and turns the others into candidates (one reservation in the candidate list per step and warp).
+// BAND: the columns whose raw value lies in [thr_key, hi_key] are listed by column only (special ones left out).
+template<int DT, bool BAND>
+__device__ __forceinline__ void f_side_step(const uint4& v, int jj, bool live, int head, u32 thr_key, u32 thr2, u32 hi2,
                                             const FSink& K, u32& relmax)
 {
     const int lane = threadIdx.x & 31;
     u32       pm   = 0;
     if (live) {
-        const u32 m0 = ge2_mask<DT>(v.x, thr2), m1 = ge2_mask<DT>(v.y, thr2);
-        const u32 m2 = ge2_mask<DT>(v.z, thr2), m3 = ge2_mask<DT>(v.w, thr2);
+        u32 m0 = ge2_mask<DT>(v.x, thr2), m1 = ge2_mask<DT>(v.y, thr2);
+        u32 m2 = ge2_mask<DT>(v.z, thr2), m3 = ge2_mask<DT>(v.w, thr2);
+        if (BAND) {
+            m0 &= le2_mask<DT>(v.x, hi2), m1 &= le2_mask<DT>(v.y, hi2);
+            m2 &= le2_mask<DT>(v.z, hi2), m3 &= le2_mask<DT>(v.w, hi2);
+        }
         pm = ((m0 & 1u) | ((m0 >> 15) & 2u)) | (((m1 & 1u) | ((m1 >> 15) & 2u)) << 2)
              | (((m2 & 1u) | ((m2 >> 15) & 2u)) << 4) | (((m3 & 1u) | ((m3 >> 15) & 2u)) << 6);
-        const u32 em = K.emask[jj];
-        u32       sp = pm & em;
-        pm &= ~em;
-        while (sp != 0) {  // rare: a special column at or above the threshold
-            const int e = __ffs(sp) - 1;
-            sp &= sp - 1;
-            const int slot = f_hash_find(K.hash, K.shift, K.mask, head + jj * 8 + e);
-            if (slot >= 0) {
-                K.sval[slot] = raw_bits<DT>(v, e);
+        if (BAND) {
+            u32 t = pm;
+            while (t != 0) {
+                const int e = __ffs(t) - 1;
+                t &= t - 1;
+                if (hash_lookup_raw(K.hash, K.shift, K.mask, head + jj * 8 + e) != 0) {
+                    pm &= ~(1u << e);
+                }
+            }
+        }
+        else {
+            const u32 em = K.emask[jj];
+            u32       sp = pm & em;
+            pm &= ~em;
+            while (sp != 0) {  // rare: a special column at or above the threshold
+                const int e = __ffs(sp) - 1;
+                sp &= sp - 1;
+                const int slot = f_hash_find(K.hash, K.shift, K.mask, head + jj * 8 + e);
+                if (slot >= 0) {
+                    K.sval[slot] = raw_bits<DT>(v, e);
+                }
             }
         }
     }
@@ -197,16 +224,23 @@ __device__ __forceinline__ void f_side_step(const uint4& v, int jj, bool live, i
     while (pm != 0) {
         const int e = __ffs(pm) - 1;
         pm &= pm - 1;
-        const u32 rel = key16(raw_bits<DT>(v, e)) - thr_key;
-        if (rel >= (u32)kFBins) {
-            *K.bad = 1;  // (the slot stays unwritten: the row is given up)
+        if (BAND) {
+            if (pos < (u32)K.cap) {
+                K.cand[pos] = (u32)(head + jj * 8 + e);
+            }
         }
         else {
-            relmax = rel > relmax ? rel : relmax;
-            if (pos < (u32)kFCap) {
-                K.cand[pos] = (rel << 20) | (u32)(head + jj * 8 + e);
+            const u32 rel = key16(raw_bits<DT>(v, e)) - thr_key;
+            if (rel >= (u32)kFBins) {
+                *K.bad = 1;  // (the slot stays unwritten: the row is given up)
             }
-            smem_add(&K.hist[rel], 1u);
+            else {
+                relmax = rel > relmax ? rel : relmax;
+                if (pos < (u32)K.cap) {
+                    K.cand[pos] = (rel << 20) | (u32)(head + jj * 8 + e);
+                }
+                smem_add(&K.hist[rel], 1u);
+            }
         }
         ++pos;
     }
@@ -217,41 +251,52 @@ __device__ __forceinline__ void f_side_step(const uint4& v, int jj, bool live, i
 // a lane does not look at its own hit: it parks the vector in a small ring of its warp, and whenever 32
 // vectors are parked the warp takes them one per lane (f_side_step).  Nothing of the row is read a second time.
 constexpr int kFRing = 64;  // parked vectors per warp
-template<int DT>
-__device__ __noinline__ void f_stream(const uint4* vp, int nfull, int head, u32 thr_key, const FSink K, u32* relmax_out)
+template<int DT, bool BAND, int UNROLL>
+__device__ __noinline__ void f_stream(const uint4* vp, int nfull, int head, u32 thr_key, u32 hi_key, const FSink& Ks,
+                                      u32* relmax_out)
 {
-    __shared__ uint4          s_wbuf[kWarps][kFRing];
-    __shared__ unsigned short s_wj[kWarps][kFRing];
+    const FSink K = Ks;  // (a copy in registers)
     FTB_ASSUME_SHARED(K.cand);
     FTB_ASSUME_SHARED(K.hist);
     FTB_ASSUME_SHARED(K.sval);
     FTB_ASSUME_SHARED(K.emask);
     FTB_ASSUME_SHARED(K.ncand);
     FTB_ASSUME_SHARED(K.bad);
+    FTB_ASSUME_SHARED(K.wbuf);
+    FTB_ASSUME_SHARED(K.wj);
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const u32 thr_raw = key16_inv(thr_key);
-    const u32 thr2    = thr_raw | (thr_raw << 16);
-    uint4* const          wbuf = s_wbuf[wid];
-    unsigned short* const wj   = s_wj[wid];
+    const u32 thr_raw = key16_inv(thr_key), hi_raw = key16_inv(hi_key);
+    const u32 thr2 = thr_raw | (thr_raw << 16), hi2 = hi_raw | (hi_raw << 16);
+    uint4* const          wbuf = K.wbuf + wid * kFRing;
+    unsigned short* const wj   = K.wj + wid * kFRing;
     int  rd = 0, cnt = 0;  // ring read position and fill (the same in every lane)
     u32  relmax = 0;
-    for (int jb = 0; jb < nfull; jb += kThreads * kFUnroll) {
-        uint4 q[kFUnroll];
+    for (int jb = 0; jb < nfull; jb += kThreads * UNROLL) {
+        uint4 q[UNROLL];
 #pragma unroll
-        for (int u = 0; u < kFUnroll; ++u) {
+        for (int u = 0; u < UNROLL; ++u) {
             const int j = jb + u * kThreads + tid;
             if (j < nfull) {
                 q[u] = ld_nc_v4(vp + j);
             }
         }
 #pragma unroll
-        for (int u = 0; u < kFUnroll; ++u) {
+        for (int u = 0; u < UNROLL; ++u) {
             const int j   = jb + u * kThreads + tid;
             bool      hit = false;
             if (j < nfull) {
-                const u32 m = (ge2_mask<DT>(q[u].x, thr2) | ge2_mask<DT>(q[u].y, thr2))
-                              | (ge2_mask<DT>(q[u].z, thr2) | ge2_mask<DT>(q[u].w, thr2));
-                hit         = m != 0;
+                u32 m;
+                if (BAND) {
+                    m = ((ge2_mask<DT>(q[u].x, thr2) & le2_mask<DT>(q[u].x, hi2))
+                         | (ge2_mask<DT>(q[u].y, thr2) & le2_mask<DT>(q[u].y, hi2)))
+                        | ((ge2_mask<DT>(q[u].z, thr2) & le2_mask<DT>(q[u].z, hi2))
+                           | (ge2_mask<DT>(q[u].w, thr2) & le2_mask<DT>(q[u].w, hi2)));
+                }
+                else {
+                    m = (ge2_mask<DT>(q[u].x, thr2) | ge2_mask<DT>(q[u].y, thr2))
+                        | (ge2_mask<DT>(q[u].z, thr2) | ge2_mask<DT>(q[u].w, thr2));
+                }
+                hit = m != 0;
             }
             const u32 hits = __ballot_sync(0xffffffffu, hit);
             if (hits == 0) {
@@ -266,7 +311,7 @@ __device__ __noinline__ void f_stream(const uint4* vp, int nfull, int head, u32 
             if (cnt >= 32) {
                 __syncwarp();
                 const int at = (rd + lane) & (kFRing - 1);
-                f_side_step<DT>(wbuf[at], (int)wj[at], true, head, thr_key, thr2, K, relmax);
+                f_side_step<DT, BAND>(wbuf[at], (int)wj[at], true, head, thr_key, thr2, hi2, K, relmax);
                 rd = (rd + 32) & (kFRing - 1);
                 cnt -= 32;
                 __syncwarp();
@@ -283,18 +328,20 @@ __device__ __noinline__ void f_stream(const uint4* vp, int nfull, int head, u32 
             v  = wbuf[at];
             jj = (int)wj[at];
         }
-        f_side_step<DT>(v, jj, live, head, thr_key, thr2, K, relmax);
+        f_side_step<DT, BAND>(v, jj, live, head, thr_key, thr2, hi2, K, relmax);
     }
-    relmax = __reduce_max_sync(0xffffffffu, relmax);
-    if (lane == 0 && relmax != 0) {
-        atomicMax(relmax_out, relmax);
+    if (!BAND) {
+        relmax = __reduce_max_sync(0xffffffffu, relmax);
+        if (lane == 0 && relmax != 0) {
+            atomicMax(relmax_out, relmax);
+        }
     }
 }
 
 // The `want`-th largest of the CTA's per-thread sample maxima (ordered 16-bit keys in smax[kThreads]), by
 // bisection inside one warp.  With `want` far below the number of threads it is, to within a few ranks, the
 // `want`-th largest of all sampled columns - on the low side, which only lets a few more candidates through.
-__device__ __forceinline__ u32 f_select_from_maxima(const unsigned short* smax, u32 want)
+__device__ __forceinline__ u32 f_select_from_maxima(const unsigned short* smax, u32 want, u32* largest)
 {
     FTB_ASSUME_SHARED(smax);
     const int lane = threadIdx.x & 31;
@@ -302,6 +349,14 @@ __device__ __forceinline__ u32 f_select_from_maxima(const unsigned short* smax, 
 #pragma unroll
     for (int i = 0; i < kThreads / 32; ++i) {
         mine[i] = smax[i * 32 + lane];
+    }
+    {
+        u32 mx = 0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) {
+            mx = mine[i] > mx ? mine[i] : mx;
+        }
+        *largest = __reduce_max_sync(0xffffffffu, mx);
     }
     u32 lo = 0, hi = 0xffffu;
 #pragma unroll 1
@@ -487,13 +542,942 @@ __device__ __forceinline__ FGeo f_geometry(const KParams& P, int r)
 }
 
 
-// One row of the top-k layer.  Returns true when the row is done, false when it has to go to the list
+// ---- top-p rows ------------------------------------------------------------------------------------------
+// After the pass a top-p row knows every column at or above the threshold (candidates, class counts, listed
+// columns) and with them the row maximum.  What the reference does next, on probabilities
+// (kernels/sampling_topp_kernels.cu:1294-1345 soft-max, :801-860 arg-max shortcut, :877-1004 sorted scan):
+//   pass 2 (the row again, mostly from L2): the soft-max denominator in the reference's order - thread t owns
+//     the "virtual threads" 4t..4t+3 (column mod 1024) and adds four exponentials per 1024-column chunk, strictly
+//     in chunk order; special columns take their final value (the per-vector bytes say where they are).  The
+//     same pass counts the bit patterns between a provisional cut and the threshold and lists the special
+//     columns that fall there, so that the sorted probability sequence is known as (probability, count) runs
+//     down to the cut;
+//   the block scan of topp_sampling is replayed over the runs (cub::BlockScan<float,256> raking order: 32
+//     segments of 8, Kogge-Stone over the segment totals, running prefix chunk by chunk);
+//   the class (bit patterns of equal probability) that holds the crossing gives the id: its J-th column in
+//     column order, from the candidate list or - below the threshold - from one filtered pass over the row.
+// Whatever does not fit (crossing below the cut, tables too small) sends the row to the general kernel.
+
+constexpr int kFMassBins = 128;  // sample mass per 16 bit patterns below the threshold
+
+struct FTopp {
+    u32   thr_key, relmax;
+    int   n_ord, n_sp;
+    float thr_y, neg_max, maxv;
+};
+
+template<int DT>
+__device__ __forceinline__ float f_round_T(float x)
+{
+    return DT == FTB200_F16 ? __half2float(__float2half_rn(x)) : x;
+}
+
+static __device__ float f_block_sum(float v, float* s_w)
+{
+    for (int m = 16; m > 0; m >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, m);
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+        s_w[threadIdx.x >> 5] = v;
+    }
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < kWarps; ++i) {
+        t += s_w[i];
+    }
+    return t;
+}
+
+// ---- shared memory by 32-bit address (the hot loop of pass 2 keeps no generic pointer) ----
+// (not volatile and without a memory clobber: the compiler may move and batch these reads - they are used on
+//  tables that nobody writes while the loop around them runs)
+__device__ __forceinline__ u32 lds_u8(u32 addr)
+{
+    u32 v;
+    asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// The same under a predicate inside the instruction (no branch around it: a run of these stays one basic block).
+__device__ __forceinline__ void reds_inc_if(u32 addr, u32 cond)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t@p red.shared.add.u32 [%0], 1;\n\t}" ::"r"(addr), "r"(cond));
+}
+// Counter update whose result nobody in the surrounding loop reads: no memory clobber, so the arithmetic of
+// neighbouring columns is free to move across it.
+__device__ __forceinline__ void reds_add_free(u32 addr, u32 v)
+{
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(v));
+}
+__device__ __forceinline__ uint2 lds_v2(u32 addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void cp_async8(u32 saddr, const void* g)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(g) : "memory");
+}
+template<int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ u32 atoms_add(u32 addr, u32 v)
+{
+    u32 old;
+    asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void sts_u64(u32 addr, u64 v)
+{
+    asm volatile("st.shared.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ void sts_f32(u32 addr, float v)
+{
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// flags of column `id` in the hash at shared address `hash` (0 when it has no entry)
+__device__ __forceinline__ u32 f_lookup_saddr(u32 hash, int shift, int mask, int id)
+{
+    u32 h = hash_slot(id, shift);
+    for (int probe = 0; probe <= mask; ++probe) {
+        const u32 v = lds_u32(hash + 4u * h);
+        if (v == kHashEmpty) {
+            return 0;
+        }
+        if ((v >> 2) == (u32)id) {
+            return v & 3u;
+        }
+        h = (h + 1) & mask;
+    }
+    return 0;
+}
+
+// Scalars of pass 2 (one argument block, by value: it travels in the parameter space of the call).
+struct FPass2 {
+    const char* rowp;
+    int         nch, vocab, shift, mask, apply_rep, penalty_type;
+    float       maxv, inv_t, theta, cut_y, thr_y, neg_max;
+    u32         thr_key, lo_n;
+    u32         emask, hash, hlo, spec, nspec, out;  // shared-memory addresses
+    __half      inv_t_h;
+};
+
+// Pass 2 of a top-p row over the whole 1024-column chunks [0, nch) and the ragged rest up to `vocab`: thread t
+// adds the exponentials of its four "virtual threads" chunk by chunk; with COUNTING the ordinary columns whose bit
+// pattern lies in the lo_n patterns below the threshold are counted; special columns take their final value and
+// are listed when it falls between the cut and the threshold.  The four sums go to out[4t .. 4t+3].
+template<int DT, bool TEMP, bool COUNTING>
+__device__ __noinline__ void f_pass2(const FPass2 A)
+{
+    const int    tid = threadIdx.x;
+    const float  maxv = A.maxv, inv_t = A.inv_t;
+    const __half inv_t_h = A.inv_t_h;
+    const u32    thr_key = A.thr_key, lo_n = A.lo_n, hlo = A.hlo;
+    float        a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    // final value of a special column (kernels/sampling_penalty_kernels.cu:367-424, :485-500; a dead one is -inf)
+    auto special = [&](float y, u32 fl) {
+        if (fl & kFlagDead) {
+            return -INFINITY;
+        }
+        if ((fl & kFlagHist) && A.apply_rep) {
+            if (A.penalty_type == FTB200_PENALTY_MULTIPLICATIVE) {
+                y = y < 0.0f ? y * A.theta : y / A.theta;
+            }
+            else if (A.penalty_type == FTB200_PENALTY_ADDITIVE) {
+                y = y - A.theta;
+            }
+            if (DT == FTB200_F16) {
+                y = __half2float(__float2half_rn(y));
+            }
+        }
+        return y;
+    };
+    auto patch = [&](float y, int v) {  // rare: column v is special
+        const float yy = special(y, f_lookup_saddr(A.hash, A.shift, A.mask, v));
+        if (yy >= A.cut_y && !(yy >= A.thr_y) && yy > A.neg_max) {  // (those at or above the threshold are listed already)
+            const u32 pos = atoms_add(A.nspec, 1u);
+            if (pos < (u32)kFPSpecCap) {
+                sts_u64(A.spec + 8u * pos, ((u64)(~fkey(yy)) << 32) | (u32)v);
+            }
+        }
+        return yy;
+    };
+    // A batch of UN chunks is worked on in stages, every stage over all 4 * UN columns of the thread: values,
+    // final values of the special ones (rare), exponentials, the four running sums in chunk order, counts.  The
+    // columns of a stage are independent of one another, so a warp has many instructions to issue between two
+    // dependent ones.
+    constexpr int UN     = 4;  // (larger batches run slower: the loop body then no longer sits in the instruction cache)
+    const char*   base   = A.rowp + (size_t)tid * 8;
+    const u32     embase = A.emask + (u32)(tid >> 1);
+    const int     nch    = A.nch;
+    const int     nib    = 4 * (tid & 1);
+    // (threshold and cut both at or above +0: see the counting stage)
+    const bool    pos_cut = thr_key - lo_n >= 0x8000u && thr_key > 0x8000u;
+    const u32     thr_m1  = (thr_key & 0x7fffu) - 1u;
+    for (int m0 = 0; m0 < nch; m0 += UN) {
+        uint2 raw[UN];
+        u32   em[UN];
+        float y[UN][4];
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            const bool in = m0 + uu < nch;
+            raw[uu]       = in ? ld_nc_v2(base + (size_t)(m0 + uu) * 2048) : make_uint2(0u, 0u);
+            em[uu]        = in ? (lds_u8(embase + (u32)(m0 + uu) * 128u) >> nib) & 0xfu : 0u;
+        }
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            y[uu][0] = f_value<DT>(raw[uu].x & 0xffffu, TEMP, inv_t, inv_t_h);
+            y[uu][1] = f_value<DT>(raw[uu].x >> 16, TEMP, inv_t, inv_t_h);
+            y[uu][2] = f_value<DT>(raw[uu].y & 0xffffu, TEMP, inv_t, inv_t_h);
+            y[uu][3] = f_value<DT>(raw[uu].y >> 16, TEMP, inv_t, inv_t_h);
+        }
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            if (em[uu] != 0) {  // rare
+                const int v0 = (m0 + uu) * 1024 + 4 * tid;
+                if (em[uu] & 1u) {
+                    y[uu][0] = patch(y[uu][0], v0);
+                }
+                if (em[uu] & 2u) {
+                    y[uu][1] = patch(y[uu][1], v0 + 1);
+                }
+                if (em[uu] & 4u) {
+                    y[uu][2] = patch(y[uu][2], v0 + 2);
+                }
+                if (em[uu] & 8u) {
+                    y[uu][3] = patch(y[uu][3], v0 + 3);
+                }
+            }
+        }
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            // a column at or below -MAX adds exactly zero, as in the reference's loop; the chunks past the end of
+            // the row are left out below
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                y[uu][e] = f_round_T<DT>(__expf(y[uu][e] - maxv));
+            }
+        }
+#pragma unroll
+        for (int uu = 0; uu < UN; ++uu) {
+            if (m0 + uu < nch) {
+                a0 += y[uu][0], a1 += y[uu][1], a2 += y[uu][2], a3 += y[uu][3];
+            }
+        }
+        if (COUNTING) {
+            // Ordinary columns between the cut and the threshold, per bit pattern.  With the cut at or above +0 (the
+            // usual case) the index below the threshold is a plain difference of the raw patterns: a negative
+            // value, or one at or above the threshold, wraps to a huge index.
+            if (pos_cut) {
+#pragma unroll
+                for (int uu = 0; uu < UN; ++uu) {
+                    if (m0 + uu < nch) {
+                        const u32 i0 = thr_m1 - (raw[uu].x & 0xffffu), i1 = thr_m1 - (raw[uu].x >> 16);
+                        const u32 i2 = thr_m1 - (raw[uu].y & 0xffffu), i3 = thr_m1 - (raw[uu].y >> 16);
+                        const u32 ok = ~em[uu];
+                        reds_inc_if(hlo + 4u * (i0 < lo_n ? i0 : 0u), (i0 < lo_n ? 1u : 0u) & ok);
+                        reds_inc_if(hlo + 4u * (i1 < lo_n ? i1 : 0u), (i1 < lo_n ? 2u : 0u) & ok);
+                        reds_inc_if(hlo + 4u * (i2 < lo_n ? i2 : 0u), (i2 < lo_n ? 4u : 0u) & ok);
+                        reds_inc_if(hlo + 4u * (i3 < lo_n ? i3 : 0u), (i3 < lo_n ? 8u : 0u) & ok);
+                    }
+                }
+            }
+            else {
+#pragma unroll
+                for (int uu = 0; uu < UN; ++uu) {
+                    if (m0 + uu < nch) {
+                        const u32 i0 = thr_key - 1u - key16(raw[uu].x & 0xffffu), i1 = thr_key - 1u - key16(raw[uu].x >> 16);
+                        const u32 i2 = thr_key - 1u - key16(raw[uu].y & 0xffffu), i3 = thr_key - 1u - key16(raw[uu].y >> 16);
+                        if (i0 < lo_n && !(em[uu] & 1u)) {
+                            reds_add_free(hlo + 4u * i0, 1u);
+                        }
+                        if (i1 < lo_n && !(em[uu] & 2u)) {
+                            reds_add_free(hlo + 4u * i1, 1u);
+                        }
+                        if (i2 < lo_n && !(em[uu] & 4u)) {
+                            reds_add_free(hlo + 4u * i2, 1u);
+                        }
+                        if (i3 < lo_n && !(em[uu] & 8u)) {
+                            reds_add_free(hlo + 4u * i3, 1u);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // the ragged rest of the row: columns nch * 1024 .. vocab - 1 (padding columns add nothing)
+    {
+        const int v0 = nch * 1024 + 4 * tid;
+        if (v0 < A.vocab) {
+            const unsigned short* row16 = (const unsigned short*)A.rowp;
+            for (int e = 0; e < 4 && v0 + e < A.vocab; ++e) {
+                const u32 r  = (u32)__ldg(row16 + v0 + e);
+                const u32 fl = f_lookup_saddr(A.hash, A.shift, A.mask, v0 + e);
+                float     yy = f_value<DT>(r, TEMP, inv_t, inv_t_h);
+                if (fl != 0) {
+                    yy = patch(yy, v0 + e);
+                }
+                const float ex = f_round_T<DT>(__expf(yy - maxv));
+                a0 += e == 0 ? ex : 0.0f, a1 += e == 1 ? ex : 0.0f, a2 += e == 2 ? ex : 0.0f, a3 += e == 3 ? ex : 0.0f;
+                if (COUNTING && fl == 0) {
+                    const u32 i0 = thr_key - 1u - key16(r);
+                    if (i0 < lo_n) {
+                        reds_add_free(hlo + 4u * i0, 1u);
+                    }
+                }
+            }
+        }
+    }
+    sts_f32(A.out + 16u * (u32)tid, a0);
+    sts_f32(A.out + 16u * (u32)tid + 4u, a1);
+    sts_f32(A.out + 16u * (u32)tid + 8u, a2);
+    sts_f32(A.out + 16u * (u32)tid + 12u, a3);
+}
+
+// Everything of a top-p row after the pass and the listed columns.  Returns true when the row is done.
+template<int DT>
+__device__ __forceinline__ bool fast_topp_tail(const KParams& P, const FMap& S, const FHdr& H, const FGeo& G, const FTopp T, u64* spec,
+                               u32* s_nspec, const u32* s_mass, float mass_tail, u32 smax_key, u64* trace)
+{
+    __shared__ float s_w[kWarps], s_den, s_R;
+    __shared__ u32   s_cut, s_wsum[kWarps], s_ncls, s_fail;
+    __shared__ int   s_c1, s_sel, s_imin, s_imax, s_first;
+    const int        tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const bool       temp = P.apply_temp != 0;
+    u32* const       hist = S.hist;
+    u32* const       hlo  = S.sval;
+    u32* const       cand = S.cand;
+    FTB_ASSUME_SHARED(hist);
+    FTB_ASSUME_SHARED(hlo);
+    FTB_ASSUME_SHARED(cand);
+    FTB_ASSUME_SHARED(spec);
+    const u32   thr_key = T.thr_key;
+    const float maxv = T.maxv, neg_max = T.neg_max;
+    const int   nfull = G.nfull;
+    auto value_of = [&](u32 key) { return f_value<DT>(key16_inv(key), temp, H.inv_t, H.inv_t_h); };
+
+    // ---- provisional cut: how far below the threshold the bit patterns have to be counted ----
+    // Mass (sum of exp(value - maximum)) at or above the threshold is known exactly; below it the sampled columns
+    // give an estimate per 16 bit patterns.  The cut is placed where the estimated cumulative share passes
+    // 1.25 u p + 0.03 - generous: counting a few more patterns costs little, a cut that proves too high costs
+    // the row a trip through the general kernel.
+    float mhi = 0.0f;
+    for (int b = tid; b <= (int)T.relmax; b += kThreads) {
+        const u32 c = hist[b];
+        if (c != 0) {
+            mhi += (float)c * __expf(value_of(thr_key + (u32)b) - maxv);
+        }
+    }
+    for (int i = tid; i < T.n_sp; i += kThreads) {
+        mhi += __expf(fkey_inv(~(u32)(spec[i] >> 32)) - maxv);
+    }
+    mhi = f_block_sum(mhi, s_w);
+    if (tid == 0) {
+        const float scale  = __expf(value_of(smax_key) - maxv) * ((float)(nfull * 8) / (float)(kThreads * 8));
+        float       lo_all = mass_tail;
+        for (int b = 0; b < kFMassBins; ++b) {
+            lo_all += (float)s_mass[b] * (1.0f / 1048576.0f);
+        }
+        const float d_est  = mhi + scale * lo_all;
+        float       share  = 1.25f * H.u * H.top_p + 0.03f;
+        const float target = share * d_est;
+        u32         cut    = thr_key;
+        if (mhi < target) {
+            float acc = mhi;
+            int   b   = 0;
+            for (; b < kFMassBins; ++b) {
+                acc += scale * (float)s_mass[b] * (1.0f / 1048576.0f);
+                if (acc >= target) {
+                    break;
+                }
+            }
+            const u32 down = 16u * (u32)(b + 2);
+            cut            = thr_key > down ? thr_key - down : 1u;
+            if (thr_key - cut > (u32)kFBins) {
+                cut = thr_key - (u32)kFBins;
+            }
+        }
+        s_cut  = cut;
+        s_fail = 0;
+    }
+    for (int i = tid; i < kFBins; i += kThreads) {
+        hlo[i] = 0;  // (the raw values of the special columns are done with: the listed ones carry their final value)
+    }
+    __syncthreads();
+    const u32   cut_key = s_cut;
+    const float cut_y   = cut_key < thr_key ? value_of(cut_key) : T.thr_y;
+    trace_mark(trace, 6);
+
+    // ---- pass 2 ----
+    float* const s_vt = (float*)S.wbuf;  // [1024] per-virtual-thread sums (the ring of the pass is idle)
+    FTB_ASSUME_SHARED(s_vt);
+    {
+        FPass2 A;
+        A.rowp = G.rowp, A.nch = P.vocab / 1024, A.vocab = P.vocab, A.shift = P.hash_shift, A.mask = P.hash_slots - 1;
+        A.apply_rep = P.apply_rep, A.penalty_type = P.penalty_type;
+        A.maxv = maxv, A.inv_t = H.inv_t, A.theta = H.theta, A.cut_y = cut_y, A.thr_y = T.thr_y, A.neg_max = neg_max;
+        A.thr_key = thr_key, A.lo_n = thr_key - cut_key, A.inv_t_h = H.inv_t_h;
+        A.emask = (u32)__cvta_generic_to_shared(S.emask), A.hash = (u32)__cvta_generic_to_shared(S.hash);
+        A.hlo = (u32)__cvta_generic_to_shared(hlo), A.spec = (u32)__cvta_generic_to_shared(spec);
+        A.nspec = (u32)__cvta_generic_to_shared(s_nspec), A.out = (u32)__cvta_generic_to_shared(s_vt);
+        // (the common case without temperature comes in two forms: with and without the per-pattern count)
+        if (temp) {
+            f_pass2<DT, true, true>(A);
+        }
+        else if (cut_key < thr_key) {
+            f_pass2<DT, false, true>(A);
+        }
+        else {
+            f_pass2<DT, false, false>(A);
+        }
+    }
+    __syncthreads();
+    trace_mark(trace, 7);
+    {
+        // the reference's blockReduceSum (utils/reduce_kernel_utils.cuh:73-103) over the 1024 partial sums: a
+        // butterfly inside every group of 32, then one over the 32 group results
+        float* const s_vw = s_vt + 1024;  // [32] (the ring area holds 8 KB)
+        for (int w = wid; w < 32; w += kWarps) {
+            float v = s_vt[w * 32 + lane];
+            for (int m = 16; m > 0; m >>= 1) {
+                v = v + __shfl_xor_sync(0xffffffffu, v, m);
+            }
+            if (lane == 0) {
+                s_vw[w] = v;
+            }
+        }
+        __syncthreads();
+        if (wid == 0) {
+            float v = s_vw[lane];
+            for (int m = 16; m > 0; m >>= 1) {
+                v = v + __shfl_xor_sync(0xffffffffu, v, m);
+            }
+            if (lane == 0) {
+                s_den = v;
+            }
+        }
+    }
+    __syncthreads();
+    const float denom = s_den + 1e-6f;
+    auto prob_of = [&](float y) { return f_round_T<DT>(f_round_T<DT>(__expf(y - maxv)) / denom); };
+    const size_t col = (size_t)P.ite * P.local_batch + H.r;
+    int* const   id_out = P.output_ids + (size_t)P.step * P.batch_size + col;
+    const int    n_sp   = (int)*s_nspec;
+    if (n_sp > kFPSpecCap) {
+        return false;
+    }
+
+    // ---- arg-max shortcut of topp_beam_topk_kernel: the largest probability alone reaches p ----
+    const float p_max = f_round_T<DT>(f_round_T<DT>(1.0f) / denom);
+    if (p_max >= H.top_p) {
+        // first column holding the maximum (larger value, then smaller column)
+        if (tid == 0) {
+            s_sel = 0x7fffffff;
+        }
+        __syncthreads();
+        const u32 kmaxv = fkey(maxv);
+        for (int i = tid; i < T.n_ord; i += kThreads) {
+            const u32 e = cand[i];
+            if ((e >> 20) == T.relmax && fkey(value_of(thr_key + (e >> 20))) == kmaxv) {
+                atomicMin(&s_sel, (int)(e & 0xfffffu));
+            }
+        }
+        for (int i = tid; i < n_sp; i += kThreads) {
+            if (~(u32)(spec[i] >> 32) == kmaxv) {
+                atomicMin(&s_sel, (int)(spec[i] & 0xffffffffu));
+            }
+        }
+        __syncthreads();
+        const int id = s_sel;
+        if (id == 0x7fffffff) {
+            return false;
+        }
+        if (tid == 0) {
+            *id_out = id;
+            if (P.seq_len != nullptr && P.finished != nullptr) {
+                P.seq_len[H.r]  = P.seq_len[H.r] + 1;
+                P.finished[H.r] = id == H.end_id ? 1 : 0;
+            }
+        }
+        return true;
+    }
+    const float rand_num = H.u * H.top_p;
+
+    // ---- runs: the counted bit patterns in descending value with the listed columns merged in by probability ----
+    // pattern u of the window: key ktop - u, counted in hist (at or above the threshold) or hlo (below it)
+    const u32 ktop = thr_key + T.relmax;
+    const int npat = (int)(ktop - cut_key) + 1;
+    if (npat > 16 * kThreads) {
+        return false;
+    }
+    auto count_of = [&](int u) {
+        const u32 key = ktop - (u32)u;
+        return u >= npat ? 0u : (key >= thr_key ? hist[key - thr_key] : hlo[thr_key - 1u - key]);
+    };
+    // listed columns: value keys -> probability keys, sorted (probability descending, column ascending)
+    for (int i = tid; i < n_sp; i += kThreads) {
+        const u64 e = spec[i];
+        spec[i]     = ((u64)(~fkey(prob_of(fkey_inv(~(u32)(e >> 32))))) << 32) | (e & 0xffffffffu);
+    }
+    __syncthreads();
+    group_sort_u64<CtaSync, true>(spec, n_sp, tid, kThreads, CtaSync());
+    __syncthreads();
+    u32* const run_pr = S.emask;            // [kFPRuns] probability of the run (float bits), descending
+    u32* const run_st = run_pr + kFPRuns;   // [kFPRuns] length, then first position of the run
+    FTB_ASSUME_SHARED(run_pr);
+    FTB_ASSUME_SHARED(run_st);
+    constexpr int PER = 16;
+    for (int i = tid; i < kFPRuns; i += kThreads) {
+        run_st[i] = 0u;  // a position no pattern takes keeps length 0 and goes to a listed column
+    }
+    __syncthreads();
+    int nA;
+    {
+        u32 cnt[PER], mine = 0;
+        for (int i = 0; i < PER; ++i) {
+            cnt[i] = count_of(tid * PER + i);
+            mine += cnt[i] != 0 ? 1u : 0u;
+        }
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        if (lane == 31) {
+            s_wsum[wid] = incl;
+        }
+        __syncthreads();
+        u32 base = 0, tot = 0;
+        for (int i = 0; i < kWarps; ++i) {
+            if (i < wid) {
+                base += s_wsum[i];
+            }
+            tot += s_wsum[i];
+        }
+        nA = (int)tot;
+        if (nA + n_sp > kFPRuns) {
+            return false;
+        }
+        u32 at = base + incl - mine;
+        for (int i = 0; i < PER; ++i) {
+            if (cnt[i] != 0) {
+                const float pr = prob_of(value_of(ktop - (u32)(tid * PER + i)));
+                const u32   kp = ~fkey(pr);  // ascending in this key = descending probability
+                int         lo = 0, hi = n_sp;  // listed columns with a strictly larger probability
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if ((u32)(spec[mid] >> 32) < kp) {
+                        lo = mid + 1;
+                    }
+                    else {
+                        hi = mid;
+                    }
+                }
+                run_pr[at + lo] = __float_as_uint(pr);
+                run_st[at + lo] = cnt[i];
+                ++at;
+            }
+        }
+    }
+    __syncthreads();
+    // both lists keep their order in the merged sequence: the listed columns fill the positions the patterns left
+    // free, in order
+    const int M = nA + n_sp;
+    {
+        constexpr int RPT = kFPRuns / kThreads;
+        u32           freem = 0, mine = 0;
+        for (int i = 0; i < RPT; ++i) {
+            const int q = tid * RPT + i;
+            if (q < M && run_st[q] == 0u) {
+                freem |= 1u << i;
+                ++mine;
+            }
+        }
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        __syncthreads();
+        if (lane == 31) {
+            s_wsum[wid] = incl;
+        }
+        __syncthreads();
+        u32 j = incl - mine;
+        for (int i = 0; i < wid; ++i) {
+            j += s_wsum[i];
+        }
+        for (int i = 0; i < RPT; ++i) {
+            if ((freem >> i) & 1u) {
+                const int q = tid * RPT + i;
+                run_pr[q]   = __float_as_uint(fkey_inv(~(u32)(spec[j] >> 32)));
+                run_st[q]   = 1u;
+                ++j;
+            }
+        }
+    }
+    __syncthreads();
+    // the exponential has to be monotone over the patterns for the order of the runs to be the sorted order
+    for (int i = tid; i + 1 < M; i += kThreads) {
+        if (__uint_as_float(run_pr[i]) < __uint_as_float(run_pr[i + 1])) {
+            s_fail = 1;
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        return false;
+    }
+    // exclusive scan of the run lengths -> first position of each run
+    u32 N;
+    {
+        constexpr int RPT = kFPRuns / kThreads;
+        u32           c[RPT], mine = 0;
+        for (int i = 0; i < RPT; ++i) {
+            const int q = tid * RPT + i;
+            c[i]        = q < M ? run_st[q] : 0u;
+            mine += c[i];
+        }
+        u32 incl = mine;
+        for (int off = 1; off < 32; off <<= 1) {
+            const u32 t = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += t;
+            }
+        }
+        __syncthreads();
+        if (lane == 31) {
+            s_wsum[wid] = incl;
+        }
+        __syncthreads();
+        u32 base = 0, tot = 0;
+        for (int i = 0; i < kWarps; ++i) {
+            if (i < wid) {
+                base += s_wsum[i];
+            }
+            tot += s_wsum[i];
+        }
+        N      = tot;
+        u32 at = base + incl - mine;
+        for (int i = 0; i < RPT; ++i) {
+            const int q = tid * RPT + i;
+            if (q < M) {
+                run_st[q] = at;
+                at += c[i];
+            }
+        }
+    }
+    __syncthreads();
+    trace_mark(trace, 8);
+    if (trace != nullptr && tid == 0) {
+        trace[4 + 20] = (u64)(thr_key - cut_key);
+        trace[4 + 21] = (u64)N;
+        trace[4 + 22] = (u64)T.n_ord;
+    }
+    const int nch = (int)((N + 255u) / 256u);
+    if (nch > 1000 || N == 0) {
+        return false;
+    }
+    auto run_of = [&](u32 p) {  // run that holds position p
+        int lo = 0, hi = M - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (run_st[mid] <= p) {
+                lo = mid;
+            }
+            else {
+                hi = mid - 1;
+            }
+        }
+        return lo;
+    };
+    // run at the first position of every 256-entry chunk, and the chunk aggregates (the pattern counts below the
+    // threshold are done with: both live where they were)
+    int* const   run_at = (int*)hlo;              // [nch + 1]
+    float* const agg    = (float*)(hlo + 1008);   // [nch]
+    FTB_ASSUME_SHARED(run_at);
+    FTB_ASSUME_SHARED(agg);
+    for (int c = tid; c <= nch; c += kThreads) {
+        run_at[c] = c < nch ? run_of((u32)c * 256u) : M - 1;
+    }
+    __syncthreads();
+    auto load8 = [&](int c, float* x) {  // the 8 consecutive probabilities of this lane in chunk c
+        const u32 p0 = (u32)c * 256u + (u32)lane * 8u;
+        int       i  = 0;
+        if (p0 < N) {
+            int lo = run_at[c], hi = run_at[c + 1];
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (run_st[mid] <= p0) {
+                    lo = mid;
+                }
+                else {
+                    hi = mid - 1;
+                }
+            }
+            i = lo;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const u32 p = p0 + (u32)e;
+            if (p < N) {
+                if (i + 1 < M && run_st[i + 1] <= p) {
+                    ++i;
+                }
+                x[e] = __uint_as_float(run_pr[i]);
+            }
+            else {
+                x[e] = 0.0f;
+            }
+        }
+    };
+    // aggregate of every 256-value chunk in cub::BlockScan's raking order (32 segments of 8, Kogge-Stone across
+    // the segment totals); the chunks are independent of the running prefix
+    for (int c = wid; c < nch; c += kWarps) {
+        float x[8];
+        load8(c, x);
+        float up = x[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            up = up + x[i];
+        }
+        float inc = up;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= off) {
+                inc = inc + t;
+            }
+        }
+        if (lane == 31) {
+            agg[c] = inc;
+        }
+    }
+    __syncthreads();
+    // running prefix chunk by chunk, as the reference's prefix functor accumulates it; stop a little early
+    // (partial sums inside a chunk differ from prefix + aggregate only in the last bits)
+    if (tid == 0) {
+        float       R    = 0.0f;
+        int         c1   = nch;
+        const float stop = rand_num * (1.0f - 1e-4f);
+        for (int c = 0; c < nch; ++c) {
+            const float R2 = R + agg[c];
+            if (R2 >= stop) {
+                c1 = c;
+                break;
+            }
+            R = R2;
+        }
+        s_c1 = c1;
+        s_R  = R;
+    }
+    __syncthreads();
+    if (s_c1 >= nch) {
+        return false;  // the draw lies beyond the counted range
+    }
+    if (wid == 0) {
+        float R   = s_R;
+        int   sel = -2;
+        for (int c = s_c1; c < nch; ++c) {
+            float x[8];
+            load8(c, x);
+            float up = x[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) {
+                up = up + x[i];
+            }
+            float inc = up;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= off) {
+                    inc = inc + t;
+                }
+            }
+            const float ag  = __shfl_sync(0xffffffffu, inc, 31);
+            const float ex  = __shfl_up_sync(0xffffffffu, inc, 1);
+            float       o   = lane == 0 ? R : R + ex;
+            u32         cnt = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                o = o + x[i];
+                cnt += rand_num <= o ? 1u : 0u;
+            }
+            // a warp of the reference covers 4 of these lanes (32 consecutive probabilities)
+            u32 c4 = cnt;
+            c4 += __shfl_xor_sync(0xffffffffu, c4, 1);
+            c4 += __shfl_xor_sync(0xffffffffu, c4, 2);
+            const u32 any = __ballot_sync(0xffffffffu, c4 > 0);
+            if (any) {
+                const int g  = (__ffs(any) - 1) >> 2;
+                const u32 pc = __shfl_sync(0xffffffffu, c4, g * 4);
+                if ((u32)(c * 256 + g * 32 + 31) >= N) {
+                    sel = -2;  // the 32 probabilities of that warp are not all known
+                }
+                else {
+                    sel = c * 256 + g * 32 + (32 - (int)pc);
+                }
+                break;
+            }
+            R = R + ag;
+        }
+        if (lane == 0) {
+            s_sel = sel;
+        }
+    }
+    __syncthreads();
+    const int sel = s_sel;
+    trace_mark(trace, 9);
+    if (sel < 0 || (u32)sel >= N) {
+        return false;
+    }
+    // ---- the class of the crossing: every column whose probability equals that of position sel ----
+    const int   i_at  = run_of((u32)sel);
+    const float p_sel = __uint_as_float(run_pr[i_at]);
+    const u32   k_sel = fkey(p_sel);
+    if (tid == 0) {
+        s_ncls = 0;
+        s_imin = 0x7fffffff;
+        s_imax = -1;
+        int lo = 0, hi = i_at;  // first run with probability == p_sel (runs are descending)
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (fkey(__uint_as_float(run_pr[mid])) > k_sel) {
+                lo = mid + 1;
+            }
+            else {
+                hi = mid;
+            }
+        }
+        s_first = (int)run_st[lo];
+    }
+    __syncthreads();
+    // bit patterns that map to this probability (one pattern past the counted range is looked at too: a class
+    // that reaches down to the cut may go on below it)
+    for (int i = 0; i < PER + 1; ++i) {
+        const int u = tid * (PER + 1) + i;
+        if (u <= npat && ktop >= (u32)u) {
+            if (fkey(prob_of(value_of(ktop - (u32)u))) == k_sel) {
+                atomicMin(&s_imin, u);
+                atomicMax(&s_imax, u);
+            }
+        }
+    }
+    __syncthreads();
+    const int J = sel - s_first;
+    if (s_imax >= npat) {
+        return false;
+    }
+    u32* const cls = S.emask;  // [kFPClsCap] columns of the class (the runs are done with)
+    FTB_ASSUME_SHARED(cls);
+    const int imin = s_imin, imax = s_imax;
+    __syncthreads();
+    // listed columns of the class
+    for (int j = tid; j < n_sp; j += kThreads) {
+        if ((u32)(spec[j] >> 32) == ~k_sel) {
+            const u32 pos = atomicAdd(&s_ncls, 1u);
+            if (pos < (u32)kFPClsCap) {
+                cls[pos] = (u32)(spec[j] & 0xffffffffu);
+            }
+        }
+    }
+    if (imax >= 0) {
+        const u32 k_hi = ktop - (u32)imin, k_lo = ktop - (u32)imax;
+        if (k_lo >= thr_key) {
+            // the class lies at or above the threshold: its ordinary columns are candidates
+            for (int i = tid; i < T.n_ord; i += kThreads) {
+                const u32 e = cand[i], key = thr_key + (e >> 20);
+                if (key >= k_lo && key <= k_hi) {
+                    const u32 pos = atomicAdd(&s_ncls, 1u);
+                    if (pos < (u32)kFPClsCap) {
+                        cls[pos] = e & 0xfffffu;
+                    }
+                }
+            }
+        }
+        else {
+            // below the threshold: one filtered pass over the row lists the ordinary columns of the band
+            __syncthreads();
+            __shared__ FSink s_band;
+            if (tid == 0) {
+                FSink& K = s_band;
+                K.cand = cls, K.hist = S.hist, K.sval = S.sval, K.hash = S.hash, K.emask = (const unsigned char*)S.cand;
+                K.ncand = &s_ncls, K.bad = &s_fail, K.shift = P.hash_shift, K.mask = P.hash_slots - 1, K.cap = kFPClsCap;
+                K.wbuf = S.wbuf, K.wj = S.wj;
+            }
+            __syncthreads();
+            f_stream<DT, true, kFUnroll>((const uint4*)(G.rowp + (size_t)G.head * 2), nfull, G.head, k_lo, k_hi, s_band, &s_fail);
+            // row edges
+            const int tail0 = G.head + nfull * 8;
+            const int nedge = G.head + (P.vocab - tail0 > 0 ? P.vocab - tail0 : 0);
+            for (int i = tid; i < nedge; i += kThreads) {
+                const int v = i < G.head ? i : tail0 + (i - G.head);
+                if (v < P.vocab && hash_lookup_raw(S.hash, P.hash_shift, P.hash_slots - 1, v) == 0) {
+                    const u32 key = key16((u32)__ldg((const unsigned short*)G.rowp + v));
+                    if (key >= k_lo && key <= k_hi) {
+                        const u32 pos = atomicAdd(&s_ncls, 1u);
+                        if (pos < (u32)kFPClsCap) {
+                            cls[pos] = (u32)v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    trace_mark(trace, 10);
+    const int ncls = (int)s_ncls;
+    if (ncls > kFPClsCap || J < 0 || J >= ncls) {
+        return false;
+    }
+    // J-th smallest column of the class (the reference's stable sort leaves equal probabilities in column order)
+    if (tid == 0) {
+        s_sel = -1;
+    }
+    __syncthreads();
+    for (int a = tid; a < ncls; a += kThreads) {
+        const u32 ca = cls[a];
+        int       rk = 0;
+        for (int b = 0; b < ncls; ++b) {
+            rk += cls[b] < ca ? 1 : 0;
+        }
+        if (rk == J) {
+            s_sel = (int)ca;
+        }
+    }
+    __syncthreads();
+    const int id = s_sel;
+    if (id < 0) {
+        return false;
+    }
+    if (tid == 0) {
+        *id_out = id;
+        if (P.seq_len != nullptr && P.finished != nullptr) {
+            P.seq_len[H.r]  = P.seq_len[H.r] + 1;
+            P.finished[H.r] = id == H.end_id ? 1 : 0;
+        }
+    }
+    return true;
+}
+
+// One row of the top-k layer (TOPP: of the top-p layer, up to the point where the two part).  Returns true when
+// the row is done, false when it has to go to the list
 // (nothing of the row's state has been touched then).  CTA-collective.  `stage1` / `stage2` are the hooks
 // of the next row's header (run by thread 0 at points where the loads of the previous stage have had time
 // to land).
-template<int DT, class S1, class S2>
-__device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u64* trace, S1&& stage1, S2&& stage2)
+template<int DT, bool TOPP, class S1, class S2>
+__device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const FHdr& H, u64* trace, S1&& stage1, S2&& stage2)
 {
+    __shared__ u32   s_mass[kFMassBins];  // sample mass per bin, in units of 2^-20 (integer adds are native)
+    __shared__ float s_mtail[kWarps];
+    __shared__ u32   s_smaxkey, s_vmaxkey;
+    __shared__ FSink s_sink;
     __shared__ u32            s_ncand, s_nspec, s_bad, s_ncls, s_lane_base[8], s_thr, s_relmax;
     __shared__ unsigned short s_smax[kThreads];
     __shared__ int            s_pick_idx, s_ans, s_nruns;
@@ -569,7 +1553,14 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
         s_lane_base[tid] = 0;
     }
     if (tid == 0) {
-        s_ncand = 0, s_nspec = 0, s_bad = 0, s_ncls = 0, s_relmax = 0;
+        s_ncand = 0, s_nspec = 0, s_bad = 0, s_ncls = 0, s_relmax = 0, s_vmaxkey = 0;
+        FSink& K = s_sink;
+        K.cand = cand, K.hist = hist, K.sval = sval, K.hash = hash, K.emask = (const unsigned char*)S.emask;
+        K.ncand = &s_ncand, K.bad = &s_bad, K.shift = P.hash_shift, K.mask = P.hash_slots - 1, K.cap = kFCap;
+        K.wbuf = S.wbuf, K.wj = S.wj;
+    }
+    if (TOPP && tid < kFMassBins) {
+        s_mass[tid] = 0u;
     }
     {
         // largest sampled column of this thread, as an ordered key
@@ -593,14 +1584,16 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
     const int ncols  = nfull * 8;
     // columns the threshold should let through: 2k, at least k + 256 (the estimate from a few sampled maxima
     // scatters widely); for k = 1 a handful is enough
-    const int target = k == 1 ? 64 : (2 * k > k + 256 ? 2 * k : k + 256);
+    const int target = TOPP ? 2048 : (k == 1 ? 64 : (2 * k > k + 256 ? 2 * k : k + 256));
     u32       want_s = (u32)(((long long)target * (kFSampleV * kThreads * 8) + ncols - 1) / ncols);
     want_s           = want_s < 3u ? 3u : want_s;
     bool words_ok    = true;
     if (wid == 0) {
-        const u32 t = f_select_from_maxima(s_smax, want_s);
+        u32       kmx = 0;
+        const u32 t   = f_select_from_maxima(s_smax, want_s, &kmx);
         if (lane == 0) {
-            s_thr = t;
+            s_thr     = t;
+            s_smaxkey = kmx;
         }
     }
     else {
@@ -658,6 +1651,36 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
     const u32   thr_raw = key16_inv(thr_key);
     const float thr_y   = f_value<DT>(thr_raw, temp, H.inv_t, H.inv_t_h);
     const float neg_max = DT == FTB200_F16 ? -65504.0f : -FLT_MAX;
+    if (TOPP) {
+        // mass of the sampled columns below the threshold, per 16 bit patterns, relative to the largest sampled value
+        // (the provisional cut of the second pass is placed with it)
+        const float v_ref = f_value<DT>(key16_inv(s_smaxkey), temp, H.inv_t, H.inv_t_h);
+        float       far   = 0.0f;
+        {
+            constexpr int v = 0;  // (half the sample is plenty here; the scale below accounts for it)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const u32 raw = raw_bits<DT>(smp[v], e);
+                const u32 kk  = key16(raw);
+                if (kk < thr_key && (raw & 0x7fffu) <= (DT == FTB200_F16 ? 0x7c00u : 0x7f80u)) {
+                    const float w = __expf(f_value<DT>(raw, temp, H.inv_t, H.inv_t_h) - v_ref);
+                    const u32   b = (thr_key - 1u - kk) >> 4;
+                    if (b < (u32)kFMassBins) {
+                        smem_add(&s_mass[b], (u32)(w * 1048576.0f));
+                    }
+                    else {
+                        far += w;
+                    }
+                }
+            }
+        }
+        for (int m = 16; m > 0; m >>= 1) {
+            far += __shfl_xor_sync(0xffffffffu, far, m);
+        }
+        if (lane == 0) {
+            s_mtail[wid] = far;
+        }
+    }
     __syncthreads();
     trace_mark(trace, 1);
     if (long_words || want_s > 96u || !(thr_y > neg_max) || thr_key == 0u) {
@@ -665,18 +1688,16 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
     }
 
     // ---- the pass ----
-    {
-        FSink K;
-        K.cand = cand, K.hist = hist, K.sval = sval, K.hash = hash, K.emask = (const unsigned char*)emask32;
-        K.ncand = &s_ncand, K.bad = &s_bad, K.shift = P.hash_shift, K.mask = P.hash_slots - 1;
-        f_stream<DT>(vp, nfull, G.head, thr_key, K, &s_relmax);
-    }
+    f_stream<DT, false, kFUnroll>(vp, nfull, G.head, thr_key, 0u, s_sink, &s_relmax);
     __syncthreads();
     trace_mark(trace, 2);
     trace_mark(trace, 3);
     trace_mark(trace, 4);
     // ---- listed columns: special ones with their final value, and the row's edges ----
-    u64* const spec = (u64*)S.emask;  // [kFSpecCap] (~key(value) << 32) | column; the per-vector bytes are done with
+    // (~key(value) << 32) | column.  Top-k rows: [kFSpecCap] where the per-vector bytes were (they are done with);
+    // top-p rows: [kFPSpecCap] where the row's set-up data was (the bytes are needed once more)
+    u64* const    spec     = TOPP ? (u64*)S.stage : (u64*)S.emask;
+    constexpr int spec_cap = TOPP ? kFPSpecCap : kFSpecCap;
     FTB_ASSUME_SHARED(spec);
     {
         Xf X;
@@ -686,8 +1707,11 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
         auto push = [&](int c, float y) {
             if (y >= thr_y && y > neg_max) {
                 const u32 pos = atomicAdd(&s_nspec, 1u);
-                if (pos < (u32)kFSpecCap) {
+                if (pos < (u32)spec_cap) {
                     spec[pos] = ((u64)(~fkey(y)) << 32) | (u32)c;
+                }
+                if (TOPP) {
+                    atomicMax(&s_vmaxkey, fkey(y));
                 }
             }
         };
@@ -719,8 +1743,24 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
     __syncthreads();
     trace_mark(trace, 5);
     const int n_ord = (int)s_ncand, n_sp = (int)s_nspec;
-    if (s_bad || n_ord > kFCap || n_sp > kFSpecCap || n_ord + n_sp < k) {
+    if (s_bad || n_ord > kFCap || n_sp > spec_cap || n_ord + n_sp < (TOPP ? 1 : k)) {
         return false;
+    }
+    if constexpr (TOPP) {
+        if (n_ord < 1 || G.head != 0) {
+            return false;  // (the second pass wants the row on a 16-byte boundary)
+        }
+        FTopp T;
+        T.thr_key = thr_key, T.relmax = s_relmax, T.n_ord = n_ord, T.n_sp = n_sp;
+        T.thr_y = thr_y, T.neg_max = neg_max;
+        const float top_ord = f_value<DT>(key16_inv(thr_key + s_relmax), temp, H.inv_t, H.inv_t_h);
+        const float top_sp  = s_vmaxkey != 0 ? fkey_inv(s_vmaxkey) : -INFINITY;
+        T.maxv              = fmaxf(top_ord, top_sp);
+        float mass_tail     = 0.0f;
+        for (int i = 0; i < kWarps; ++i) {
+            mass_tail += s_mtail[i];
+        }
+        return fast_topp_tail<DT>(P, S, H, G, T, spec, &s_nspec, s_mass, mass_tail, s_smaxkey, trace);
     }
 
     // ---- the draw (warp 0): runs of equal values from the top, then the reference's sequential sum and walk ----
@@ -981,24 +2021,30 @@ __device__ bool fast_topk_row(const KParams& P, const FMap& S, const FHdr& H, u6
     return true;
 }
 
-template<int DT>
-__global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid_constant__ KParams P)
+template<int DT, bool TOPP>
+__global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(const __grid_constant__ KParams P)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ FHdr                               s_hdr[2];
     __shared__ __align__(16) u32                  s_pre[kFPreWords];
-    FMap                                          S;
+    __shared__ uint4                              s_wbuf[kWarps * 64];
+    __shared__ unsigned short                     s_wj[kWarps * 64];
+    FMap S;
+    {
+    S.wbuf = s_wbuf;
+    S.wj   = s_wj;
     S.cand = (u32*)smem_raw;
     S.emask = S.cand + kFCap;
     S.hash  = S.emask + fast_mask_bytes(P.vocab_padded) / 4;
     S.sval  = S.hash + P.hash_slots;
-    S.hist  = S.sval + P.hash_slots;
+    S.hist  = S.sval + (P.hash_slots > kFBins ? P.hash_slots : kFBins);
     S.stage = S.hist + kFBins;
+    }
     const int tid = threadIdx.x;
     // thread 0 keeps the next row's ticket and number between the stages
     int nt = 0, nr = 0;
     if (tid == 0) {
-        nt = (int)atomicAdd(P.ticket, 1u);
+        nt = (int)atomicAdd(P.ticket + (TOPP ? 3 : 0), 1u);
         if (nt < P.local_batch) {
             nr = P.row_order != nullptr ? P.row_order[nt] : nt;
             f_prefetch_header(P, nr, s_pre);
@@ -1013,13 +2059,13 @@ __global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid
             break;
         }
         const int  r   = H.r;
-        u64* const rec = P.trace != nullptr ? P.trace + (size_t)H.t * kTraceWords : nullptr;
+        u64* const rec = P.trace != nullptr ? P.trace + ((size_t)H.t + (TOPP ? 2 * (size_t)P.local_batch : 0)) * kTraceWords : nullptr;
         if (tid == 0) {
             if (rec != nullptr) {
                 rec[0] = (u64)r, rec[1] = (u64)blockIdx.x, rec[2] = global_timer_ns();
                 rec[4 + 25] = (u64)clock64();
             }
-            nt = (int)atomicAdd(P.ticket, 1u);  // stage 0 of the next row's header
+            nt = (int)atomicAdd(P.ticket + (TOPP ? 3 : 0), 1u);  // stage 0 of the next row's header
         }
         auto stage1 = [&]() {
             if (tid == 0 && nt < P.local_batch) {
@@ -1033,7 +2079,19 @@ __global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid
         };
         bool       done   = false;
         int* const id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
-        if (H.mode == 1 && !H.fin) {
+        const bool topp_row = H.mode == 2 && !H.fin;
+        if (topp_row != TOPP) {
+            // the other kernel's row
+            stage1();
+            stage2();
+            __syncthreads();
+            if (tid == 0) {
+                cp_async_wait_all();
+                f_compose_header(P, nt, nr, s_pre, s_hdr[cur ^ 1]);
+            }
+            continue;
+        }
+        if (H.mode != 0 && !H.fin) {
             const FGeo G  = f_geometry(P, r);
             // (a penalty that can raise a value - repetition below 1, presence below 0 - would make columns
             //  under the threshold candidates: those rows go to the general kernel)
@@ -1043,11 +2101,12 @@ __global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid
                             && (P.apply_rep ? P.step : 0) <= kFMaxHist
                             && (P.bad_words != nullptr ? P.bad_words_len : 0) <= kFMaxWords;
             if (ok) {
-                done = fast_topk_row<DT>(P, S, H, rec, stage1, stage2);
+                done = fast_row<DT, TOPP>(P, S, H, rec, stage1, stage2);
                 if (done && tid == 0) {
-                    curandState_t st = P.topk_states[r];
+                    curandState_t* states = H.mode == 1 ? P.topk_states : P.topp_states;
+                    curandState_t  st     = states[r];
                     (void)curand_uniform(&st);
-                    P.topk_states[r] = st;
+                    states[r] = st;
                 }
             }
             else {
@@ -1065,6 +2124,22 @@ __global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid
                 // kernels/sampling_topk_kernels.cu:249-252: end id, no draw, length unchanged
                 if (tid == 0) {
                     *id_out = H.end_id;
+                }
+                done = true;
+            }
+            else {
+                // a finished row of the top-p layer: one-hot on the end id with probability 1 / (1 + 1e-6)
+                // (kernels/sampling_topp_kernels.cu:1309-1341); the layer still draws
+                if (tid == 0) {
+                    const float p0 = DT == FTB200_F16 ? __half2float(__float2half_rn(1.0f / (1.0f + 1e-6f))) :
+                                                        1.0f / (1.0f + 1e-6f);
+                    *id_out        = H.end_id;
+                    if ((p0 >= H.top_p || H.u * H.top_p <= p0) && P.seq_len != nullptr && P.finished != nullptr) {
+                        P.finished[r] = 1;
+                    }
+                    curandState_t st = P.topp_states[r];
+                    (void)curand_uniform(&st);
+                    P.topp_states[r] = st;
                 }
                 done = true;
             }
@@ -1098,19 +2173,36 @@ __global__ void __launch_bounds__(kThreads, 3) fast_sampling_kernel(const __grid
     }
 }
 
-template<int DT>
+template<int DT, bool TOPP>
 int fast_sampling_occupancy(size_t smem, int* per_sm)
 {
-    FTB_CUDA_CHECK(
-        cudaFuncSetAttribute(fast_sampling_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    FTB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, fast_sampling_kernel<DT>, kThreads, smem));
+    // per device: the opt-in to the shared-memory size (a per-device attribute of the kernel) and the answer
+    constexpr int     kMaxDev = 64;
+    static std::mutex mu;
+    static size_t     set_smem[kMaxDev];
+    static int        val[kMaxDev];
+    int               dev = 0;
+    FTB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDev) {
+        set_error("ftb200_decode_step_sampling: device ordinal out of range");
+        return FTB200_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (set_smem[dev] != smem) {
+        FTB_CUDA_CHECK(cudaFuncSetAttribute(fast_sampling_kernel<DT, TOPP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)smem));
+        FTB_CUDA_CHECK(
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&val[dev], fast_sampling_kernel<DT, TOPP>, kThreads, smem));
+        set_smem[dev] = smem;
+    }
+    *per_sm = val[dev];
     return FTB200_OK;
 }
 
-template<int DT>
+template<int DT, bool TOPP>
 int fast_sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st)
 {
-    fast_sampling_kernel<DT><<<grid, kThreads, smem, st>>>(K);
+    fast_sampling_kernel<DT, TOPP><<<grid, kThreads, smem, st>>>(K);
     FTB_CUDA_CHECK(cudaGetLastError());
     return FTB200_OK;
 }

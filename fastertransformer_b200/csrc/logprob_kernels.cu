@@ -234,12 +234,10 @@ int launch_log_probs(float* cum, const void* logits, const int* ids, const int* 
                      size_t batch, size_t vocab, size_t vocab_padded, float* log_probs, cudaStream_t st,
                      int batch_first)
 {
-    static int n_sm = 0;
-    if (n_sm == 0) {
-        int dev = 0;
-        FTB_CUDA_CHECK(cudaGetDevice(&dev));
-        FTB_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-    }
+    // (asked per call: the attribute query is a host-side table look-up, and a process may drive several devices)
+    int n_sm = 0, dev = 0;
+    FTB_CUDA_CHECK(cudaGetDevice(&dev));
+    FTB_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     const long long rows = (long long)(max_len - 1) * (long long)batch;
     if (rows > 0) {
         const int grid = (int)std::min<long long>(rows, (long long)n_sm * 8);

@@ -1,4 +1,7 @@
 // extern "C" entry of the fused decode-sampling step: argument checks, shared-memory plan, launch.
+#include <atomic>
+#include <mutex>
+
 #include "sampling_params.cuh"
 
 namespace ftb200 {
@@ -13,15 +16,19 @@ extern template int sampling_occupancy<FTB200_BF16>(size_t, int*);
 extern template int sampling_launch<FTB200_F32>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
-template<int DT>
+template<int DT, bool TOPP>
 int fast_sampling_occupancy(size_t smem, int* per_sm);
-template<int DT>
+template<int DT, bool TOPP>
 int fast_sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st);
-extern template int fast_sampling_occupancy<FTB200_F16>(size_t, int*);
-extern template int fast_sampling_occupancy<FTB200_BF16>(size_t, int*);
-extern template int fast_sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
-extern template int fast_sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
-size_t fast_smem_for(int hash_slots, int vocab_padded);
+extern template int fast_sampling_occupancy<FTB200_F16, false>(size_t, int*);
+extern template int fast_sampling_occupancy<FTB200_BF16, false>(size_t, int*);
+extern template int fast_sampling_launch<FTB200_F16, false>(const KParams&, int, size_t, cudaStream_t);
+extern template int fast_sampling_launch<FTB200_BF16, false>(const KParams&, int, size_t, cudaStream_t);
+extern template int fast_sampling_occupancy<FTB200_F16, true>(size_t, int*);
+extern template int fast_sampling_occupancy<FTB200_BF16, true>(size_t, int*);
+extern template int fast_sampling_launch<FTB200_F16, true>(const KParams&, int, size_t, cudaStream_t);
+extern template int fast_sampling_launch<FTB200_BF16, true>(const KParams&, int, size_t, cudaStream_t);
+size_t fast_smem_for(int hash_slots, int vocab_padded, bool topp);
 template<int DT>
 int vp_merge_launch(const KParams& K, const u64* gathered, int nranks, int* overflow, int grid, cudaStream_t st);
 extern template int vp_merge_launch<FTB200_F32>(const KParams&, const u64*, int, int*, int, cudaStream_t);
@@ -30,16 +37,23 @@ extern template int vp_merge_launch<FTB200_BF16>(const KParams&, const u64*, int
 
 static int sm_count()
 {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) {
-            n = 148;
-        }
+    // per device (a process may drive several GPUs, one thread each)
+    constexpr int           kMaxDev = 64;
+    static std::atomic<int> n[kMaxDev];
+    int                     dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= kMaxDev) {
+        dev = 0;
     }
-    return n;
+    int v = n[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        if (v <= 0) {
+            v = 148;
+        }
+        n[dev].store(v, std::memory_order_relaxed);
+    }
+    return v;
 }
 
 constexpr int kMaxCtasPerSm = 2;
@@ -59,6 +73,33 @@ static size_t redo_list_bytes(int local_batch)
 }
 
 static int g_fast_path = 1;  // see ftb200_set_single_pass
+
+// Second stream of the single-pass step (one per device, made on first use) with the two events of its fork and join.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t  fork = nullptr, join = nullptr;
+};
+static int side_stream(SideStream** out)
+{
+    constexpr int     kMaxDev = 64;
+    static SideStream g_side[kMaxDev];
+    static std::mutex g_mu;
+    int               dev = 0;
+    FTB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDev) {
+        set_error("ftb200_decode_step_sampling: device ordinal out of range");
+        return FTB200_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(g_mu);
+    SideStream& s = g_side[dev];
+    if (s.stream == nullptr) {
+        FTB_CUDA_CHECK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+        FTB_CUDA_CHECK(cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming));
+        FTB_CUDA_CHECK(cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming));
+    }
+    *out = &s;
+    return FTB200_OK;
+}
 
 }  // namespace ftb200
 
@@ -247,31 +288,61 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
                              && K.out_log_probs == nullptr && p->vocab_size_padded <= (1 << 20)
                              && p->vocab_size >= 16384 + 16;
     if (single_pass) {
-        const size_t fsmem = fast_smem_for(K.hash_slots, p->vocab_size_padded);
-        int          fper  = 0;
-        rc = p->dtype == FTB200_F16 ? fast_sampling_occupancy<FTB200_F16>(fsmem, &fper) :
-                                      fast_sampling_occupancy<FTB200_BF16>(fsmem, &fper);
+        const size_t fsmem = fast_smem_for(K.hash_slots, p->vocab_size_padded, false);
+        const size_t psmem = fast_smem_for(K.hash_slots, p->vocab_size_padded, true);
+        const bool   f16   = p->dtype == FTB200_F16;
+        int          fper = 0, pper = 0;
+        rc = f16 ? fast_sampling_occupancy<FTB200_F16, false>(fsmem, &fper) :
+                   fast_sampling_occupancy<FTB200_BF16, false>(fsmem, &fper);
+        if (rc == FTB200_OK && K.topp_states != nullptr) {
+            rc = f16 ? fast_sampling_occupancy<FTB200_F16, true>(psmem, &pper) :
+                       fast_sampling_occupancy<FTB200_BF16, true>(psmem, &pper);
+        }
         if (rc != FTB200_OK) {
             return rc;
         }
-        if (fper >= 1) {
+        if (fper >= 1 && (K.topp_states == nullptr || pper >= 1)) {
             KParams F    = K;
             F.redo_count = K.ticket + 1;
             F.redo_rows  = (int*)((char*)p->workspace + 256);
-            int fgrid    = sm_count() * fper;
-            fgrid        = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;
-            rc = p->dtype == FTB200_F16 ? fast_sampling_launch<FTB200_F16>(F, fgrid, fsmem, st) :
-                                          fast_sampling_launch<FTB200_BF16>(F, fgrid, fsmem, st);
+            // The rows of the top-p layer have a kernel of their own (it wants more registers than the top-k rows'
+            // kernel can spare); the two run side by side, the top-p one on a second stream that forks from and
+            // joins the caller's.  Each walks the row list and skips the other's rows.
+            SideStream* side = nullptr;
+            if (K.topp_states != nullptr) {
+                rc = side_stream(&side);
+                if (rc != FTB200_OK) {
+                    return rc;
+                }
+                FTB_CUDA_CHECK(cudaEventRecord(side->fork, st));
+                FTB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
+                int pgrid = sm_count() * pper;
+                pgrid     = pgrid < p->local_batch_size ? pgrid : p->local_batch_size;
+                rc = f16 ? fast_sampling_launch<FTB200_F16, true>(F, pgrid, psmem, side->stream) :
+                           fast_sampling_launch<FTB200_BF16, true>(F, pgrid, psmem, side->stream);
+                if (rc != FTB200_OK) {
+                    return rc;
+                }
+                note_launch(1);
+                FTB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
+            }
+            int fgrid = sm_count() * fper;
+            fgrid     = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;
+            rc = f16 ? fast_sampling_launch<FTB200_F16, false>(F, fgrid, fsmem, st) :
+                       fast_sampling_launch<FTB200_BF16, false>(F, fgrid, fsmem, st);
             if (rc != FTB200_OK) {
                 return rc;
             }
             note_launch(1);
+            if (side != nullptr) {
+                FTB_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
+            }
             K.ticket        = K.ticket + 2;
             K.row_order     = F.redo_rows;
+            K.row_count_dev = F.redo_count;
             if (K.trace != nullptr) {
                 K.trace += (size_t)p->local_batch_size * 32;  // the general kernel's records follow the single-pass kernel's
             }
-            K.row_count_dev = F.redo_count;
         }
     }
     switch (p->dtype) {

@@ -16,6 +16,7 @@
 #pragma once
 #include <curand_kernel.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "sampling_params.cuh"
@@ -4309,24 +4310,39 @@ int vp_merge_launch(const KParams& K, const u64* gathered, int nranks, int* over
 template<int DT>
 int sampling_occupancy(size_t smem, int* per_sm)
 {
-    // one query per distinct shared-memory size; the answer is cached for the life of the process
-    static size_t cached_smem[8];
-    static int    cached_val[8];
-    static int    n_cached = 0;
-    for (int i = 0; i < n_cached; ++i) {
-        if (cached_smem[i] == smem) {
-            *per_sm = cached_val[i];
+    // One query per device and distinct shared-memory size; the answers are kept for the life of the process.  The
+    // opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel: it is set on
+    // every device before the first query there.
+    constexpr int     kMaxDev = 64, kSizes = 8;
+    static std::mutex mu;
+    static bool       opted_in[kMaxDev];
+    static size_t     cached_smem[kMaxDev][kSizes];
+    static int        cached_val[kMaxDev][kSizes];
+    static int        n_cached[kMaxDev];
+    int               dev = 0;
+    FTB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDev) {
+        set_error("ftb200_decode_step_sampling: device ordinal out of range");
+        return FTB200_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!opted_in[dev]) {
+        FTB_CUDA_CHECK(
+            cudaFuncSetAttribute(decode_sampling_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        opted_in[dev] = true;
+    }
+    for (int i = 0; i < n_cached[dev]; ++i) {
+        if (cached_smem[dev][i] == smem) {
+            *per_sm = cached_val[dev][i];
             return FTB200_OK;
         }
     }
     FTB_CUDA_CHECK(
-        cudaFuncSetAttribute(decode_sampling_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    FTB_CUDA_CHECK(
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, decode_sampling_kernel<DT>, kThreads, smem));
-    if (n_cached < 8) {
-        cached_smem[n_cached] = smem;
-        cached_val[n_cached]  = *per_sm;
-        ++n_cached;
+    if (n_cached[dev] < kSizes) {
+        cached_smem[dev][n_cached[dev]] = smem;
+        cached_val[dev][n_cached[dev]]  = *per_sm;
+        ++n_cached[dev];
     }
     return FTB200_OK;
 }

@@ -384,4 +384,4 @@ class DynamicDecodeLayer:
             self.kernel_events.append((e0, e1))
         else:
             check(lib.ftb200_decode_step_sampling(C.byref(P)))
-        self.launches += 1
+        self.launches += lib.ftb200_last_launch_count()

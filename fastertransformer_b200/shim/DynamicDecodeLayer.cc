@@ -12,6 +12,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <map>
 #include <numeric>
 #include <stdexcept>
 
@@ -127,7 +128,7 @@ private:
         workspace_ = nullptr, workspace_bytes_ = 0;
         beam_ws_ = nullptr, beam_ws_bytes_ = 0;
         count_dev_ = nullptr, count_host_ = nullptr;
-        order_ = nullptr;
+        orders_.clear();
     }
 
     // runtime argument [1] or [batch] -> vector [batch]
@@ -193,8 +194,11 @@ private:
     SamplingState                       topk_, topp_;
     int                                 max_top_k_ = 1;
     std::vector<double>                 row_cost_;
-    int*                                order_ = nullptr;
-    size_t                              order_lo_ = (size_t)-1, order_n_ = 0;
+    struct OrderBuf {
+        std::vector<int> host;
+        int*             dev = nullptr;
+    };
+    std::map<std::pair<size_t, size_t>, OrderBuf> orders_;  // launch orders by (first row, rows) of a slice
     void*                               workspace_ = nullptr;
     size_t                              workspace_bytes_ = 0;
     void*                               beam_ws_ = nullptr;
@@ -337,7 +341,18 @@ void DecodeCore::setup(size_t batch_size, size_t beam_width, TensorMap* args)
             }
         }
     }
-    order_lo_ = (size_t)-1;
+    // the launch orders follow the new arguments: their buffers go back to the allocator
+    for (auto& kv : orders_) {
+        void* p = kv.second.dev;
+        for (auto it = owned_.begin(); it != owned_.end(); ++it) {
+            if (it->first == p) {
+                owned_.erase(it);
+                break;
+            }
+        }
+        allocator_->free(&p, false);
+    }
+    orders_.clear();
 }
 
 void DecodeCore::forward(TensorMap* out, TensorMap* in)
@@ -454,16 +469,23 @@ void DecodeCore::sample(TensorMap* out, TensorMap* in, size_t B, int step, int i
         // [request_output_len, batch] sliced at (step - max_input_length) (DynamicDecodeLayer.cc:427-435)
         p.output_log_probs = out->at("output_log_probs").getPtrWithOffset<float>((size_t)(step - mil) * B + lo);
     }
-    if (order_lo_ != lo || order_n_ != lbs) {
-        std::vector<int> ord(lbs);
-        std::iota(ord.begin(), ord.end(), 0);
-        std::stable_sort(ord.begin(), ord.end(), [&](int a, int b) { return row_cost_[lo + a] > row_cost_[lo + b]; });
-        order_ = alloc<int>(lbs);
-        check_cuda(cudaMemcpyAsync(order_, ord.data(), 4 * lbs, cudaMemcpyHostToDevice, stream_));
-        check_cuda(cudaStreamSynchronize(stream_));
-        order_lo_ = lo, order_n_ = lbs;
+    // Launch order of the slice (costliest rows first), one device buffer per (first row, rows) pair seen since
+    // the last setup(): a caller that walks its micro-batches with `ite` gets every order built once, and
+    // forward() neither allocates nor waits for the stream after that.
+    auto ord_it = orders_.find({lo, lbs});
+    if (ord_it == orders_.end()) {
+        OrderBuf ob;
+        ob.host.resize(lbs);
+        std::iota(ob.host.begin(), ob.host.end(), 0);
+        std::stable_sort(ob.host.begin(), ob.host.end(),
+                         [&](int a, int b) { return row_cost_[lo + a] > row_cost_[lo + b]; });
+        ob.dev = alloc<int>(lbs);
+        ord_it = orders_.emplace(std::make_pair(lo, lbs), std::move(ob)).first;
+        // (the host vector lives in the map, so the copy may complete after this call returns)
+        check_cuda(cudaMemcpyAsync(ord_it->second.dev, ord_it->second.host.data(), 4 * lbs, cudaMemcpyHostToDevice,
+                                   stream_));
     }
-    p.row_order = order_;
+    p.row_order = ord_it->second.dev;
     size_t need = 0;
     check(ftb200_sampling_workspace_bytes(dtype_, (int)lbs, (int)vocab_padded_, &need));
     if (workspace_ == nullptr || workspace_bytes_ < need) {
