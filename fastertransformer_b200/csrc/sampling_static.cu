@@ -4,12 +4,13 @@
 //   * an inference server that reserves the whole GPU for its own memory pool at start-up, so that a
 //     later cudaMalloc from a plug-in fails or fragments the pool;
 //   * a plug-in whose per-step callback is forbidden to allocate (TensorRT's enqueue(), a Triton
-//     backend's execute path) because allocation synchronises the device and adds jitter to every token;
-//   * code that runs between cudaStreamBeginCapture and cudaStreamEndCapture, where cudaMalloc is illegal.
+//     backend's execute path) because allocation synchronises the device and adds jitter to every token.
 // For them the scratch of the fused step lives in a fixed array inside the library image.  Every GPU that
 // loads the library carries the array (kStaticScratchBytes) until the process exits, used or not, so it is
 // kept small; shapes that need more are refused and have to be sent in slices (the `ite` /
 // `local_batch_size` fields of the argument block exist for exactly that).
+// The entry point itself allocates nothing and creates nothing: no cudaMalloc / cudaFree, no stream, no event
+// (the single-pass kernels of the step run one after the other on the caller's stream here).
 #include <mutex>
 
 #include "common.cuh"
@@ -48,6 +49,10 @@ int static_scratch(void** out)
 
 }  // namespace
 
+namespace ftb200 {
+int decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork);
+}
+
 extern "C" size_t ftb200_static_scratch_bytes(void)
 {
     return kStaticScratchBytes;
@@ -82,5 +87,5 @@ extern "C" int ftb200_decode_step_sampling_static(const ftb200_sampling_params* 
     ftb200_sampling_params q = *p;
     q.workspace              = scratch;
     q.workspace_bytes        = kStaticScratchBytes;
-    return ftb200_decode_step_sampling(&q);
+    return ftb200::decode_step_sampling_impl(&q, false);
 }
