@@ -29,6 +29,8 @@ extern template int fast_sampling_occupancy<FTB200_BF16, true>(size_t, int*);
 extern template int fast_sampling_launch<FTB200_F16, true>(const KParams&, int, size_t, cudaStream_t);
 extern template int fast_sampling_launch<FTB200_BF16, true>(const KParams&, int, size_t, cudaStream_t);
 size_t fast_smem_for(int hash_slots, int vocab_padded, bool topp);
+int    fast_max_history();
+int    fast_max_words();
 template<int DT>
 int vp_merge_launch(const KParams& K, const u64* gathered, int nranks, int* overflow, int grid, cudaStream_t st);
 extern template int vp_merge_launch<FTB200_F32>(const KParams&, const u64*, int, int*, int, cudaStream_t);
@@ -267,7 +269,18 @@ extern "C" int ftb200_set_row_trace(uint64_t* device_buf)
     return FTB200_OK;
 }
 
+// One fused step.  `fork` allows the second stream of the single-pass kernels (made on first use); without it
+// the same kernels run one after the other on the caller's stream and nothing is created.
+namespace ftb200 {
+int decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork);
+}
+
 extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
+{
+    return decode_step_sampling_impl(p, true);
+}
+
+int ftb200::decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork)
 {
     reset_launch_count();
     KParams K;
@@ -286,7 +299,8 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
     // leaves a list of the rows it does not cover; decode_sampling_kernel then works that list off.
     const bool single_pass = g_fast_path && p->dtype != FTB200_F32 && K.bias == nullptr && K.cum_log_probs == nullptr
                              && K.out_log_probs == nullptr && p->vocab_size_padded <= (1 << 20)
-                             && p->vocab_size >= 16384 + 16;
+                             && p->vocab_size >= 16384 + 16 && (K.apply_rep ? p->step : 0) <= fast_max_history()
+                             && (K.bad_words != nullptr ? K.bad_words_len : 0) <= fast_max_words();
     if (single_pass) {
         const size_t fsmem = fast_smem_for(K.hash_slots, p->vocab_size_padded, false);
         const size_t psmem = fast_smem_for(K.hash_slots, p->vocab_size_padded, true);
@@ -310,21 +324,27 @@ extern "C" int ftb200_decode_step_sampling(const ftb200_sampling_params* p)
             // joins the caller's.  Each walks the row list and skips the other's rows.
             SideStream* side = nullptr;
             if (K.topp_states != nullptr) {
-                rc = side_stream(&side);
-                if (rc != FTB200_OK) {
-                    return rc;
+                cudaStream_t pst = st;
+                if (fork) {
+                    rc = side_stream(&side);
+                    if (rc != FTB200_OK) {
+                        return rc;
+                    }
+                    FTB_CUDA_CHECK(cudaEventRecord(side->fork, st));
+                    FTB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
+                    pst = side->stream;
                 }
-                FTB_CUDA_CHECK(cudaEventRecord(side->fork, st));
-                FTB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
                 int pgrid = sm_count() * pper;
                 pgrid     = pgrid < p->local_batch_size ? pgrid : p->local_batch_size;
-                rc = f16 ? fast_sampling_launch<FTB200_F16, true>(F, pgrid, psmem, side->stream) :
-                           fast_sampling_launch<FTB200_BF16, true>(F, pgrid, psmem, side->stream);
+                rc = f16 ? fast_sampling_launch<FTB200_F16, true>(F, pgrid, psmem, pst) :
+                           fast_sampling_launch<FTB200_BF16, true>(F, pgrid, psmem, pst);
                 if (rc != FTB200_OK) {
                     return rc;
                 }
                 note_launch(1);
-                FTB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
+                if (side != nullptr) {
+                    FTB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
+                }
             }
             int fgrid = sm_count() * fper;
             fgrid     = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;

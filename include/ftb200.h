@@ -162,6 +162,11 @@ typedef struct ftb200_sampling_params {
  * invokeTopKSampling / invokeTopPSampling (TopKSamplingLayer.cu:93-108, TopPSamplingLayer.cu:120-141). */
 int ftb200_sampling_workspace_bytes(int dtype, int local_batch_size, int vocab_size_padded, size_t* bytes);
 
+/* Limits (FTB200_UNSUPPORTED beyond them): vocab_size_padded <= 2^21; with a repetition or presence penalty
+ * on, step + bad_words_len + 2 <= 4096 - the columns that need individual treatment (token history, banned
+ * words, min-length mask) are kept in a shared-memory table, two slots per column, and 8192 slots is what fits
+ * next to the other tables of the kernel.  Without a penalty the history does not enter the table and only
+ * bad_words_len + 2 <= 4096 applies. */
 int ftb200_decode_step_sampling(const ftb200_sampling_params* p);
 
 /* Number of kernels the last ftb200_decode_step_sampling call on this thread launched. */
@@ -215,17 +220,21 @@ int ftb200_wait_should_stop(const int* finished_count_host, int batch_size, int 
  * No counterpart in the reference: FasterTransformer always draws its buffers from an IAllocator.
  *
  * For hosts that cannot allocate device memory at the point of call - a server whose memory pool owns the
- * whole GPU, a plug-in callback that is forbidden to allocate, code inside a stream capture - the scratch
- * of ftb200_decode_step_sampling is a fixed area of ftb200_static_scratch_bytes() (64 MiB) built into the
- * library; every GPU that loads the library holds it until the process exits.  `workspace` and
- * `workspace_bytes` of the argument block are ignored; everything else means what it means above and the
- * results are the same.  No cudaMalloc, cudaFree or other allocating call is made.
+ * whole GPU, a plug-in callback that is forbidden to allocate - the scratch of ftb200_decode_step_sampling is
+ * a fixed area of ftb200_static_scratch_bytes() (64 MiB) built into the library; every GPU that loads the
+ * library holds it until the process exits.  `workspace` and `workspace_bytes` of the argument block are
+ * ignored; everything else means what it means above and the results are the same.  No cudaMalloc, cudaFree
+ * or other allocating call is made, and no stream or event is created: the kernels of the step run one
+ * after the other on `stream`.
  *
  *   - A shape whose ftb200_sampling_workspace_bytes() exceeds the area is refused with
- *     FTB200_WORKSPACE_SMALL (about 63 rows per call at vocab 128256, 255 at 32000): slice the batch with
- *     `ite` / `local_batch_size`.
- *   - The first call on each device looks up the device address of the area (cudaGetSymbolAddress); make
- *     that first call before any stream capture begins on that device.
+ *     FTB200_WORKSPACE_SMALL.  For local_batch_size up to twice the SM count the need is
+ *     256 + ceil256(4 * rows) + rows * ceil256(vocab_size_padded) * 8 bytes, which admits 65 rows per call at
+ *     vocab 128256 (66 are refused) and 262 at 32000: slice the batch with `ite` / `local_batch_size`.
+ *   - The first call on each device looks up the device address of the area (cudaGetSymbolAddress), and the
+ *     first call of each kernel variant on a device sets its shared-memory attribute and asks its occupancy.
+ *     That set-up belongs before any stream capture on that device; whether the call itself can be recorded
+ *     in a capture is not stated here either way.
  *   - All calls on a device share the one area.  Calls that may overlap on the GPU (different streams, or
  *     several host threads) race on it: serialise them, or give the overlapping ones their own workspace
  *     through ftb200_decode_step_sampling.

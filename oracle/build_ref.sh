@@ -4,10 +4,14 @@
 # oracle/ref_harness.cu.  Nothing is copied out of the reference tree; only
 # object files and the shared library land in oracle/_ref/ (git-ignored).
 #
-# usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default: $FT_REFERENCE_ROOT, else the build host's checkout)
+# usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default: $FT_REFERENCE_ROOT)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-${FT_REFERENCE_ROOT:-/root/reference}}"
+REF="${1:-${FT_REFERENCE_ROOT:-}}"
+if [ -z "$REF" ]; then
+    echo "usage: oracle/build_ref.sh REFERENCE_ROOT   (or set FT_REFERENCE_ROOT to a FasterTransformer checkout)" >&2
+    exit 2
+fi
 OUT="$HERE/_ref"
 OBJ="$OUT/obj"
 mkdir -p "$OBJ"

@@ -5,14 +5,16 @@ compiled or run): the 3x8 toy logits (probabilities 0.4/0.3/0.2/0.1 on four colu
 every TYPED_TEST(SamplingDecodeTest, ...), the runtime top-k / top-p arguments and the set of ids each
 (step, row) may produce.  Output: tests/golden/sampling_layer_kat.json.
 
-usage: python tests/golden/make_sampling_layer_kat.py [FT_ROOT]     (default: the build host's checkout)
+usage: python tests/golden/make_sampling_layer_kat.py [FT_ROOT]     (default: $FT_REFERENCE_ROOT)
 """
 import json
 import os
 import re
 import sys
 
-root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FT_REFERENCE_ROOT", "")
+if not root:
+    sys.exit("usage: make_sampling_layer_kat.py REFERENCE_ROOT   (or set FT_REFERENCE_ROOT)")
 src = open(os.path.join(root, "tests/unittests/test_sampling_layer.cu")).read()
 
 m = re.search(r"test_input_logits = new T\[24\]\{(.*?)\};", src, re.S)

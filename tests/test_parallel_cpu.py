@@ -12,7 +12,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from fastertransformer_b200.parallel import gather_rows, merge_records, pack_record, shard_rows
+from fastertransformer_b200.parallel import gather_rows, shard_rows
+from vp_records import merge_records, pack_record
 from ft_oracle import OracleDynamicDecodeLayer
 
 B, V, K, MIL = 6, 512, 7, 3

@@ -268,3 +268,25 @@ def test_config3_full_size_bit_exact(cuda_device):
             if e - start == 1:
                 assert (mine["ids"][:, b] != bw[b, 0, start]).all()
             start = e
+
+
+# ---- longest token history the kernels take ------------------------------------------------------------------
+def test_history_limit_against_reference(cuda_device):
+    """With a repetition penalty on, the columns of the token history live in a shared-memory table of at most
+    8192 slots (two per column): steps up to 4094 run and equal the reference, step 4095 is refused with
+    FTB200_UNSUPPORTED and leaves the row state untouched."""
+    from fastertransformer_b200 import FtbError
+    from fastertransformer_b200.workloads import SamplingWorkload
+    rng = np.random.default_rng(31)
+    B, V, mil, steps = 2, 4099, 4091, 5                       # steps 4091 .. 4095
+    args = {"runtime_top_k": np.asarray([3, 0], np.uint32), "runtime_top_p": np.asarray([0.0, 0.8], np.float32),
+            "repetition_penalty": np.asarray([1.2], np.float32), "random_seed": np.asarray([3, 4], np.uint64)}
+    w = SamplingWorkload("long", B, V, V, torch.float32, 2.0, steps, mil, V - 1, args, 12,
+                         prompt=rng.integers(0, V, size=(mil, B)).astype(np.int32))
+    mine_l, ref_l, ref_dt = _layers(w, cuda_device)
+    ref = _run(ref_l, w, cuda_device, cast=ref_dt, is_ref=True, steps=4)
+    mine = _run(mine_l, w, cuda_device, steps=4)
+    _same(mine, ref, "history of 4091..4094 tokens")
+    with pytest.raises(FtbError) as e:
+        _run(mine_l, w, cuda_device, steps=5)
+    assert e.value.status == 5 and "history too long" in str(e.value)      # FTB200_UNSUPPORTED
