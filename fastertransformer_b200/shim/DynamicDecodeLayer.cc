@@ -90,6 +90,7 @@ public:
 
     void setup(size_t batch_size, size_t beam_width, TensorMap* args);
     void forward(TensorMap* out, TensorMap* in);
+    void checkStep(TensorMap* out, TensorMap* in) const;
     void setStream(cudaStream_t stream)
     {
         stream_ = stream;
@@ -353,6 +354,31 @@ void DecodeCore::setup(size_t batch_size, size_t beam_width, TensorMap* args)
         allocator_->free(&p, false);
     }
     orders_.clear();
+}
+
+// What the reference's BaseSamplingLayer<T>::forward asserts before it touches the logits
+// (BaseSamplingLayer.cc:253-290): the step's tensors are there and the slice lies inside the batch set up.
+void DecodeCore::checkStep(TensorMap* out, TensorMap* in) const
+{
+    if (out == nullptr || in == nullptr) {
+        throw std::runtime_error("[FT][ERROR] forward() needs both tensor maps");
+    }
+    for (const char* key : {"logits", "step", "max_input_length", "end_id"}) {
+        if (!in->isExist(key)) {
+            throw std::runtime_error(std::string("[FT][ERROR] Cannot find a tensor of name ") + key + " in the tensor map");
+        }
+    }
+    if (!out->isExist("output_ids")) {
+        throw std::runtime_error("[FT][ERROR] Cannot find a tensor of name output_ids in the tensor map");
+    }
+    const Tensor& logits = in->at("logits");
+    const size_t  B      = logits.shape.empty() ? 0 : logits.shape[0];
+    const size_t  lbs    = in->isExist("local_batch_size") ? (size_t)in->getVal<int>("local_batch_size") : B;
+    const size_t  ite    = (size_t)in->getVal<uint32_t>("ite", 0u);
+    if (batch_ == 0 || lbs == 0 || (ite + 1) * lbs > batch_) {
+        throw std::runtime_error("[FT][ERROR] the slice [ite * local_batch_size, (ite + 1) * local_batch_size) lies "
+                                 "outside the batch given to setup()");
+    }
 }
 
 void DecodeCore::forward(TensorMap* out, TensorMap* in)
@@ -671,11 +697,71 @@ void DynamicDecodeLayer<T>::forward(std::unordered_map<std::string, Tensor>*    
 
 // ---- the sampling layers on their own ---------------------------------------------------------------
 template<typename T>
-TopKSamplingLayer<T>::TopKSamplingLayer(size_t, size_t vocab_size, size_t vocab_size_padded, int, size_t,
+BaseSamplingLayer<T>::BaseSamplingLayer(size_t, size_t vocab_size, size_t vocab_size_padded, int, size_t top_k, float,
                                         unsigned long long, float, float, float, cudaStream_t stream, cublasMMWrapper*,
-                                        IAllocator* allocator, bool is_free_buffer_after_forward):
-    core_(new DecodeCore(Mode::TopKOnly, DtypeOf<T>::value, vocab_size, vocab_size_padded, stream, allocator,
-                         is_free_buffer_after_forward))
+                                        IAllocator* allocator, bool is_free_buffer_after_forward, cudaDeviceProp*):
+    vocab_size_(vocab_size),
+    vocab_size_padded_(vocab_size_padded),
+    core_(new DecodeCore(top_k > 0 ? Mode::TopKOnly : Mode::TopPOnly, DtypeOf<T>::value, vocab_size, vocab_size_padded,
+                         stream, allocator, is_free_buffer_after_forward))
+{
+    // the per-layer defaults (top_k, top_p, temperature, penalties, seed) are dead arguments in the reference
+    // too: setup() reads everything from runtime_args (BaseSamplingLayer.cc:120-206)
+}
+template<typename T>
+BaseSamplingLayer<T>::BaseSamplingLayer(BaseSamplingLayer const& other):
+    vocab_size_(other.vocab_size_), vocab_size_padded_(other.vocab_size_padded_), core_(other.core_->cloneConfiguration())
+{
+}
+template<typename T>
+BaseSamplingLayer<T>::~BaseSamplingLayer() = default;
+template<typename T>
+void BaseSamplingLayer<T>::setup(const size_t batch_size, const size_t beam_width, TensorMap* runtime_args)
+{
+    core_->setup(batch_size, beam_width, runtime_args);
+}
+template<typename T>
+void BaseSamplingLayer<T>::forward(TensorMap* output_tensors, TensorMap* input_tensors)
+{
+    core_->checkStep(output_tensors, input_tensors);
+    runSampling(output_tensors, input_tensors);
+}
+template<typename T>
+void BaseSamplingLayer<T>::forward(std::unordered_map<std::string, Tensor>*       output_tensors,
+                                   const std::unordered_map<std::string, Tensor>* input_tensors)
+{
+    TensorMap in(*input_tensors), out(*output_tensors);
+    forward(&out, &in);
+}
+template<typename T>
+void BaseSamplingLayer<T>::forward(std::vector<Tensor>*, const std::vector<Tensor>*)
+{
+    throw std::runtime_error("[FT][ERROR] the positional forward() of a sampling layer is not supported");
+}
+template<typename T>
+void BaseSamplingLayer<T>::setStream(cudaStream_t stream)
+{
+    core_->setStream(stream);
+}
+template<typename T>
+cudaStream_t BaseSamplingLayer<T>::getStream()
+{
+    return core_->getStream();
+}
+
+template<typename T>
+TopKSamplingLayer<T>::TopKSamplingLayer(size_t max_batch_size, size_t vocab_size, size_t vocab_size_padded, int end_id,
+                                        size_t top_k, unsigned long long random_seed, float temperature,
+                                        float len_penalty, float repetition_penalty, cudaStream_t stream,
+                                        cublasMMWrapper* cublas_wrapper, IAllocator* allocator,
+                                        bool is_free_buffer_after_forward):
+    BaseSamplingLayer<T>(max_batch_size, vocab_size, vocab_size_padded, end_id, top_k > 0 ? top_k : 1, 0.0f, random_seed,
+                         temperature, len_penalty, repetition_penalty, stream, cublas_wrapper, allocator,
+                         is_free_buffer_after_forward, nullptr)
+{
+}
+template<typename T>
+TopKSamplingLayer<T>::TopKSamplingLayer(TopKSamplingLayer<T> const& other): BaseSamplingLayer<T>(other)
 {
 }
 template<typename T>
@@ -683,20 +769,27 @@ TopKSamplingLayer<T>::~TopKSamplingLayer() = default;
 template<typename T>
 void TopKSamplingLayer<T>::setup(const size_t batch_size, const size_t beam_width, TensorMap* runtime_args)
 {
-    core_->setup(batch_size, beam_width, runtime_args);
+    BaseSamplingLayer<T>::setup(batch_size, beam_width, runtime_args);
 }
 template<typename T>
-void TopKSamplingLayer<T>::forward(TensorMap* output_tensors, TensorMap* input_tensors)
+void TopKSamplingLayer<T>::runSampling(TensorMap* output_tensors, TensorMap* input_tensors)
 {
     core_->forward(output_tensors, input_tensors);
 }
 
 template<typename T>
-TopPSamplingLayer<T>::TopPSamplingLayer(size_t, size_t vocab_size, size_t vocab_size_padded, int, float,
-                                        unsigned long long, float, float, float, cudaStream_t stream, cublasMMWrapper*,
-                                        IAllocator* allocator, bool is_free_buffer_after_forward, cudaDeviceProp*):
-    core_(new DecodeCore(Mode::TopPOnly, DtypeOf<T>::value, vocab_size, vocab_size_padded, stream, allocator,
-                         is_free_buffer_after_forward))
+TopPSamplingLayer<T>::TopPSamplingLayer(size_t max_batch_size, size_t vocab_size, size_t vocab_size_padded, int end_id,
+                                        float top_p, unsigned long long random_seed, float temperature,
+                                        float len_penalty, float repetition_penalty, cudaStream_t stream,
+                                        cublasMMWrapper* cublas_wrapper, IAllocator* allocator,
+                                        bool is_free_buffer_after_forward, cudaDeviceProp* cuda_device_prop):
+    BaseSamplingLayer<T>(max_batch_size, vocab_size, vocab_size_padded, end_id, 0, top_p, random_seed, temperature,
+                         len_penalty, repetition_penalty, stream, cublas_wrapper, allocator,
+                         is_free_buffer_after_forward, cuda_device_prop)
+{
+}
+template<typename T>
+TopPSamplingLayer<T>::TopPSamplingLayer(TopPSamplingLayer<T> const& other): BaseSamplingLayer<T>(other)
 {
 }
 template<typename T>
@@ -704,10 +797,10 @@ TopPSamplingLayer<T>::~TopPSamplingLayer() = default;
 template<typename T>
 void TopPSamplingLayer<T>::setup(const size_t batch_size, const size_t beam_width, TensorMap* runtime_args)
 {
-    core_->setup(batch_size, beam_width, runtime_args);
+    BaseSamplingLayer<T>::setup(batch_size, beam_width, runtime_args);
 }
 template<typename T>
-void TopPSamplingLayer<T>::forward(TensorMap* output_tensors, TensorMap* input_tensors)
+void TopPSamplingLayer<T>::runSampling(TensorMap* output_tensors, TensorMap* input_tensors)
 {
     core_->forward(output_tensors, input_tensors);
 }
@@ -737,6 +830,7 @@ void OnlineBeamSearchLayer<T>::forward(TensorMap* output_tensors, TensorMap* inp
 
 #define FTB200_INSTANTIATE(T)                                                                                          \
     template class DynamicDecodeLayer<T>;                                                                              \
+    template class BaseSamplingLayer<T>;                                                                               \
     template class TopKSamplingLayer<T>;                                                                               \
     template class TopPSamplingLayer<T>;                                                                               \
     template class OnlineBeamSearchLayer<T>;

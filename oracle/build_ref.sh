@@ -1,8 +1,11 @@
 #!/usr/bin/env bash
 # TEST INFRASTRUCTURE.  Compiles the reference's own decode-sampling sources,
 # where they lie, into oracle/_ref/libft_decode_ref.so together with
-# oracle/ref_harness.cu.  Nothing is copied out of the reference tree; only
-# object files and the shared library land in oracle/_ref/ (git-ignored).
+# oracle/ref_harness.cu.  Only object files and the shared library land in
+# oracle/_ref/ (git-ignored), plus one test file of the reference placed there
+# unchanged (oracle/_ref/th_op/test_th_decode_op.py: the reference's own test
+# of its torch op, which tests/test_th_decode_op_gpu.py runs as it stands
+# against this package's torch class).  Nothing of the reference enters history.
 #
 # usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default: $FT_REFERENCE_ROOT)
 set -euo pipefail
@@ -74,3 +77,6 @@ done
 
 "$NVCC" -shared -o "$OUT/libft_decode_ref.so" "${objs[@]}" -lcudart -lcurand -lcublas -lcublasLt
 echo "built $OUT/libft_decode_ref.so"
+mkdir -p "$OUT/th_op"
+cp "$REF/tests/unittests/th_op/test_th_decode_op.py" "$OUT/th_op/test_th_decode_op.py"
+echo "placed $OUT/th_op/test_th_decode_op.py"

@@ -2,10 +2,18 @@
 // fastertransformer::DynamicDecodeLayer<T> on seeded inputs and prints the ids of every step, one line per
 // step.  tests/test_shim_gpu.py feeds the same inputs to the Python host mirror and compares the lines.
 //
-//   shim_driver <dtype: f32|f16|bf16> <batch> <vocab> <steps> <case: topk|topp|mixed|beam>
+//   shim_driver <dtype: f32|f16|bf16> <batch> <vocab> <steps> <case>
+//     topk | topp | mixed | beam   through DynamicDecodeLayer<T>
+//     topk_layer | topp_layer      through TopKSamplingLayer<T> / TopPSamplingLayer<T>, held and called as
+//                                  BaseSamplingLayer<T>* (setup, forward -> runSampling)
+//     slices                       the mixed case with the batch sent in two slices per step (ite 0 and 1); the
+//                                  allocator counts live allocations and the run fails if that count moves after
+//                                  the first step
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -43,16 +51,60 @@ static U* to_device(const std::vector<U>& v)
     return d;
 }
 
+// CudaAllocator that counts what is live.
+class CountingAllocator: public CudaAllocator {
+public:
+    mutable long live = 0, total = 0;
+    void*        malloc(size_t size, const bool is_set_zero = true, bool is_host = false) override
+    {
+        void* p = CudaAllocator::malloc(size, is_set_zero, is_host);
+        if (p != nullptr) {
+            ++live, ++total;
+        }
+        return p;
+    }
+    void free(void** ptr, bool is_host = false) const override
+    {
+        if (ptr != nullptr && *ptr != nullptr) {
+            --live;
+        }
+        CudaAllocator::free(ptr, is_host);
+    }
+};
+
 template<typename T>
-static int run(DataType dt, int B, int V, int steps, const std::string& which)
+static int run(DataType dt, int B, int V, int steps, std::string which)
 {
     const int     K   = which == "beam" ? 4 : 1;
     const int     mil = 4, L = mil + steps;
     cudaStream_t  stream;
     cudaStreamCreate(&stream);
-    CudaAllocator alloc;
+    CountingAllocator alloc;
     alloc.setStream(stream);
-    DynamicDecodeLayer<T> layer(V, V, V - 1, stream, nullptr, &alloc, false, nullptr);
+    const bool slices = which == "slices";
+    std::unique_ptr<DynamicDecodeLayer<T>> dispatcher;
+    std::unique_ptr<BaseSamplingLayer<T>>  sampler;  // the derived layers are used through the base's interface
+    if (which == "topk_layer") {
+        sampler.reset(new TopKSamplingLayer<T>(B, V, V, V - 1, 1, 0ull, 1.0f, 1.0f, 1.0f, stream, nullptr, &alloc, false));
+        which = "topk";
+    }
+    else if (which == "topp_layer") {
+        sampler.reset(new TopPSamplingLayer<T>(B, V, V, V - 1, 0.5f, 0ull, 1.0f, 1.0f, 1.0f, stream, nullptr, &alloc, false,
+                                               nullptr));
+        which = "topp";
+    }
+    else {
+        dispatcher.reset(new DynamicDecodeLayer<T>(V, V, V - 1, stream, nullptr, &alloc, false, nullptr));
+        if (slices) {
+            which = "mixed";
+        }
+    }
+    std::function<void(size_t, size_t, TensorMap*)> do_setup = [&](size_t b, size_t k, TensorMap* a) {
+        sampler ? sampler->setup(b, k, a) : dispatcher->setup(b, k, a);
+    };
+    std::function<void(TensorMap*, TensorMap*)> do_forward = [&](TensorMap* o, TensorMap* i) {
+        sampler ? sampler->forward(o, i) : dispatcher->forward(o, i);
+    };
 
     // runtime arguments (host tensors)
     std::vector<uint32_t>           top_k(B);
@@ -84,7 +136,7 @@ static int run(DataType dt, int B, int V, int steps, const std::string& which)
     else {
         args.insert("len_penalty", Tensor(MEMORY_CPU, TYPE_FP32, {1}, len_pen.data()));
     }
-    layer.setup(B, K, &args);
+    do_setup(B, K, &args);
 
     // state
     std::vector<int> ids_h((size_t)L * B * K, 0);
@@ -120,8 +172,11 @@ static int run(DataType dt, int B, int V, int steps, const std::string& which)
             logits_h[i] = convert<T>(unit(1000003ull * (s + 1), i));
         }
         cudaMemcpy(logits, logits_h.data(), sizeof(T) * logits_h.size(), cudaMemcpyHostToDevice);
-        int      step_v = step, mil_v = mil, lbs_v = B;
-        uint32_t ite_v = 0;
+        const int n_slices = slices ? 2 : 1;
+        long      live_before = alloc.live;
+        for (int sl = 0; sl < n_slices; ++sl) {
+        int      step_v = step, mil_v = mil, lbs_v = B / n_slices;
+        uint32_t ite_v = (uint32_t)sl;
         TensorMap in, out;
         if (K == 1) {
             in.insert("logits", Tensor(MEMORY_GPU, dt, {(size_t)B, (size_t)V}, logits));
@@ -145,7 +200,12 @@ static int run(DataType dt, int B, int V, int steps, const std::string& which)
         out.insert("sequence_length", Tensor(MEMORY_GPU, TYPE_INT32, {(size_t)B * K}, seq_len));
         out.insert("cum_log_probs", Tensor(MEMORY_GPU, TYPE_FP32, {(size_t)B * K}, cum));
         out.insert("should_stop", Tensor(MEMORY_CPU, TYPE_BOOL, {1}, &should_stop));
-        layer.forward(&out, &in);
+        do_forward(&out, &in);
+        }
+        if (slices && s > 0 && alloc.live != live_before) {
+            std::fprintf(stderr, "live allocations moved from %ld to %ld at step %d\n", live_before, alloc.live, step);
+            return 4;
+        }
         if (K > 1) {
             std::swap(src_ci, tgt_ci);
         }
@@ -156,6 +216,9 @@ static int run(DataType dt, int B, int V, int steps, const std::string& which)
             std::printf(" %d", v);
         }
         std::printf("\n");
+    }
+    if (slices) {
+        std::printf("allocations %ld live %ld\n", alloc.total, alloc.live);
     }
     const cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
@@ -168,7 +231,7 @@ static int run(DataType dt, int B, int V, int steps, const std::string& which)
 int main(int argc, char** argv)
 {
     if (argc < 6) {
-        std::fprintf(stderr, "usage: shim_driver f32|f16|bf16 batch vocab steps topk|topp|mixed|beam\n");
+        std::fprintf(stderr, "usage: shim_driver f32|f16|bf16 batch vocab steps topk|topp|mixed|beam|topk_layer|topp_layer|slices\n");
         return 1;
     }
     const std::string dt = argv[1], which = argv[5];

@@ -27,8 +27,9 @@ def _unit(seed, n):
     return ((m >> np.uint64(48)).astype(np.int64) - 32768).astype(np.float32) / np.float32(8192.0)
 
 
-def _python_side(dtype, B, V, steps, which):
-    from fastertransformer_b200 import DynamicDecodeLayer
+def _python_side(dtype, B, V, steps, which, layer_cls=None):
+    if layer_cls is None:
+        from fastertransformer_b200 import DynamicDecodeLayer as layer_cls
     dev = torch.device("cuda:0")
     K = 4 if which == "beam" else 1
     mil, L = 4, 4 + steps
@@ -47,7 +48,7 @@ def _python_side(dtype, B, V, steps, which):
                 "random_seed": (100 + 7 * idx).astype(np.uint64)}
     else:
         args = {"len_penalty": np.asarray([1.0], np.float32)}
-    layer = DynamicDecodeLayer(V, V, dtype, dev)
+    layer = layer_cls(V, V, dtype, dev)
     layer.setup(B, K, args)
     ids = np.zeros((L, B * K), np.int32)
     with np.errstate(over="ignore"):
@@ -87,8 +88,7 @@ CASES = [("f32", torch.float32, 6, 8, 6, "topk"), ("f32", torch.float32, 24, 204
          ("bf16", torch.bfloat16, 16, 8192, 3, "topk"), ("f16", torch.float16, 4, 4096, 4, "beam")]
 
 
-@pytest.mark.parametrize("name,dtype,B,V,steps,which", CASES)
-def test_cpp_layers_match_python_mirror(name, dtype, B, V, steps, which):
+def _driver(name, B, V, steps, which):
     if not os.path.exists(DRIVER):
         # built binaries normally travel with the tree; build here when this one did not
         from fastertransformer_b200.build import build_shim_driver
@@ -96,6 +96,50 @@ def test_cpp_layers_match_python_mirror(name, dtype, B, V, steps, which):
     assert os.path.exists(DRIVER), "shim driver not built: run python -m fastertransformer_b200.build"
     r = subprocess.run([DRIVER, name, str(B), str(V), str(steps), which], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
-    cpp = [l for l in r.stdout.strip().split("\n") if l.startswith("step")]
+    return r.stdout.strip().split("\n")
+
+
+def _ids_only(lines):
+    return [l.split(" ids ")[1] for l in lines if l.startswith("step")]
+
+
+@pytest.mark.parametrize("name,dtype,B,V,steps,which", CASES)
+def test_cpp_layers_match_python_mirror(name, dtype, B, V, steps, which):
+    cpp = [l for l in _driver(name, B, V, steps, which) if l.startswith("step")]
     py = _python_side(dtype, B, V, steps, which)
     assert cpp == py
+
+
+# The C++ classes against the compiled, unmodified reference on the same seeded inputs (the reference has no bf16
+# instantiation of this path).  "*_layer" drives TopKSamplingLayer<T> / TopPSamplingLayer<T> through a
+# BaseSamplingLayer<T>*; the reference's dispatcher with the same runtime arguments gives the ids to expect, since it
+# hands the rows to exactly that layer.  The last column says whether the stop flag of the step is compared too
+# (the sampling layers on their own have no stop criteria).  Every k stays below the vocabulary size: above it the
+# reference's first top-k stage runs out of columns and writes through the index -1 it keeps for "none found".
+REF_CASES = [("f32", torch.float32, 6, 64, 6, "topk", True), ("f32", torch.float32, 24, 2048, 4, "mixed", True),
+             ("f16", torch.float16, 24, 4096, 4, "topp", True), ("f16", torch.float16, 36, 8192, 4, "mixed", True),
+             ("f16", torch.float16, 20, 32768, 3, "mixed", True), ("f32", torch.float32, 12, 4096, 4, "topk_layer", False),
+             ("f16", torch.float16, 12, 4096, 4, "topp_layer", False), ("f16", torch.float16, 16, 32768, 3, "topk_layer", False),
+             ("f16", torch.float16, 4, 4096, 4, "beam", True)]
+
+
+@pytest.mark.parametrize("name,dtype,B,V,steps,which,with_stop", REF_CASES)
+def test_cpp_layers_match_compiled_reference(name, dtype, B, V, steps, which, with_stop):
+    import ft_reference
+    if not ft_reference.available():
+        pytest.skip("oracle/_ref/libft_decode_ref.so is not built")
+    cpp = [l for l in _driver(name, B, V, steps, which) if l.startswith("step")]
+    ref = _python_side(dtype, B, V, steps, which.replace("_layer", ""), ft_reference.RefDynamicDecodeLayer)
+    if with_stop:
+        assert cpp == ref
+    else:
+        assert _ids_only(cpp) == _ids_only(ref)
+
+
+@pytest.mark.parametrize("name,dtype,V", [("f32", torch.float32, 2048), ("bf16", torch.bfloat16, 32768)])
+def test_cpp_layer_slices_do_not_allocate_after_first_step(name, dtype, V):
+    """The batch sent as two slices per step (ite 0, 1) over 50 steps: same ids as the whole batch in one call, and
+    the driver itself fails when the allocator's count of live allocations moves after the first step."""
+    lines = _driver(name, 24, V, 50, "slices")
+    assert any(l.startswith("allocations ") for l in lines)
+    assert _ids_only(lines) == _ids_only(_python_side(dtype, 24, V, 50, "mixed"))

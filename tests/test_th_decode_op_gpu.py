@@ -187,3 +187,4 @@ def test_compiled_class_16_bit_logits(dtype):
     IMPL = "torch_class"
     assert bool((outs[0]["output_token_ids"] == outs[1]["output_token_ids"]).all())
     assert bool((outs[0]["output_sequence_lengths"] == outs[1]["output_sequence_lengths"]).all())
+
