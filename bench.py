@@ -22,6 +22,7 @@ reference sources) on the same workload through the reference's own DynamicDecod
 reference has no bf16 path, so it is fed the lossless fp32 up-cast, as its own models do.
 """
 import argparse
+import copy
 import json
 import os
 import subprocess
@@ -333,6 +334,29 @@ def run_ours(a, rank, world, local):
     return line
 
 
+def e2e_through_cpp_classes(rows=1024, vocab=128256, steps=12):
+    """The end-to-end leg once more with the host side in C++: the driver of the C++ decode layers
+    (tests/cpp/shim_driver.cc, built to fastertransformer_b200/lib/shim_driver) copies bf16 logits from pinned host
+    memory, calls fastertransformer::DynamicDecodeLayer<__nv_bfloat16>::forward and reads the ids back, every step,
+    and prints the rate itself.  Rows mix k in {0, 1, 8, 64} with p in {0, 0.5, 0.9}, repetition penalty 1.2."""
+    exe = os.path.join(ROOT, "fastertransformer_b200", "lib", "shim_driver")
+    if not os.path.exists(exe):
+        return {"unavailable": "fastertransformer_b200/lib/shim_driver is not built"}
+    try:
+        r = subprocess.run([exe, "bf16", str(rows), str(vocab), str(steps), "e2e"], capture_output=True, text=True,
+                           timeout=600)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "shim_driver did not finish in 600 s"}
+    for ln in r.stdout.split("\n"):
+        if ln.startswith("e2e "):
+            f = dict(kv.split("=") for kv in ln.split()[1:])
+            return {"value": float(f["tokens_per_s"]), "unit": "tokens/s", "ms_per_step": float(f["ms_per_step"]),
+                    "steps": int(f["steps"]), "h2d_bytes_per_step": int(f["h2d_bytes"]),
+                    "d2h_bytes_per_step": int(f["d2h_bytes"]),
+                    "workload": "batch %d x vocab %d bf16 through DynamicDecodeLayer<__nv_bfloat16> (C++)" % (rows, vocab)}
+    return {"unavailable": "shim_driver exit %d: %s" % (r.returncode, r.stderr[-200:])}
+
+
 def run_beam(a, rank, world, local, reference=False):
     """Config 4: beam search via online-softmax top-k. Batch 64 x beam 4 x vocab 32000 fp16, length penalty 1.0,
     cum_log_probs ~ N(-5, 1), end id 2; the batch is the unit that shards over GPUs (weak scaling here)."""
@@ -592,7 +616,9 @@ def main():
     ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5", "lp"],
                     help="c3 (default, the headline) | c1 / c2 the small sampling configurations | c4 beam search | "
                          "c5 vocabulary-parallel | lp context log-probs")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg and the C++-classes leg")
+    ap.add_argument("--no-other-configs", action="store_true",
+                    help="at N > 1: skip the config 5 / config 4 measurements added to the line")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch of the fused kernel from an ncu capture (profiles/)")
     a = ap.parse_args()
@@ -615,6 +641,20 @@ def main():
         line = run_reference(a, rank, world, local)
     else:
         line = run_ours(a, rank, world, local)
+        if world > 1 and a.workload == "c3" and not a.no_other_configs:
+            # the configurations that exist only on several GPUs, measured in the same process group: config 5
+            # (vocabulary in `world` shards, one all-gather per step) and config 4 (beam search, batch sharded)
+            b = copy.copy(a)
+            b.steps, b.warmup, b.batch = min(a.steps, 32), 3, None
+            other = {}
+            for name, leg in (("c5", run_vocab_parallel), ("c4", run_beam)):
+                got = leg(b, rank, world, local)
+                other[name] = {"ms_per_step": got["ms_per_step"], "value": got["value"], "unit": got["unit"],
+                               "scaling": got["scaling"], "steps": got["steps"], "config": got["config"],
+                               "roofline_frac": got["roofline"]["frac"]}
+            line["other_configs"] = other
+        if world == 1 and rank == 0 and a.workload == "c3" and not a.no_cpu:
+            line["e2e_cpp_classes"] = e2e_through_cpp_classes()
     if rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:

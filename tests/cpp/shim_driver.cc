@@ -9,6 +9,9 @@
 //     slices                       the mixed case with the batch sent in two slices per step (ite 0 and 1); the
 //                                  allocator counts live allocations and the run fails if that count moves after
 //                                  the first step
+//     e2e                          the mixed case timed end to end: every step copies the logits from pinned host
+//                                  memory, runs forward() and reads the step's ids back; prints one line
+//                                  "e2e tokens_per_s=... ms_per_step=... steps=... h2d_bytes=... d2h_bytes=..."
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -72,9 +75,132 @@ public:
     }
 };
 
+// End-to-end rate of DynamicDecodeLayer<T>::forward with host buffers: two pinned logits buffers alternate, the
+// copy of the next step's logits runs on a second stream under this step's kernels, the ids of every step are
+// read back before the next forward() is issued.  All copies lie inside the timed region.
+template<typename T>
+static int run_e2e(DataType dt, int B, int V, int steps)
+{
+    const int     mil = 4, warm = 3, L = mil + warm + steps;
+    cudaStream_t  stream, copy_stream;
+    cudaStreamCreate(&stream);
+    cudaStreamCreate(&copy_stream);
+    CudaAllocator alloc;
+    alloc.setStream(stream);
+    DynamicDecodeLayer<T> layer(V, V, V - 1, stream, nullptr, &alloc, false, nullptr);
+    std::vector<uint32_t>           top_k(B);
+    std::vector<float>              top_p(B), rep(1, 1.2f);
+    std::vector<unsigned long long> seeds(B);
+    for (int i = 0; i < B; ++i) {
+        const uint32_t ks[4] = {0, 1, 8, 64};
+        const float    ps[3] = {0.0f, 0.5f, 0.9f};
+        top_k[i] = ks[i % 4], top_p[i] = ps[(i / 4) % 3], seeds[i] = 100 + 7 * i;
+    }
+    TensorMap args;
+    args.insert("runtime_top_k", Tensor(MEMORY_CPU, TYPE_UINT32, {(size_t)B}, top_k.data()));
+    args.insert("runtime_top_p", Tensor(MEMORY_CPU, TYPE_FP32, {(size_t)B}, top_p.data()));
+    args.insert("repetition_penalty", Tensor(MEMORY_CPU, TYPE_FP32, {1}, rep.data()));
+    args.insert("random_seed", Tensor(MEMORY_CPU, TYPE_UINT64, {(size_t)B}, seeds.data()));
+    layer.setup(B, 1, &args);
+
+    std::vector<int> ids_h((size_t)L * B, 0);
+    for (int t = 0; t < mil; ++t) {
+        for (int b = 0; b < B; ++b) {
+            ids_h[(size_t)t * B + b] = (int)(mix(9000 + t * 131 + b) % (uint64_t)V);
+        }
+    }
+    int*      output_ids = to_device(ids_h);
+    uint8_t*  finished   = to_device(std::vector<uint8_t>((size_t)B, 0));
+    int*      seq_len    = to_device(std::vector<int>((size_t)B, mil));
+    int*      end_ids    = to_device(std::vector<int>(B, V - 1));
+    int*      in_len     = to_device(std::vector<int>((size_t)B, mil));
+    uint32_t* seq_lim    = to_device(std::vector<uint32_t>(B, (uint32_t)L + 1));
+    const size_t n = (size_t)B * V;
+    T *          host[2], *dev[2];
+    int*         ids_back = nullptr;
+    cudaMallocHost(&ids_back, sizeof(int) * B);
+    for (int b = 0; b < 2; ++b) {
+        cudaMallocHost(&host[b], sizeof(T) * n);
+        cudaMalloc(&dev[b], sizeof(T) * n);
+        for (size_t i = 0; i < n; ++i) {
+            host[b][i] = convert<T>(unit(1000003ull * (b + 1), i));
+        }
+    }
+    cudaEvent_t copied[2], consumed[2], t0, t1;
+    for (int b = 0; b < 2; ++b) {
+        cudaEventCreateWithFlags(&copied[b], cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&consumed[b], cudaEventDisableTiming);
+    }
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    bool should_stop = false;
+    auto copy_in     = [&](int i) {
+        const int b = i % 2;
+        cudaStreamWaitEvent(copy_stream, consumed[b], 0);
+        cudaMemcpyAsync(dev[b], host[b], sizeof(T) * n, cudaMemcpyHostToDevice, copy_stream);
+        cudaEventRecord(copied[b], copy_stream);
+    };
+    auto one_step = [&](int i, int step) {
+        const int b      = i % 2;
+        int       step_v = step, mil_v = mil, lbs_v = B;
+        uint32_t  ite_v = 0;
+        TensorMap in, out;
+        in.insert("logits", Tensor(MEMORY_GPU, dt, {(size_t)B, (size_t)V}, dev[b]));
+        in.insert("step", Tensor(MEMORY_CPU, TYPE_INT32, {1}, &step_v));
+        in.insert("max_input_length", Tensor(MEMORY_CPU, TYPE_INT32, {1}, &mil_v));
+        in.insert("ite", Tensor(MEMORY_CPU, TYPE_UINT32, {1}, &ite_v));
+        in.insert("local_batch_size", Tensor(MEMORY_CPU, TYPE_INT32, {1}, &lbs_v));
+        in.insert("end_id", Tensor(MEMORY_GPU, TYPE_INT32, {(size_t)B}, end_ids));
+        in.insert("input_lengths", Tensor(MEMORY_GPU, TYPE_INT32, {(size_t)B}, in_len));
+        in.insert("sequence_limit_length", Tensor(MEMORY_GPU, TYPE_UINT32, {(size_t)B}, seq_lim));
+        out.insert("output_ids", Tensor(MEMORY_GPU, TYPE_INT32, {(size_t)L, (size_t)B, 1}, output_ids));
+        out.insert("finished", Tensor(MEMORY_GPU, TYPE_BOOL, {(size_t)B}, finished));
+        out.insert("sequence_length", Tensor(MEMORY_GPU, TYPE_INT32, {(size_t)B}, seq_len));
+        out.insert("should_stop", Tensor(MEMORY_CPU, TYPE_BOOL, {1}, &should_stop));
+        cudaStreamWaitEvent(stream, copied[b], 0);
+        layer.forward(&out, &in);
+        cudaEventRecord(consumed[b], stream);
+        cudaMemcpyAsync(ids_back, output_ids + (size_t)step * B, sizeof(int) * B, cudaMemcpyDeviceToHost, stream);
+        cudaStreamSynchronize(stream);
+    };
+    int i = 0;
+    for (int b = 0; b < 2; ++b) {
+        cudaEventRecord(consumed[b], stream);
+    }
+    copy_in(0);
+    for (; i < warm; ++i) {
+        copy_in(i + 1);
+        one_step(i, mil + i);
+    }
+    cudaDeviceSynchronize();
+    // the buffer of step `warm` was copied during the warm-up; copy it again inside the timed region
+    cudaEventRecord(t0, stream);
+    copy_in(i);
+    for (; i < warm + steps; ++i) {
+        if (i + 1 < warm + steps) {
+            copy_in(i + 1);
+        }
+        one_step(i, mil + i);
+    }
+    cudaEventRecord(t1, stream);
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        std::fprintf(stderr, "CUDA error: %s\n", cudaGetErrorString(e));
+        return 2;
+    }
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, t0, t1);
+    std::printf("e2e tokens_per_s=%.1f ms_per_step=%.4f steps=%d h2d_bytes=%zu d2h_bytes=%zu\n",
+                (double)B * steps / (ms * 1e-3), ms / steps, steps, sizeof(T) * n, sizeof(int) * (size_t)B);
+    return 0;
+}
+
 template<typename T>
 static int run(DataType dt, int B, int V, int steps, std::string which)
 {
+    if (which == "e2e") {
+        return run_e2e<T>(dt, B, V, steps);
+    }
     const int     K   = which == "beam" ? 4 : 1;
     const int     mil = 4, L = mil + steps;
     cudaStream_t  stream;
@@ -231,7 +357,7 @@ static int run(DataType dt, int B, int V, int steps, std::string which)
 int main(int argc, char** argv)
 {
     if (argc < 6) {
-        std::fprintf(stderr, "usage: shim_driver f32|f16|bf16 batch vocab steps topk|topp|mixed|beam|topk_layer|topp_layer|slices\n");
+        std::fprintf(stderr, "usage: shim_driver f32|f16|bf16 batch vocab steps topk|topp|mixed|beam|topk_layer|topp_layer|slices|e2e\n");
         return 1;
     }
     const std::string dt = argv[1], which = argv[5];
