@@ -173,10 +173,12 @@ int ftb200_decode_step_sampling(const ftb200_sampling_params* p);
 int ftb200_last_launch_count(void);
 
 /* Diagnostic, no counterpart in the reference: when `device_buf` is not null every later
- * ftb200_decode_step_sampling call writes, per row ticket t, 32 uint64 at device_buf[32t..]:
- * {row, CTA, start, end, 28 phase marks} with the times in nanoseconds of the GPU's global timer
- * (a mark the row did not pass is left untouched).  The buffer must hold 256 bytes per row of the
- * call.  Pass null to switch the trace off (the default). */
+ * ftb200_decode_step_sampling call writes records of 32 uint64 each, {row, CTA, start, end, 28 phase marks}
+ * with the times in nanoseconds of the GPU's global timer (a mark the row did not pass is left untouched).
+ * With R = local_batch_size the record of the single-pass top-k kernel's ticket t lies at device_buf[32 t..],
+ * the general kernel's at device_buf[32 (R + t)..] and the single-pass top-p kernel's at
+ * device_buf[32 (2 R + t)..]: the buffer must hold 3 * 256 bytes per row of the call.  Pass null to switch the
+ * trace off (the default). */
 int ftb200_set_row_trace(uint64_t* device_buf);
 
 /* Diagnostic, no counterpart in the reference.  ftb200_decode_step_sampling serves 16-bit logits in two
