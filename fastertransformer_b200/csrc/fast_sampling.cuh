@@ -962,6 +962,9 @@ __device__ __forceinline__ bool fast_topp_tail(const KParams& P, const FMap& S, 
     }
     __syncthreads();
     const float denom = s_den + 1e-6f;
+    if (!(denom > 0.0f && denom < 3.0e38f)) {
+        return false;  // (not a number, or out of range: nothing below may index with what would follow from it)
+    }
     auto prob_of = [&](float y) { return f_round_T<DT>(f_round_T<DT>(__expf(y - maxv)) / denom); };
     const size_t col = (size_t)P.ite * P.local_batch + H.r;
     int* const   id_out = P.output_ids + (size_t)P.step * P.batch_size + col;
