@@ -49,12 +49,58 @@ def test_shards_match_full_row(n_shards, shard, k, coarse, cuda_device):
             assert torch.equal(s_full[key], s_vp[key]), (s, key)
 
 
+@pytest.mark.parametrize("dtype,n_shards,shard,sigma", [(torch.bfloat16, 4, 4096, 4.0), (torch.float16, 2, 5000, 5.0),
+                                                        (torch.float32, 8, 2048, 6.0), (torch.bfloat16, 4, 8192, 1.2),
+                                                        (torch.bfloat16, 2, 16448, 2.5), (torch.float16, 4, 8200, 1.0)])
+@pytest.mark.parametrize("all_top_p", [False, True], ids=["mixed", "all_top_p"])
+def test_vocab_parallel_top_p_rows_exact(dtype, n_shards, shard, sigma, all_top_p, cuda_device):
+    """The default form: pure top-p rows are gathered and sampled unsharded.  Everything - ids of every row,
+    finished flags, lengths and both layers' generator states - must EQUAL the unsharded layer's over several
+    steps, on peaked and on deliberately flat rows (sigma 1.0 - 1.2), with shards that are and are not a
+    multiple of 1024 columns, and nothing may be reported as overflow."""
+    from fastertransformer_b200 import DynamicDecodeLayer
+    from fastertransformer_b200.vocab_parallel import VocabParallelSampler
+    B, mil, steps = 64, 6, 4
+    V = shard * n_shards
+    rng = np.random.default_rng(170 + n_shards)
+    ks = np.zeros(B, np.uint32) if all_top_p else rng.choice(np.asarray([0, 0, 8, 40], np.uint32), size=B)
+    args = {"runtime_top_k": ks, "runtime_top_p": rng.choice(np.asarray([0.3, 0.6, 0.9, 0.97], np.float32), size=B),
+            "temperature": np.asarray([0.9], np.float32), "repetition_penalty": np.asarray([1.2], np.float32),
+            "random_seed": (np.arange(B) * 5 + 3).astype(np.uint64)}
+    prompt = torch.from_numpy(rng.integers(0, V, size=(mil, B)).astype(np.int32)).to(cuda_device)
+
+    def state():
+        ids = torch.zeros(mil + steps, B, dtype=torch.int32, device=cuda_device)
+        ids[:mil] = prompt
+        return {"output_ids": ids, "finished": torch.zeros(B, dtype=torch.bool, device=cuda_device),
+                "sequence_length": torch.full((B,), mil, dtype=torch.int32, device=cuda_device)}
+
+    full = DynamicDecodeLayer(V, V, dtype, cuda_device)
+    full.setup(B, 1, args)
+    vp = VocabParallelSampler(V, shard, n_shards, dtype, cuda_device)
+    vp.setup(B, 1, args)
+    st_a, st_b = state(), state()
+    end = torch.full((B,), V - 1, dtype=torch.int32, device=cuda_device)
+    g = torch.Generator(device=cuda_device)
+    for s in range(steps):
+        g.manual_seed(900 + s)
+        x = (torch.randn(B, V, generator=g, device=cuda_device) * sigma).to(dtype)
+        inp = {"step": mil + s, "max_input_length": mil, "end_id": end, "ite": 0, "local_batch_size": B}
+        full.forward(st_a, dict(inp, logits=x))
+        vp.forward_shards(st_b, inp, [x[:, i * shard:(i + 1) * shard].contiguous() for i in range(n_shards)])
+        torch.cuda.synchronize()
+        for key in ("output_ids", "finished", "sequence_length"):
+            assert torch.equal(st_a[key], st_b[key]), (s, key)
+        assert torch.equal(vp.topp.curand, full.topp.curand) and torch.equal(vp.topk.curand, full.topk.curand)
+        assert vp.overflow_count() == 0
+
+
 @pytest.mark.parametrize("resolve", [True, False], ids=["second_round", "report_only"])
 @pytest.mark.parametrize("dtype,n_shards,sigma,max_undecided", [(torch.bfloat16, 4, 4.0, 0.2), (torch.float16, 2, 5.0, 0.2),
                                                                 (torch.float32, 8, 6.0, 0.2), (torch.bfloat16, 4, 1.2, 1.0)])
 def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, resolve, cuda_device):
-    """Mixed top-k / top-p rows over a sharded vocabulary against the unsharded kernel.  Top-k rows must be
-    identical.  Top-p rows combine per-shard soft-max statistics, so their denominator is summed in another
+    """The approximate form (top_p="statistics"): mixed top-k / top-p rows over a sharded vocabulary against the
+    unsharded kernel.  Top-k rows must be identical.  Top-p rows combine per-shard soft-max statistics, so their denominator is summed in another
     order: ids are compared.  The rows the exchange cannot decide either get a second round on their gathered
     logits (then they are the unsharded kernel's ids, and no -1 is left) or are reported with id -1 and an
     untouched generator."""
@@ -77,7 +123,7 @@ def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, resolv
 
     full = DynamicDecodeLayer(V, V, dtype, cuda_device)
     full.setup(B, 1, args)
-    vp = VocabParallelSampler(V, shard, n_shards, dtype, cuda_device, resolve_undecided=resolve)
+    vp = VocabParallelSampler(V, shard, n_shards, dtype, cuda_device, resolve_undecided=resolve, top_p="statistics")
     vp.setup(B, 1, args)
     st_a, st_b = state(), state()
     end = torch.full((B,), V - 1, dtype=torch.int32, device=cuda_device)
