@@ -194,6 +194,7 @@ class DynamicDecodeLayer:
                 .to(self.device),
             }
         self._g = g
+        self._stream = self._stream_ptr()  # one look-up per call, used by the sampling and the criteria launch
         topk_on, topp_on = g["topk_on"], g["topp_on"]
         if topk_on or topp_on:
             self._sample(outputs, inputs, logits, B, step, ite, lbs, mil, lo, hi, topk_on, topp_on)
@@ -207,7 +208,7 @@ class DynamicDecodeLayer:
         ite = int(inputs.get("ite", 0))
         lbs = int(inputs.get("local_batch_size", B))
         mil = int(inputs["max_input_length"])
-        st = self._stream_ptr()
+        st = self._stream = self._stream_ptr()
         es = logits.element_size()
         out_ids = outputs["output_ids"]
         L = out_ids.shape[0]
@@ -295,7 +296,7 @@ class DynamicDecodeLayer:
             self._count_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._count_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         L = 0 if sw is None else sw.shape[-1]
-        st = self._stream_ptr()
+        st = getattr(self, "_stream", None) or self._stream_ptr()
         check(lib.ftb200_stop_criteria(
             _ptr(outputs["output_ids"]), _ptr(outputs.get("parent_ids")),
             None if sw is None else C.c_void_p(sw.data_ptr() + lo * 2 * L * 4), L, _ptr(outputs["finished"]),
@@ -312,10 +313,34 @@ class DynamicDecodeLayer:
         Vp = self.vocab_size_padded
         es = logits.element_size()
 
-        P = SamplingParams()
+        # The argument block of a slice is kept between steps: what setup() fixed (the layer's own buffers, the
+        # launch order, the slice) is written once, the step's own values every time.
+        P = self._g.get("params")
+        if P is None or self._g["params_key"] != (B, lbs, ite, topk_on, topp_on):
+            P = SamplingParams()
+            P.batch_size, P.local_batch_size, P.ite = B, lbs, ite
+            P.vocab_size, P.vocab_size_padded = self.vocab_size, Vp
+            P.temperature = self.temperature.data_ptr() + lo * 4
+            P.repetition_penalty = self.penalty.data_ptr() + lo * 4
+            P.penalty_type = self.penalty_type
+            P.min_lengths = self.min_length.data_ptr() + lo * 4
+            if topk_on:
+                P.topk_states = self.topk.curand.data_ptr() + lo * CURAND_STATE_BYTES
+                P.topk_ks = self.topk.top_ks.data_ptr() + lo * 4
+                P.topk_ps = self.topk.top_ps.data_ptr() + lo * 4
+                P.topk_skip = self.topk.skip.data_ptr() + lo
+                P.max_top_k = self.max_top_k
+            if topp_on:
+                P.topp_states = self.topp.curand.data_ptr() + lo * CURAND_STATE_BYTES
+                P.topp_ps = self.topp.top_ps.data_ptr() + lo * 4
+                P.topp_skip = self.topp.skip.data_ptr() + lo
+                P.topp_initial_ps = self.topp.initial.data_ptr() + lo * 4
+                P.topp_decay = self.topp.decay.data_ptr() + lo * 4
+                P.topp_min = self.topp.min.data_ptr() + lo * 4
+                P.topp_reset_ids = self.topp.reset.data_ptr() + lo * 4
+            P.row_order = self._g["order"].data_ptr()
+            self._g["params"], self._g["params_key"] = P, (B, lbs, ite, topk_on, topp_on)
         P.dtype = _DT[logits.dtype]
-        P.batch_size, P.local_batch_size, P.ite = B, lbs, ite
-        P.vocab_size, P.vocab_size_padded = self.vocab_size, Vp
         P.step, P.max_input_length = step, mil
         P.logits = logits.data_ptr() + lo * Vp * es
         bias = inputs.get("embedding_bias")
@@ -330,29 +355,12 @@ class DynamicDecodeLayer:
             L = bw.shape[-1]
             P.bad_words = bw.data_ptr() if shared else bw.data_ptr() + lo * 2 * L * 4
             P.bad_words_len, P.bad_words_shared = L, int(shared)
+        else:
+            P.bad_words, P.bad_words_len, P.bad_words_shared = None, 0, 0
         # host-side gating of the penalty kernels (BaseSamplingLayer.cc:302-349)
-        P.temperature = self.temperature.data_ptr() + lo * 4
         P.apply_temperature = int(bias is not None or self._g["temp"])
-        P.repetition_penalty = self.penalty.data_ptr() + lo * 4
-        P.penalty_type = self.penalty_type
         P.apply_repetition = int(step > 1 and self.penalty_type != 2 and self._g["pen"])
-        P.min_lengths = self.min_length.data_ptr() + lo * 4
         P.apply_min_length = int(self._g["minlen"] > step - mil)
-
-        if topk_on:
-            P.topk_states = self.topk.curand.data_ptr() + lo * CURAND_STATE_BYTES
-            P.topk_ks = self.topk.top_ks.data_ptr() + lo * 4
-            P.topk_ps = self.topk.top_ps.data_ptr() + lo * 4
-            P.topk_skip = self.topk.skip.data_ptr() + lo
-            P.max_top_k = self.max_top_k
-        if topp_on:
-            P.topp_states = self.topp.curand.data_ptr() + lo * CURAND_STATE_BYTES
-            P.topp_ps = self.topp.top_ps.data_ptr() + lo * 4
-            P.topp_skip = self.topp.skip.data_ptr() + lo
-            P.topp_initial_ps = self.topp.initial.data_ptr() + lo * 4
-            P.topp_decay = self.topp.decay.data_ptr() + lo * 4
-            P.topp_min = self.topp.min.data_ptr() + lo * 4
-            P.topp_reset_ids = self.topp.reset.data_ptr() + lo * 4
 
         def sl(key, width):
             t = outputs.get(key)
@@ -362,11 +370,9 @@ class DynamicDecodeLayer:
         P.finished = sl("finished", 1)
         P.cum_log_probs = sl("cum_log_probs", 4)
         olp = outputs.get("output_log_probs")
-        if olp is not None:
-            # [request_output_len, batch] sliced at (step - max_input_length) (DynamicDecodeLayer.cc:427-435)
-            P.output_log_probs = olp.data_ptr() + ((step - mil) * B + lo) * 4
+        # [request_output_len, batch] sliced at (step - max_input_length) (DynamicDecodeLayer.cc:427-435)
+        P.output_log_probs = None if olp is None else olp.data_ptr() + ((step - mil) * B + lo) * 4
 
-        P.row_order = self._g["order"].data_ptr()
         if self._workspace is None or self._ws_key != (P.dtype, lbs, Vp):
             need = C.c_size_t(0)
             check(lib.ftb200_sampling_workspace_bytes(P.dtype, lbs, Vp, C.byref(need)))
@@ -375,7 +381,7 @@ class DynamicDecodeLayer:
             self._ws_key = (P.dtype, lbs, Vp)
         P.workspace = self._workspace.data_ptr()
         P.workspace_bytes = self._workspace.numel()
-        P.stream = self._stream_ptr().value
+        P.stream = self._stream.value
         if self.time_kernels:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
