@@ -876,33 +876,50 @@ __device__ __forceinline__ bool fast_topp_tail(const KParams& P, const FMap& S, 
         mhi += __expf(fkey_inv(~(u32)(spec[i] >> 32)) - maxv);
     }
     mhi = f_block_sum(mhi, s_w);
-    if (tid == 0) {
-        const float scale  = __expf(value_of(smax_key) - maxv) * ((float)(nfull * 8) / (float)(kThreads * 8));
-        float       lo_all = mass_tail;
-        for (int b = 0; b < kFMassBins; ++b) {
-            lo_all += (float)s_mass[b] * (1.0f / 1048576.0f);
+    if (wid == 0) {
+        // (warp 0: four mass bins per lane, a scan over the lanes; the sums are estimates, their order is free)
+        static_assert(kFMassBins == 128, "four bins per lane");
+        const float scale = __expf(value_of(smax_key) - maxv) * ((float)(nfull * 8) / (float)(kThreads * 8));
+        float       mb[4], mine = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            mb[i] = (float)s_mass[lane * 4 + i] * (1.0f / 1048576.0f);
+            mine += mb[i];
         }
+        float incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, incl, o);
+            incl += lane >= o ? t : 0.0f;
+        }
+        const float lo_all = mass_tail + __shfl_sync(0xffffffffu, incl, 31);
         const float d_est  = mhi + scale * lo_all;
-        float       share  = 1.02f * H.u * H.top_p + 0.05f;
+        const float share  = 1.02f * H.u * H.top_p + 0.05f;
         const float target = share * d_est;
-        u32         cut    = thr_key;
-        if (mhi < target) {
-            float acc = mhi;
-            int   b   = 0;
-            for (; b < kFMassBins; ++b) {
-                acc += scale * (float)s_mass[b] * (1.0f / 1048576.0f);
-                if (acc >= target) {
-                    break;
+        // first bin at which the running mass reaches the target (128: none)
+        float acc   = mhi + scale * (incl - mine);
+        int   first = kFMassBins;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc += scale * mb[i];
+            if (acc >= target && first == kFMassBins) {
+                first = lane * 4 + i;
+            }
+        }
+        const u32 hit = __ballot_sync(0xffffffffu, first < kFMassBins);
+        const int b   = hit != 0 ? __shfl_sync(0xffffffffu, first, __ffs(hit) - 1) : kFMassBins;
+        if (lane == 0) {
+            u32 cut = thr_key;
+            if (mhi < target) {
+                const u32 down = 16u * (u32)(b + 2);
+                cut            = thr_key > down ? thr_key - down : 1u;
+                if (thr_key - cut > (u32)kFBins) {
+                    cut = thr_key - (u32)kFBins;
                 }
             }
-            const u32 down = 16u * (u32)(b + 2);
-            cut            = thr_key > down ? thr_key - down : 1u;
-            if (thr_key - cut > (u32)kFBins) {
-                cut = thr_key - (u32)kFBins;
-            }
+            s_cut  = cut;
+            s_fail = 0;
         }
-        s_cut  = cut;
-        s_fail = 0;
     }
     for (int i = tid; i < kFBins; i += kThreads) {
         hlo[i] = 0;  // (the raw values of the special columns are done with: the listed ones carry their final value)
