@@ -1492,9 +1492,14 @@ __device__ __forceinline__ bool fast_topp_tail(const KParams& P, const FMap& S, 
 // (nothing of the row's state has been touched then).  CTA-collective.  `stage1` / `stage2` are the hooks
 // of the next row's header (run by thread 0 at points where the loads of the previous stage have had time
 // to land).
-template<int DT, bool TOPP, class S1, class S2>
+// VP: the row of a vocabulary-parallel local pass (top-k rows only).  The logits are one column shard of the
+// vocabulary: token ids become columns by subtracting P.vocab_offset, and instead of drawing the row hands every
+// column whose value reaches the shard's k-th value (whole tie class) to the exchange record, as topk_tail does.
+template<int DT, bool TOPP, int VP, class S1, class S2>
 __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const FHdr& H, u64* trace, S1&& stage1, S2&& stage2)
 {
+    static_assert(!(TOPP && VP), "the record form serves top-k rows");
+    const int id_shift = VP ? P.vocab_offset : 0;
     __shared__ u32   s_mass[kFMassBins];  // sample mass per bin, in units of 2^-20 (integer adds are native)
     __shared__ float s_mtail[kWarps];
     __shared__ u32   s_smaxkey, s_vmaxkey;
@@ -1622,7 +1627,7 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
         for (int t = wt; t < nhist; t += wn) {
             const int id = stage_ids[t];
             if (id >= 0) {
-                f_hash_insert(hash, P.hash_slots, P.hash_shift, id, kFlagHist, P.vocab_padded);
+                f_hash_insert(hash, P.hash_slots, P.hash_shift, id - id_shift, kFlagHist, P.vocab_padded);
             }
         }
         for (int i = wt; i < L; i += wn) {
@@ -1645,14 +1650,14 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
             }
             if (b) {
                 const int tok = stage_words[e1 - 1];
-                if (0 < tok && tok < P.vocab_padded) {
-                    f_hash_insert(hash, P.hash_slots, P.hash_shift, tok, kFlagDead, P.vocab_padded);
+                if (0 < tok && (VP || tok < P.vocab_padded)) {
+                    f_hash_insert(hash, P.hash_slots, P.hash_shift, tok - id_shift, kFlagDead, P.vocab_padded);
                 }
             }
         }
         if (P.apply_minlen && wt == 0) {
             if (P.seq_len[r] + 1 - P.max_input_len < P.min_lengths[r]) {
-                f_hash_insert(hash, P.hash_slots, P.hash_shift, H.end_id, kFlagDead, P.vocab_padded);
+                f_hash_insert(hash, P.hash_slots, P.hash_shift, H.end_id - id_shift, kFlagDead, P.vocab_padded);
             }
         }
     }
@@ -1766,6 +1771,69 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
     const int n_ord = (int)s_ncand, n_sp = (int)s_nspec;
     if (s_bad || n_ord > kFCap || n_sp > spec_cap || n_ord + n_sp < (TOPP ? 1 : k)) {
         return false;
+    }
+    if constexpr (VP != 0) {
+        // ---- vocabulary-parallel local pass: the record of this row (see topk_tail) ----
+        const int n = n_ord + n_sp;
+        if (n > kFCap / 2) {
+            return false;  // (the entries are sorted as 64-bit words in the candidate area)
+        }
+        __shared__ int s_m;
+        u64* const     big = (u64*)cand;
+        FTB_ASSUME_SHARED(big);
+        {
+            constexpr int PER = (kFCap / 2 + kThreads - 1) / kThreads;
+            u64           mine[PER];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int a = tid + i * kThreads;
+                mine[i]     = ~0ull;
+                if (a < n_ord) {
+                    const u32 e = cand[a];
+                    const u32 kv = fkey(f_value<DT>(key16_inv(thr_key + (e >> 20)), temp, H.inv_t, H.inv_t_h));
+                    mine[i]      = ((u64)(~kv) << 32) | (u64)(e & 0xfffffu);
+                }
+                else if (a < n) {
+                    mine[i] = spec[a - n_ord];
+                }
+            }
+            __syncthreads();  // every 32-bit entry has been read before the 64-bit ones take its place
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int a = tid + i * kThreads;
+                if (a < n) {
+                    big[a] = mine[i];
+                }
+            }
+        }
+        __syncthreads();
+        group_sort_u64(big, n, tid, kThreads, CtaSync());
+        __syncthreads();
+        const int k_eff = k < n ? k : n;
+        if (tid == 0) {
+            s_m = k_eff;
+        }
+        __syncthreads();
+        const u32 kv = (u32)(big[k_eff - 1] >> 32);
+        if (DT == FTB200_F16 && temp && ~kv == fkey(thr_y)) {
+            return false;  // half products round: patterns below the threshold may share the lowest class's value
+        }
+        for (int i = k_eff + tid; i < n; i += kThreads) {
+            if ((u32)(big[i] >> 32) == kv) {
+                atomicMax(&s_m, i + 1);
+            }
+        }
+        __syncthreads();
+        const int m   = s_m;
+        u64*      out = P.vp_out + (size_t)r * (P.vp_cap + 2);
+        if (tid == 0) {
+            out[0] = m > P.vp_cap ? ~0ull : (u64)m;  // ~0: more ties than the exchange record holds
+        }
+        for (int i = tid; i < m && i < P.vp_cap; i += kThreads) {
+            const u64 e = big[i];
+            out[1 + i]  = (e & 0xffffffff00000000ull) | (u64)((u32)(e & 0xffffffffu) + (u32)P.vocab_offset);
+        }
+        return true;
     }
     if constexpr (TOPP) {
         if (n_ord < 1 || G.head != 0) {
@@ -2042,7 +2110,7 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
     return true;
 }
 
-template<int DT, bool TOPP>
+template<int DT, bool TOPP, int VP = 0>
 __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(const __grid_constant__ KParams P)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -2101,7 +2169,7 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
         bool       done   = false;
         int* const id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
         const bool topp_row = H.mode == 2 && !H.fin;
-        if (topp_row != TOPP) {
+        if (VP == 0 && topp_row != TOPP) {
             // the other kernel's row
             stage1();
             stage2();
@@ -2112,7 +2180,19 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
             }
             continue;
         }
-        if (H.mode != 0 && !H.fin) {
+        if (VP != 0 && !(H.mode == 1 && !H.fin)) {
+            // vocabulary-parallel local pass: a top-p row is left to the general kernel (its statistics form), any
+            // other row has nothing to send
+            stage1();
+            stage2();
+            if (!topp_row) {
+                if (tid == 0) {
+                    P.vp_out[(size_t)r * (P.vp_cap + 2)] = 0;
+                }
+                done = true;
+            }
+        }
+        else if (H.mode != 0 && !H.fin) {
             const FGeo G  = f_geometry(P, r);
             // (a penalty that can raise a value - repetition below 1, presence below 0 - would make columns
             //  under the threshold candidates: those rows go to the general kernel)
@@ -2122,8 +2202,8 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
                             && (P.apply_rep ? P.step : 0) <= kFMaxHist
                             && (P.bad_words != nullptr ? P.bad_words_len : 0) <= kFMaxWords;
             if (ok) {
-                done = fast_row<DT, TOPP>(P, S, H, rec, stage1, stage2);
-                if (done && tid == 0) {
+                done = fast_row<DT, TOPP, VP>(P, S, H, rec, stage1, stage2);
+                if (VP == 0 && done && tid == 0) {
                     curandState_t* states = H.mode == 1 ? P.topk_states : P.topp_states;
                     curandState_t  st     = states[r];
                     (void)curand_uniform(&st);
@@ -2175,7 +2255,7 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
             if (!done) {
                 P.redo_rows[atomicAdd(P.redo_count, 1u)] = r;
             }
-            else if (P.topp_states != nullptr && P.topp_decay != nullptr) {
+            else if (VP == 0 && P.topp_states != nullptr && P.topp_decay != nullptr) {
                 // top-p decay / reset (kernels/sampling_topp_kernels.cu:1381-1408), applied to every row of the call
                 const int id = *id_out;
                 float     p  = P.topp_ps[r];
@@ -2194,7 +2274,7 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
     }
 }
 
-template<int DT, bool TOPP>
+template<int DT, bool TOPP, int VP = 0>
 int fast_sampling_occupancy(size_t smem, int* per_sm)
 {
     // per device: the opt-in to the shared-memory size (a per-device attribute of the kernel) and the answer
@@ -2210,20 +2290,20 @@ int fast_sampling_occupancy(size_t smem, int* per_sm)
     }
     std::lock_guard<std::mutex> lock(mu);
     if (set_smem[dev] != smem) {
-        FTB_CUDA_CHECK(cudaFuncSetAttribute(fast_sampling_kernel<DT, TOPP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        FTB_CUDA_CHECK(cudaFuncSetAttribute(fast_sampling_kernel<DT, TOPP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)smem));
         FTB_CUDA_CHECK(
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&val[dev], fast_sampling_kernel<DT, TOPP>, kThreads, smem));
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&val[dev], fast_sampling_kernel<DT, TOPP, VP>, kThreads, smem));
         set_smem[dev] = smem;
     }
     *per_sm = val[dev];
     return FTB200_OK;
 }
 
-template<int DT, bool TOPP>
+template<int DT, bool TOPP, int VP = 0>
 int fast_sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st)
 {
-    fast_sampling_kernel<DT, TOPP><<<grid, kThreads, smem, st>>>(K);
+    fast_sampling_kernel<DT, TOPP, VP><<<grid, kThreads, smem, st>>>(K);
     FTB_CUDA_CHECK(cudaGetLastError());
     return FTB200_OK;
 }

@@ -16,10 +16,14 @@ extern template int sampling_occupancy<FTB200_BF16>(size_t, int*);
 extern template int sampling_launch<FTB200_F32>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_F16>(const KParams&, int, size_t, cudaStream_t);
 extern template int sampling_launch<FTB200_BF16>(const KParams&, int, size_t, cudaStream_t);
-template<int DT, bool TOPP>
+template<int DT, bool TOPP, int VP = 0>
 int fast_sampling_occupancy(size_t smem, int* per_sm);
-template<int DT, bool TOPP>
+template<int DT, bool TOPP, int VP = 0>
 int fast_sampling_launch(const KParams& K, int grid, size_t smem, cudaStream_t st);
+extern template int fast_sampling_occupancy<FTB200_F16, false, 1>(size_t, int*);
+extern template int fast_sampling_occupancy<FTB200_BF16, false, 1>(size_t, int*);
+extern template int fast_sampling_launch<FTB200_F16, false, 1>(const KParams&, int, size_t, cudaStream_t);
+extern template int fast_sampling_launch<FTB200_BF16, false, 1>(const KParams&, int, size_t, cudaStream_t);
 extern template int fast_sampling_occupancy<FTB200_F16, false>(size_t, int*);
 extern template int fast_sampling_occupancy<FTB200_BF16, false>(size_t, int*);
 extern template int fast_sampling_launch<FTB200_F16, false>(const KParams&, int, size_t, cudaStream_t);
@@ -410,6 +414,37 @@ extern "C" int ftb200_vocab_parallel_local(const ftb200_sampling_params* p, int 
     K.vocab_offset = vocab_offset;
     cudaStream_t st = (cudaStream_t)p->stream;
     FTB_CUDA_CHECK(cudaMemsetAsync(K.ticket, 0, 256, st));
+    // 16-bit shards of at least 16 k columns: the single-pass kernel in its record form serves the top-k rows and
+    // leaves a list of the others (top-p rows of the statistics form, rows it cannot decide) to the kernel below
+    const bool single_pass = g_fast_path && p->dtype != FTB200_F32 && K.bias == nullptr && p->vocab_size_padded <= (1 << 20)
+                             && p->vocab_size >= 16384 + 16 && (K.apply_rep ? p->step : 0) <= fast_max_history()
+                             && (K.bad_words != nullptr ? K.bad_words_len : 0) <= fast_max_words();
+    if (single_pass) {
+        const size_t fsmem = fast_smem_for(K.hash_slots, p->vocab_size_padded, false);
+        const bool   f16   = p->dtype == FTB200_F16;
+        int          fper  = 0;
+        rc = f16 ? fast_sampling_occupancy<FTB200_F16, false, 1>(fsmem, &fper) :
+                   fast_sampling_occupancy<FTB200_BF16, false, 1>(fsmem, &fper);
+        if (rc != FTB200_OK) {
+            return rc;
+        }
+        if (fper >= 1) {
+            KParams F    = K;
+            F.redo_count = K.ticket + 1;
+            F.redo_rows  = (int*)((char*)p->workspace + 256);
+            int fgrid    = sm_count() * fper;
+            fgrid        = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;
+            rc = f16 ? fast_sampling_launch<FTB200_F16, false, 1>(F, fgrid, fsmem, st) :
+                       fast_sampling_launch<FTB200_BF16, false, 1>(F, fgrid, fsmem, st);
+            if (rc != FTB200_OK) {
+                return rc;
+            }
+            note_launch(1);
+            K.ticket        = K.ticket + 2;
+            K.row_order     = F.redo_rows;
+            K.row_count_dev = F.redo_count;
+        }
+    }
     switch (p->dtype) {
         case FTB200_F32: rc = sampling_launch<FTB200_F32>(K, grid, smem, st); break;
         case FTB200_F16: rc = sampling_launch<FTB200_F16>(K, grid, smem, st); break;

@@ -7,7 +7,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n_shards,shard,k", [(8, 4000, 64), (4, 2560, 5), (2, 8192, 1), (8, 1024, 40)])
+# (shards of 16400 columns and more of 16-bit logits take the single-pass kernel in its record form)
+@pytest.mark.parametrize("n_shards,shard,k", [(8, 4000, 64), (4, 2560, 5), (2, 8192, 1), (8, 1024, 40), (2, 32000, 64),
+                                              (4, 16448, 40), (2, 20000, 1), (2, 32768, 300), (3, 17000, 1000)])
 @pytest.mark.parametrize("coarse", [False, True], ids=["distinct", "ties"])
 def test_shards_match_full_row(n_shards, shard, k, coarse, cuda_device):
     from fastertransformer_b200 import DynamicDecodeLayer
@@ -26,7 +28,8 @@ def test_shards_match_full_row(n_shards, shard, k, coarse, cuda_device):
                 "sequence_length": torch.full((B,), mil, dtype=torch.int32, device=cuda_device)}
 
     full = DynamicDecodeLayer(V, V, torch.bfloat16, cuda_device)
-    vp = VocabParallelSampler(V, shard, n_shards, torch.bfloat16, cuda_device)
+    # (room in the records for the tie classes of the coarse case: about a hundred columns share a value there)
+    vp = VocabParallelSampler(V, shard, n_shards, torch.bfloat16, cuda_device, cap_extra=512 if coarse else 64)
     full.setup(B, 1, args)
     vp.setup(B, 1, args)
     s_full, s_vp = state(), state()
@@ -97,7 +100,8 @@ def test_vocab_parallel_top_p_rows_exact(dtype, n_shards, shard, sigma, all_top_
 
 @pytest.mark.parametrize("resolve", [True, False], ids=["second_round", "report_only"])
 @pytest.mark.parametrize("dtype,n_shards,sigma,max_undecided", [(torch.bfloat16, 4, 4.0, 0.2), (torch.float16, 2, 5.0, 0.2),
-                                                                (torch.float32, 8, 6.0, 0.2), (torch.bfloat16, 4, 1.2, 1.0)])
+                                                                (torch.float32, 8, 6.0, 0.2), (torch.bfloat16, 4, 1.2, 1.0),
+                                                                (torch.bfloat16, 2, 4.0, 0.2)])
 def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, resolve, cuda_device):
     """The approximate form (top_p="statistics"): mixed top-k / top-p rows over a sharded vocabulary against the
     unsharded kernel.  Top-k rows must be identical.  Top-p rows combine per-shard soft-max statistics, so their denominator is summed in another
@@ -106,7 +110,9 @@ def test_vocab_parallel_top_p_rows(dtype, n_shards, sigma, max_undecided, resolv
     untouched generator."""
     from fastertransformer_b200 import DynamicDecodeLayer
     from fastertransformer_b200.vocab_parallel import VocabParallelSampler
-    B, shard, mil, steps = 96, 4096, 6, 4
+    # (two shards: wide ones, which take the single-pass kernel for the top-k rows and leave the top-p rows to the
+    #  general kernel's statistics form)
+    B, shard, mil, steps = 96, (4096 if n_shards > 2 or dtype != torch.bfloat16 else 17408), 6, 4
     V = shard * n_shards
     rng = np.random.default_rng(17 + n_shards)
     args = {"runtime_top_k": rng.choice(np.asarray([0, 0, 8, 40], np.uint32), size=B),
