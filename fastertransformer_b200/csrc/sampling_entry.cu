@@ -476,7 +476,7 @@ extern "C" int ftb200_vocab_parallel_merge(const ftb200_sampling_params* p, cons
     }
     K.vp_cap        = cap;
     cudaStream_t st = (cudaStream_t)p->stream;
-    grid            = sm_count() * 2 < p->local_batch_size ? sm_count() * 2 : p->local_batch_size;
+    grid            = sm_count() * 3 < p->local_batch_size ? sm_count() * 3 : p->local_batch_size;  // (3 CTAs of 52 KB per SM)
     switch (p->dtype) {
         case FTB200_F32: rc = vp_merge_launch<FTB200_F32>(K, (const u64*)gathered, n_ranks, overflow_count, grid, st); break;
         case FTB200_F16: rc = vp_merge_launch<FTB200_F16>(K, (const u64*)gathered, n_ranks, overflow_count, grid, st); break;

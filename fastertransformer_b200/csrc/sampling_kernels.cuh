@@ -4213,7 +4213,7 @@ __device__ __noinline__ void vp_merge_topp_row(const KParams& P, const Smem& S, 
 // union is sorted and handed to the same draw and tie-order code as the single-GPU path, so every rank
 // arrives at the id the reference would sample from the full row.
 template<int DT>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nranks, int* overflow)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
