@@ -1610,7 +1610,10 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
     const int ncols  = nfull * 8;
     // columns the threshold should let through: 2k, at least k + 256 (the estimate from a few sampled maxima
     // scatters widely); for k = 1 a handful is enough
-    const int target = TOPP ? 2048 : (k == 1 ? 64 : (2 * k > k + 256 ? 2 * k : k + 256));
+    // (a top-p row of a smaller vocabulary aims lower: the estimate needs the wanted rank well inside the 256
+    //  per-thread maxima of the sample, want_s <= 96 below)
+    const int tp_cap = (int)(((long long)ncols * 96) / (kFSampleV * kThreads * 8));
+    const int target = TOPP ? (tp_cap < 2048 ? tp_cap : 2048) : (k == 1 ? 64 : (2 * k > k + 256 ? 2 * k : k + 256));
     u32       want_s = (u32)(((long long)target * (kFSampleV * kThreads * 8) + ncols - 1) / ncols);
     want_s           = want_s < 3u ? 3u : want_s;
     bool words_ok    = true;
@@ -2169,8 +2172,9 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
         bool       done   = false;
         int* const id_out = P.output_ids + (size_t)P.step * P.batch_size + (size_t)P.ite * P.local_batch + r;
         const bool topp_row = H.mode == 2 && !H.fin;
-        if (VP == 0 && topp_row != TOPP) {
-            // the other kernel's row
+        if (VP == 0 && topp_row != TOPP && !(TOPP && P.topk_states == nullptr)) {
+            // the other kernel's row (a call without a top-k layer launches the top-p rows' kernel alone, and that one
+            // then looks after every row)
             stage1();
             stage2();
             __syncthreads();

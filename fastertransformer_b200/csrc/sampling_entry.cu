@@ -326,10 +326,11 @@ int ftb200::decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork
             // The rows of the top-p layer have a kernel of their own (it wants more registers than the top-k rows'
             // kernel can spare); the two run side by side, the top-p one on a second stream that forks from and
             // joins the caller's.  Each walks the row list and skips the other's rows.
-            SideStream* side = nullptr;
+            SideStream* side      = nullptr;
+            const bool  topp_only = K.topp_states != nullptr && K.topk_states == nullptr;  // no fork, one launch
             if (K.topp_states != nullptr) {
                 cudaStream_t pst = st;
-                if (fork) {
+                if (fork && !topp_only) {
                     rc = side_stream(&side);
                     if (rc != FTB200_OK) {
                         return rc;
@@ -350,14 +351,16 @@ int ftb200::decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork
                     FTB_CUDA_CHECK(cudaEventRecord(side->join, side->stream));
                 }
             }
-            int fgrid = sm_count() * fper;
-            fgrid     = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;
-            rc = f16 ? fast_sampling_launch<FTB200_F16, false>(F, fgrid, fsmem, st) :
-                       fast_sampling_launch<FTB200_BF16, false>(F, fgrid, fsmem, st);
-            if (rc != FTB200_OK) {
-                return rc;
+            if (!topp_only) {
+                int fgrid = sm_count() * fper;
+                fgrid     = fgrid < p->local_batch_size ? fgrid : p->local_batch_size;
+                rc = f16 ? fast_sampling_launch<FTB200_F16, false>(F, fgrid, fsmem, st) :
+                           fast_sampling_launch<FTB200_BF16, false>(F, fgrid, fsmem, st);
+                if (rc != FTB200_OK) {
+                    return rc;
+                }
+                note_launch(1);
             }
-            note_launch(1);
             if (side != nullptr) {
                 FTB_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
             }
