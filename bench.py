@@ -7,19 +7,25 @@ Workload: configuration 3 of the baseline - batch 1024, vocab 128256, bf16 logit
 per-row top-k in {0,1,40,1024} / top-p in {0,0.5,0.95}, repetition penalty 1.1 over a 512-token prompt
 plus everything generated so far, 8 bad words per row, end id 128001, length criterion.  Seeded synthetic
 logits stand in for a model (no dataset is involved).  A step is one pass of the path over the batch:
-the fused sampling kernel, the stop-criteria kernel and the host read of should_stop.
+the fused sampling step (the single-pass kernels of the top-p and of the top-k rows side by side, then the
+general kernel on the rows they leave), the stop-criteria kernel and the host read of should_stop.
 
 One JSON line on stdout (rank 0):
   value      sampled tokens/s with the logits resident in HBM (4 distinct 263 MB buffers rotate, so no
              step finds its logits in the 126 MB L2), CUDA events around exactly K steps, max over ranks
   e2e        same metric with the step's logits starting in pinned HOST memory and the sampled ids read
              back to the host, copies inside the timed region
-  roofline   algorithmic bytes of one launch of the fused kernel / its mean CUDA-event duration,
+  roofline   algorithmic bytes of one step / the mean CUDA-event duration of its sampling launches,
              against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  e2e_cpp_classes  (N = 1) the end-to-end leg once more with the host side in C++ (the driver of the C++
+             decode layers, fastertransformer_b200/lib/shim_driver)
+  other_configs    (N > 1) config 5 (vocabulary in N shards, one all-gather per step) and config 4 (beam
+             search, batch-sharded) measured in the same process group
   cpu_baseline  the CPU oracle (oracle/ft_oracle.cpp) on a bounded sample, all host cores
 --impl reference times the unmodified FasterTransformer kernels (oracle/_ref, built for sm_100a from the
-reference sources) on the same workload through the reference's own DynamicDecodeLayer<float>; the
-reference has no bf16 path, so it is fed the lossless fp32 up-cast, as its own models do.
+reference sources) on the same workload, seeds and rank layout through the reference's own
+DynamicDecodeLayer<float> (on every rank at N > 1); the reference has no bf16 path, so it is fed the lossless
+fp32 up-cast, as its own models do.
 """
 import argparse
 import copy
