@@ -4220,6 +4220,8 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
     __shared__ float                              s_u;
     __shared__ u32                                s_n;
     __shared__ curandState_t                      s_before_k;  // generator of a top-k row before its draw
+    constexpr int                                 kMergeRanks = 64;
+    __shared__ u32                                s_off[kMergeRanks + 1];  // start of every rank's record in the union
     Smem                                          S;
     S.cand  = (u64*)smem_raw;
     S.hist  = (u32*)(S.cand + kCap);
@@ -4274,6 +4276,9 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
                     S.cand[base + i] = rec[1 + i];
                 }
                 if (tid == 0) {
+                    if (q < kMergeRanks) {
+                        s_off[q] = base, s_off[q + 1] = base + (u32)c;
+                    }
                     s_n = base + (u32)c;
                 }
             }
@@ -4287,12 +4292,49 @@ vp_merge_kernel(const __grid_constant__ KParams P, const u64* gathered, int nran
             }
             continue;
         }
-        const int n = (int)s_n;
-        group_sort_u64(S.cand, n, tid, kThreads, CtaSync());
-        __syncthreads();
+        const int n      = (int)s_n;
+        u64*      sorted = S.cand;
+        if (nranks <= kMergeRanks && n <= kCap / 2) {
+            // every rank's record is sorted already: the place of an entry in the union is its index in its own
+            // record plus the number of smaller entries in each of the others (a binary search each; the entries are
+            // distinct).  No sorting network, two barriers.
+            u64* const dst = S.cand + kCap / 2;
+            for (int a = tid; a < n; a += kThreads) {
+                int q = 0;
+                while (q + 1 < nranks && (u32)a >= s_off[q + 1]) {
+                    ++q;
+                }
+                const u64 e    = S.cand[a];
+                int       rank = a - (int)s_off[q];
+                for (int o = 0; o < nranks; ++o) {
+                    if (o == q) {
+                        continue;
+                    }
+                    int lo = (int)s_off[o], hi = (int)s_off[o + 1];  // first entry of record o that is not below e
+                    const int lo0 = lo;
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (S.cand[mid] < e) {
+                            lo = mid + 1;
+                        }
+                        else {
+                            hi = mid;
+                        }
+                    }
+                    rank += lo - lo0;
+                }
+                dst[rank] = e;
+            }
+            __syncthreads();
+            sorted = dst;
+        }
+        else {
+            group_sort_u64(S.cand, n, tid, kThreads, CtaSync());
+            __syncthreads();
+        }
         int k = (int)P.topk_ks[r];
         k     = k < 1 ? 1 : (k > kMaxTopK ? kMaxTopK : k);
-        topk_finish(P, S, O, S.cand, n, k, s_u, P.topk_ps[r], true, false);
+        topk_finish(P, S, O, sorted, n, k, s_u, P.topk_ps[r], true, false);
     }
 }
 
