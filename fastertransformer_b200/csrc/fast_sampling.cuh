@@ -734,21 +734,23 @@ __device__ __noinline__ void f_pass2(const FPass2 A)
             y[uu][2] = f_value<DT>(raw[uu].y & 0xffffu, TEMP, inv_t, inv_t_h);
             y[uu][3] = f_value<DT>(raw[uu].y >> 16, TEMP, inv_t, inv_t_h);
         }
+        {
+            // Special columns: rare for a thread, but some lane of a warp has one in nearly every batch.  One copy of
+            // the code for the whole batch (the column is picked and put back with selects): a copy per column
+            // made the loop body several times larger than the instruction cache likes.
+            u32 todo = em[0] | (em[1] << 4) | (em[2] << 8) | (em[3] << 12);
+            while (todo != 0) {
+                const int j = __ffs(todo) - 1;
+                todo &= todo - 1;
+                float yv = 0.0f;
 #pragma unroll
-        for (int uu = 0; uu < UN; ++uu) {
-            if (em[uu] != 0) {  // rare
-                const int v0 = (m0 + uu) * 1024 + 4 * tid;
-                if (em[uu] & 1u) {
-                    y[uu][0] = patch(y[uu][0], v0);
+                for (int a = 0; a < 4 * UN; ++a) {
+                    yv = j == a ? y[a >> 2][a & 3] : yv;
                 }
-                if (em[uu] & 2u) {
-                    y[uu][1] = patch(y[uu][1], v0 + 1);
-                }
-                if (em[uu] & 4u) {
-                    y[uu][2] = patch(y[uu][2], v0 + 2);
-                }
-                if (em[uu] & 8u) {
-                    y[uu][3] = patch(y[uu][3], v0 + 3);
+                yv = patch(yv, (m0 + (j >> 2)) * 1024 + 4 * tid + (j & 3));
+#pragma unroll
+                for (int a = 0; a < 4 * UN; ++a) {
+                    y[a >> 2][a & 3] = j == a ? yv : y[a >> 2][a & 3];
                 }
             }
         }
