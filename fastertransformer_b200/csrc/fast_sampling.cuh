@@ -738,7 +738,11 @@ __device__ __noinline__ void f_pass2(const FPass2 A)
             // Special columns: rare for a thread, but some lane of a warp has one in nearly every batch.  One copy of
             // the code for the whole batch (the column is picked and put back with selects): a copy per column
             // made the loop body several times larger than the instruction cache likes.
-            u32 todo = em[0] | (em[1] << 4) | (em[2] << 8) | (em[3] << 12);
+            u32 todo = 0;
+#pragma unroll
+            for (int uu = 0; uu < UN; ++uu) {
+                todo |= em[uu] << (4 * uu);
+            }
             while (todo != 0) {
                 const int j = __ffs(todo) - 1;
                 todo &= todo - 1;
