@@ -191,7 +191,7 @@ def workload_config(wname, B, vocab, first_step, K, n_buffers, world):
                    "8 bad words/row, length criterion"}[wname] % (B, vocab)
     return {"workload": label, "rows_per_gpu": B, "history_tokens": "%d..%d" % (first_step, first_step + K),
             "l2": "%d logits buffers rotate, every one larger than the 126 MB L2 or all of them together "
-                  "more than twice its size" % n_buffers,
+                  "more than twice its size; each time round the batch starts one row further down its buffer" % n_buffers,
             "parallelism": "batch-sharded, no collective" if world > 1 else "single GPU"}
 
 
@@ -200,12 +200,29 @@ def n_buffers_for(B, vocab_padded, element_size):
     return max(4, min(200, -(-300_000_000 // (B * vocab_padded * element_size))))
 
 
+POOL_EXTRA_ROWS = 61  # a buffer holds this many rows more than the batch (see step_logits)
+
+
 def make_pool(w, device, dtype, n):
+    """`n` logits buffers of batch + POOL_EXTRA_ROWS rows each."""
+    wide = copy.copy(w)
+    wide.batch = w.batch + POOL_EXTRA_ROWS
     pool = []
     for i in range(n):
-        x = w.logits(10_000 + i, device)
+        x = wide.logits(10_000 + i, device)
         pool.append(x if dtype == w.dtype else x.to(dtype))
     return pool
+
+
+def step_logits(pool, it, batch):
+    """Logits of the `it`-th step of a run: the buffers rotate (so that no step finds its logits in L2), and each
+    time round the batch starts one row further down its buffer, so that a row does not meet the same logits
+    again every len(pool) steps - a model never repeats them, and a row that decodes greedily would otherwise put
+    the largest columns of those few vectors into its own history one by one.  A contiguous view; the row pitch
+    is a multiple of 16 bytes for every configuration."""
+    buf = pool[it % len(pool)]
+    off = (it // len(pool)) % (POOL_EXTRA_ROWS + 1)
+    return buf[off:off + batch]
 
 
 def run_ours(a, rank, world, local):
@@ -228,12 +245,13 @@ def run_ours(a, rank, world, local):
 
     step_no = [w.max_input_length]
 
-    def one_step(logits):
-        layer.forward(st, dict(inputs, logits=logits, step=step_no[0]))
+    def one_step(logits=None):
+        it = step_no[0] - w.max_input_length
+        layer.forward(st, dict(inputs, logits=step_logits(pool, it, B) if logits is None else logits, step=step_no[0]))
         step_no[0] += 1
 
     for i in range(W):
-        one_step(pool[i % N_BUFFERS])
+        one_step()
     torch.cuda.synchronize()
     barrier(world)
     torch.cuda.synchronize()
@@ -247,7 +265,7 @@ def run_ours(a, rank, world, local):
     for i in range(K):
         # the event pair brackets the fused sampling launch; the criteria kernel follows it
         kev[i][0].record()
-        one_step(pool[i % N_BUFFERS])
+        one_step()
         kev[i][1].record()
     ev1.record()
     torch.cuda.synchronize()
@@ -261,7 +279,7 @@ def run_ours(a, rank, world, local):
     # kernel-only duration of the fused launch: events directly around the C-ABI call
     layer.time_kernels = True
     for i in range(min(K, 32)):
-        one_step(pool[i % N_BUFFERS])
+        one_step()
     torch.cuda.synchronize()
     layer.time_kernels = False
     kern_ms = [e0.elapsed_time(e1) for e0, e1 in layer.kernel_events]
@@ -270,10 +288,10 @@ def run_ours(a, rank, world, local):
     # end to end: logits start in pinned host memory, ids come back to the host, every step
     host_pool = [torch.empty(B, w.vocab_padded, dtype=w.dtype).pin_memory() for _ in range(2)]
     for h, d in zip(host_pool, pool):
-        h.copy_(d)
+        h.copy_(d[:B])
     # two device buffers: the copy of the next step's logits (copy stream) runs under this step's kernel; every
     # copy, every kernel and every read-back of the ids lies inside the timed region
-    dev_logits = [torch.empty_like(pool[0]) for _ in range(2)]
+    dev_logits = [torch.empty_like(pool[0][:B]) for _ in range(2)]
     ids_host = torch.empty(B, dtype=torch.int32).pin_memory()
     copy_stream = torch.cuda.Stream(device=device)
     main = torch.cuda.current_stream()
@@ -508,7 +526,7 @@ def run_reference(a, rank, world, local):
     inputs = w.static_inputs(device)
     n_buffers = n_buffers_for(B, w.vocab_padded, torch.empty(0, dtype=w.dtype).element_size())
     pool = make_pool(w, device, ref_dt, min(n_buffers, 4))
-    work = torch.empty_like(pool[0])
+    work = torch.empty_like(pool[0][:B])
     sampler = ClockSampler(local, period=0.02)
     total_ms, n = 0.0, 0
     barrier(world)
@@ -516,7 +534,7 @@ def run_reference(a, rank, world, local):
         if i == W:
             sampler.start()
         step = w.max_input_length + i
-        work.copy_(pool[i % len(pool)])  # the reference overwrites its logits; a model would produce fresh ones
+        work.copy_(step_logits(pool, i, B))  # the reference overwrites its logits; a model would produce fresh ones
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()

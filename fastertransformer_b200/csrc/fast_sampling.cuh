@@ -29,7 +29,8 @@ constexpr int kFSpecCap  = 128;   // listed columns (special or edge) at or abov
 constexpr int kFClsCap   = 768;   // members of the class the draw lands in
 constexpr int kFRuns     = 1536;  // runs the draw may walk (classes + listed columns among the first k)
 constexpr int kFRunBytes = kFRuns * 6 + kFBins * 2;  // top-k draw: value, count per run; class ranks
-constexpr int kFPRuns    = 1792;  // top-p: runs of the replayed scan (probability, first position)
+constexpr int kFPRuns    = 2560;  // top-p: runs of the replayed scan (probability, first position); a long history
+                                  //        adds a run per listed column to the ~1500 patterns of a deep window
 constexpr int kFPSpecCap = 1024;  // top-p: listed columns above the cut
 constexpr int kFPClsCap  = 2048;  // top-p: members of the class the scan stops in
 constexpr int kFSampleV  = 2;     // sampled vectors per thread (4096 columns per row)
@@ -52,18 +53,19 @@ constexpr int kFMaxHist    = 1024;  // token-history entries the single-pass ker
 constexpr int kFMaxWords   = 128;   // bad-word list length it stages
 constexpr int kFStageBytes = 8192;  // >= (kFMaxHist + 2 * kFMaxWords + 4) * 4; later kFPSpecCap listed columns of a top-p row
 // bytes of the per-vector mask area: one byte per aligned vector, and room for what follows the pass
-__host__ __device__ inline size_t fast_mask_bytes(int vocab_padded)
+__host__ __device__ inline size_t fast_mask_bytes(int vocab_padded, bool topp)
 {
     const size_t need = ((size_t)vocab_padded / 8 + 16 + 15) / 16 * 16;
-    size_t post = (size_t)kFSpecCap * 8 + (size_t)kFRunBytes;
-    post        = post > (size_t)kFPRuns * 8 ? post : (size_t)kFPRuns * 8;
-    post        = post > (size_t)kFPClsCap * 4 ? post : (size_t)kFPClsCap * 4;
+    size_t post = (size_t)kFSpecCap * 8 + (size_t)kFRunBytes;  // the top-k rows' kernel
+    if (topp) {
+        post = (size_t)kFPRuns * 8 > (size_t)kFPClsCap * 4 ? (size_t)kFPRuns * 8 : (size_t)kFPClsCap * 4;
+    }
     return need > post ? need : post;
 }
-__host__ __device__ inline size_t fast_smem_bytes(int hash_slots, int vocab_padded, bool /*topp*/)
+__host__ __device__ inline size_t fast_smem_bytes(int hash_slots, int vocab_padded, bool topp)
 {
     const size_t sv = hash_slots > kFBins ? hash_slots : kFBins;  // the value area doubles as a class table
-    return (size_t)kFCap * 4 + fast_mask_bytes(vocab_padded) + (size_t)hash_slots * 4 + sv * 4 + (size_t)kFBins * 4
+    return (size_t)kFCap * 4 + fast_mask_bytes(vocab_padded, topp) + (size_t)hash_slots * 4 + sv * 4 + (size_t)kFBins * 4
            + (size_t)kFStageBytes;
 }
 
@@ -2133,7 +2135,7 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
     S.wj   = s_wj;
     S.cand = (u32*)smem_raw;
     S.emask = S.cand + kFCap;
-    S.hash  = S.emask + fast_mask_bytes(P.vocab_padded) / 4;
+    S.hash  = S.emask + fast_mask_bytes(P.vocab_padded, TOPP) / 4;
     S.sval  = S.hash + P.hash_slots;
     S.hist  = S.sval + (P.hash_slots > kFBins ? P.hash_slots : kFBins);
     S.stage = S.hist + kFBins;
