@@ -181,10 +181,13 @@ int ftb200_last_launch_count(void);
  * trace off (the default). */
 int ftb200_set_row_trace(uint64_t* device_buf);
 
-/* Diagnostic, no counterpart in the reference.  ftb200_decode_step_sampling serves 16-bit logits in two
- * launches: a single-pass kernel (one read of each row, several rows in flight per SM) and then the general
- * kernel on the rows the first one leaves behind.  ftb200_set_single_pass(0) sends every row to the general
- * kernel (the results are the same either way; tests compare the two); 1 (the default) restores the pair. */
+/* Diagnostic, no counterpart in the reference.  ftb200_decode_step_sampling serves 16-bit logits of at least
+ * 16400 columns (no embedding bias, no log-probabilities) in up to three launches: a single-pass kernel for the
+ * top-p rows and one for the top-k rows side by side (one read of each row for a top-k row, several rows in
+ * flight per SM), then the general kernel on the rows those two leave behind; ftb200_vocab_parallel_local does
+ * the same with the top-k rows' kernel in its record form.  ftb200_set_single_pass(0) sends every row to the
+ * general kernel (the results are the same either way; tests compare the two); 1 (the default) restores the
+ * single-pass kernels.  Process-wide. */
 int ftb200_set_single_pass(int on);
 
 /* ------------------------------------------------------------------------------------------
