@@ -63,7 +63,7 @@ __global__ void ban_bad_words_kernel(T* logits, const int* output_ids, const int
 // One CTA: stop words for the local rows, then the length limit and the finished count for the batch.
 __global__ void stop_criteria_kernel(const int* output_ids, const int* parent_ids, const int* stop_words, int L,
                                      uint8_t* finished, const uint32_t* limit, int id_offset, int local_batch,
-                                     int batch_size, int beam_width, int step, int* count_out)
+                                     int batch_size, int beam_width, int step, int* count_out, int* count_host)
 {
     __shared__ int s_count;
     if (threadIdx.x == 0) {
@@ -105,6 +105,9 @@ __global__ void stop_criteria_kernel(const int* output_ids, const int* parent_id
         __syncthreads();
         if (threadIdx.x == 0) {
             *count_out = s_count;
+            if (count_host != nullptr) {
+                *count_host = s_count;  // pinned host memory, written from here: no copy has to follow the kernel
+            }
         }
     }
 }
@@ -164,12 +167,24 @@ extern "C" int ftb200_stop_criteria(const int* output_ids, const int* parent_ids
         return FTB200_OK;
     }
     cudaStream_t st = (cudaStream_t)stream;
+    // Where the host word is page-locked memory the kernel can reach (cudaHostAlloc / cudaMallocHost / a registered
+    // range), the kernel stores the count there itself; otherwise a copy follows it.  Asked on every call: the
+    // same address may be pageable memory the next time.
+    int* direct = nullptr;
+    if (sequence_limit_length != nullptr) {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, finished_count_host) == cudaSuccess && attr.type == cudaMemoryTypeHost
+            && attr.devicePointer != nullptr) {
+            direct = (int*)attr.devicePointer;
+        }
+        (void)cudaGetLastError();  // (an unregistered pointer is reported as an error by older drivers)
+    }
     stop_criteria_kernel<<<1, 1024, 0, st>>>(output_ids, parent_ids, stop_words_len > 0 ? stop_words : nullptr,
                                              stop_words_len, finished, sequence_limit_length, id_offset,
-                                             local_batch_size, batch_size, beam_width, step, finished_count_dev);
+                                             local_batch_size, batch_size, beam_width, step, finished_count_dev, direct);
     FTB_CUDA_CHECK(cudaGetLastError());
     note_launch(1);
-    if (sequence_limit_length != nullptr) {
+    if (sequence_limit_length != nullptr && direct == nullptr) {
         FTB_CUDA_CHECK(cudaMemcpyAsync(finished_count_host, finished_count_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
     }
     return FTB200_OK;
