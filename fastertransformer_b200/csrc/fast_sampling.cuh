@@ -29,9 +29,9 @@ constexpr int kFSpecCap  = 128;   // listed columns (special or edge) at or abov
 constexpr int kFClsCap   = 768;   // members of the class the draw lands in
 constexpr int kFRuns     = 1536;  // runs the draw may walk (classes + listed columns among the first k)
 constexpr int kFRunBytes = kFRuns * 6 + kFBins * 2;  // top-k draw: value, count per run; class ranks
-constexpr int kFPRuns    = 2560;  // top-p: runs of the replayed scan (probability, first position); a long history
+constexpr int kFPRuns    = 3584;  // top-p: runs of the replayed scan (probability, first position); a long history
                                   //        adds a run per listed column to the ~1500 patterns of a deep window
-constexpr int kFPSpecCap = 1024;  // top-p: listed columns above the cut
+constexpr int kFPSpecCap = 2048;  // top-p: listed columns above the cut (a history of 2000 ids puts a thousand in a deep window)
 constexpr int kFPClsCap  = 2048;  // top-p: members of the class the scan stops in
 constexpr int kFSampleV  = 2;     // sampled vectors per thread (4096 columns per row)
 constexpr int kFUnroll   = 8;     // 16-byte loads in flight per thread
@@ -49,7 +49,8 @@ struct FMap {
     unsigned short* wj;    // [kWarps * kFRing]
 };
 
-constexpr int kFMaxHist    = 1024;  // token-history entries the single-pass kernel stages
+constexpr int kFMaxHist    = 1024;  // token-history entries the single-pass kernel stages at a time
+constexpr int kFMaxHistAll = 4094;  // and in all (the table of special columns: step + words + 2 <= 4096)
 constexpr int kFMaxWords   = 128;   // bad-word list length it stages
 constexpr int kFStageBytes = 8192;  // >= (kFMaxHist + 2 * kFMaxWords + 4) * 4; later kFPSpecCap listed columns of a top-p row
 // bytes of the per-vector mask area: one byte per aligned vector, and room for what follows the pass
@@ -66,7 +67,7 @@ __host__ __device__ inline size_t fast_smem_bytes(int hash_slots, int vocab_padd
 {
     const size_t sv = hash_slots > kFBins ? hash_slots : kFBins;  // the value area doubles as a class table
     return (size_t)kFCap * 4 + fast_mask_bytes(vocab_padded, topp) + (size_t)hash_slots * 4 + sv * 4 + (size_t)kFBins * 4
-           + (size_t)kFStageBytes;
+           + (topp ? (size_t)kFPSpecCap * 8 : (size_t)kFStageBytes);  // (the area is the last of the map)
 }
 
 __device__ __forceinline__ void cp_async4(u32 saddr, const void* g)
@@ -1554,7 +1555,7 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
     {
         // (input_lengths is read here, one dependent load: it is the same few cache lines for every row)
         const int input_len = P.apply_rep ? (P.input_lengths != nullptr ? P.input_lengths[r] : P.max_input_len) : 0;
-        for (int t = tid; t < nhist; t += kThreads) {
+        for (int t = tid; t < nhist && t < kFMaxHist; t += kThreads) {
             if (t >= input_len && t < P.max_input_len) {
                 stage_ids[t] = -1;
             }
@@ -1635,7 +1636,7 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
     }
     else {
         const int wt = tid - 32, wn = kThreads - 32;
-        for (int t = wt; t < nhist; t += wn) {
+        for (int t = wt; t < nhist && t < kFMaxHist; t += wn) {
             const int id = stage_ids[t];
             if (id >= 0) {
                 f_hash_insert(hash, P.hash_slots, P.hash_shift, id - id_shift, kFlagHist, P.vocab_padded);
@@ -1673,6 +1674,28 @@ __device__ __forceinline__ bool fast_row(const KParams& P, const FMap& S, const 
         }
     }
     const bool long_words = __syncthreads_or(!words_ok);
+    // a history of more than kFMaxHist ids comes through the staging area a tile at a time
+    for (int base = kFMaxHist; base < nhist; base += kFMaxHist) {
+        const int input_len = P.input_lengths != nullptr ? P.input_lengths[r] : P.max_input_len;
+        for (int t = base + tid; t < nhist && t < base + kFMaxHist; t += kThreads) {
+            if (t >= input_len && t < P.max_input_len) {
+                stage_ids[t - base] = -1;
+            }
+            else {
+                cp_async4((u32)__cvta_generic_to_shared(&stage_ids[t - base]), P.output_ids + (size_t)t * P.batch_size + col);
+            }
+        }
+        cp_async_commit();
+        cp_async_wait_all();
+        __syncthreads();
+        for (int t = base + tid; t < nhist && t < base + kFMaxHist; t += kThreads) {
+            const int id = stage_ids[t - base];
+            if (id >= 0) {
+                f_hash_insert(hash, P.hash_slots, P.hash_shift, id - id_shift, kFlagHist, P.vocab_padded);
+            }
+        }
+        __syncthreads();
+    }
     stage2();
     // per-vector byte: which columns of the vector are special
     for (int i = tid; i < P.hash_slots; i += kThreads) {
@@ -2211,7 +2234,7 @@ __global__ void __launch_bounds__(kThreads, TOPP ? 2 : 3) fast_sampling_kernel(c
             const bool lowers = !P.apply_rep || (P.penalty_type == FTB200_PENALTY_MULTIPLICATIVE ? H.theta >= 1.0f :
                                                  P.penalty_type == FTB200_PENALTY_ADDITIVE ? H.theta >= 0.0f : true);
             const bool ok = lowers && G.nfull >= 2048 && G.nfull <= 65535 && H.inv_t > 0.0f && H.inv_t < 3.0e38f
-                            && (P.apply_rep ? P.step : 0) <= kFMaxHist
+                            && (P.apply_rep ? P.step : 0) <= kFMaxHistAll
                             && (P.bad_words != nullptr ? P.bad_words_len : 0) <= kFMaxWords;
             if (ok) {
                 done = fast_row<DT, TOPP, VP>(P, S, H, rec, stage1, stage2);

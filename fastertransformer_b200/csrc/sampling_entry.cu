@@ -225,6 +225,10 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
     while (slots < 2 * specials) {
         slots <<= 1;
     }
+    // (a large table costs the kernels resident CTAs: above 2048 slots it may be three quarters full)
+    if (slots > 2048 && 3 * (slots / 2) >= 4 * specials) {
+        slots /= 2;
+    }
     K.hash_slots = slots;
     int lg       = 0;
     while ((1 << lg) < slots) {
@@ -233,7 +237,7 @@ static int plan_sampling(const ftb200_sampling_params* p, KParams& K, size_t& sm
     K.hash_shift = 32 - lg;
     smem         = (size_t)kCap * 8 + (size_t)kNB * 4 + 1024 * 4 + (size_t)K.flag_words * 4 + (size_t)slots * 12 + 32
                    + (size_t)kThreads * 16 * 2;
-    if (smem > 200 * 1024) {
+    if (smem > 200 * 1024 || specials > 4096) {
         set_error("ftb200_decode_step_sampling: token history too long for the shared-memory hash");
         return FTB200_UNSUPPORTED;
     }

@@ -8,7 +8,7 @@ size_t fast_smem_for(int hash_slots, int vocab_padded, bool topp)
 }
 int fast_max_history()
 {
-    return kFMaxHist;
+    return kFMaxHistAll;
 }
 int fast_max_words()
 {

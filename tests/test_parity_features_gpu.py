@@ -290,3 +290,26 @@ def test_history_limit_against_reference(cuda_device):
     with pytest.raises(FtbError) as e:
         _run(mine_l, w, cuda_device, steps=5)
     assert e.value.status == 5 and "history too long" in str(e.value)      # FTB200_UNSUPPORTED
+
+
+@pytest.mark.parametrize("dtype,mil", [(torch.bfloat16, 1500), (torch.float16, 1100), (torch.bfloat16, 3000),
+                                       (torch.float16, 4060)])
+def test_long_history_single_pass_rows_against_reference(dtype, mil, cuda_device):
+    """Histories of more than 1024 ids at a vocabulary the single-pass kernels serve: the ids come through the
+    staging area a tile at a time and the table of special columns grows to 4096 / 8192 slots.  Mixed top-k and
+    top-p rows, bad words, three steps, ids / flags / lengths equal to the reference."""
+    from fastertransformer_b200.workloads import SamplingWorkload, _bad_words
+    rng = np.random.default_rng(mil)
+    B, V, steps = 10, 32768, 3
+    args = {"runtime_top_k": np.asarray([1, 0, 40, 0, 8, 1024, 0, 2, 0, 64], np.uint32),
+            "runtime_top_p": np.asarray([0.0, 0.5, 0.9, 0.95, 1.0, 0.7, 0.3, 0.0, 0.8, 0.6], np.float32),
+            "repetition_penalty": np.asarray([1.15], np.float32),
+            "random_seed": (np.arange(B) * 7 + 1).astype(np.uint64)}
+    # (a prompt drawn from a part of the vocabulary, so that many ids repeat as they do in real text)
+    prompt = rng.integers(0, 6000, size=(mil, B)).astype(np.int32)
+    w = SamplingWorkload("longfast", B, V, V, dtype, 2.5, steps, mil, V - 1, args, 77,
+                         bad_words=_bad_words(rng, B, V), prompt=prompt)
+    mine_l, ref_l, ref_dt = _layers(w, cuda_device)
+    ref = _run(ref_l, w, cuda_device, cast=ref_dt, is_ref=True)
+    mine = _run(mine_l, w, cuda_device)
+    _same(mine, ref, "history of %d ids" % mil)
