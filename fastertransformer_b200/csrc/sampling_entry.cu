@@ -84,6 +84,8 @@ static int g_fast_path = 1;  // see ftb200_set_single_pass
 struct SideStream {
     cudaStream_t stream = nullptr;
     cudaEvent_t  fork = nullptr, join = nullptr;
+    std::mutex   use;  // held from the record of `fork` to the wait on `join`: two host threads on one device
+                       // share the stream and the events, and a wait takes the latest record of its event
 };
 static int side_stream(SideStream** out)
 {
@@ -330,7 +332,8 @@ int ftb200::decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork
             // The rows of the top-p layer have a kernel of their own (it wants more registers than the top-k rows'
             // kernel can spare); the two run side by side, the top-p one on a second stream that forks from and
             // joins the caller's.  Each walks the row list and skips the other's rows.
-            SideStream* side      = nullptr;
+            SideStream*                  side      = nullptr;
+            std::unique_lock<std::mutex> side_use;
             const bool  topp_only = K.topp_states != nullptr && K.topk_states == nullptr;  // no fork, one launch
             if (K.topp_states != nullptr) {
                 cudaStream_t pst = st;
@@ -339,6 +342,7 @@ int ftb200::decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork
                     if (rc != FTB200_OK) {
                         return rc;
                     }
+                    side_use = std::unique_lock<std::mutex>(side->use);
                     FTB_CUDA_CHECK(cudaEventRecord(side->fork, st));
                     FTB_CUDA_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
                     pst = side->stream;
@@ -367,6 +371,7 @@ int ftb200::decode_step_sampling_impl(const ftb200_sampling_params* p, bool fork
             }
             if (side != nullptr) {
                 FTB_CUDA_CHECK(cudaStreamWaitEvent(st, side->join, 0));
+                side_use.unlock();
             }
             K.ticket        = K.ticket + 2;
             K.row_order     = F.redo_rows;
